@@ -1,0 +1,34 @@
+"""Seeded synthetic GGUF blocks and activations.
+
+The reference measures on tensors of a real model file, which is not available here; these
+generators stand in for it.  Quant bytes are uniform over 0..255, which is a valid block for every
+format of the path and exercises every codebook entry, sign pattern and sub-block scale; the fp16
+super-block scales are |N(0,1)| * scale so that outputs stay O(1).
+"""
+import numpy as np
+
+from . import formats as F
+
+# byte offsets of the fp16 fields inside one block
+_FP16_FIELDS = {
+    "Q8_0": (0,), "Q4_K": (0, 2), "Q5_K": (0, 2), "Q6_K": (208,),
+    "IQ3_XXS": (0,), "IQ3_S": (0,), "IQ4_XS": (0,),
+}
+
+
+def make_weights(fmt, M: int, K: int, seed: int, scale: float = 1e-3) -> np.ndarray:
+    """Returns a uint8 array [M, row_bytes] of random valid blocks."""
+    f = F.get(fmt)
+    rng = np.random.Generator(np.random.PCG64(seed))
+    nblk = K // f.block_elems
+    w = rng.integers(0, 256, size=(M, nblk, f.block_bytes), dtype=np.uint8)
+    for off in _FP16_FIELDS[f.name]:
+        d = (np.abs(rng.standard_normal((M, nblk), dtype=np.float32)) * np.float32(scale)).astype(np.float16)
+        w[:, :, off:off + 2] = d.view(np.uint8).reshape(M, nblk, 2)
+    return w.reshape(M, nblk * f.block_bytes)
+
+
+def make_activations(nb: int, K: int, seed: int) -> np.ndarray:
+    """fp32 [nb, K], elements N(0,1)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return rng.standard_normal((nb, K), dtype=np.float32)
