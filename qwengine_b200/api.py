@@ -1,0 +1,157 @@
+"""ctypes binding of the C ABI (include/q38b200.h) for torch CUDA tensors.
+
+Mirrors the reference's CUDA-side interface for this path (src/cuda/gemv.cuh:14-37,
+src/cuda/prefill.cuh:17-28): weights are uint8 tensors holding GGUF blocks row by row, outputs are
+``y[c, r]`` (column-major in the reference's sense: column c at ``y + c * y_ld``).
+"""
+import ctypes as C
+import os
+
+import torch
+
+from . import formats as F
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
+_OUT_DTYPES = {OUT_F32: torch.float32, OUT_F16: torch.float16, OUT_BF16: torch.bfloat16}
+
+
+class Q38BError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        super().__init__(f"{what}: {status_string(status)} ({status})")
+
+
+def library_path():
+    return os.path.join(_HERE, "libq38b200.so")
+
+
+def load_library():
+    """Loads libq38b200.so; raises if it has not been built (there is no fallback path)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build it with `python -m qwengine_b200.build` (needs nvcc)")
+    lib = C.CDLL(path)
+    vp, ll, i32, u32, sz = C.c_void_p, C.c_longlong, C.c_int, C.c_uint32, C.c_size_t
+    lib.q38b_ctx_create.argtypes = [i32, C.POINTER(vp)]
+    lib.q38b_ctx_destroy.argtypes = [vp]
+    lib.q38b_ctx_destroy.restype = None
+    lib.q38b_ctx_check.argtypes = [vp, vp]
+    lib.q38b_last_cuda_error.argtypes = [vp]
+    lib.q38b_ctx_set_pdl.argtypes = [vp, i32]
+    lib.q38b_status_string.argtypes = [i32]
+    lib.q38b_status_string.restype = C.c_char_p
+    lib.q38b_format_supported.argtypes = [u32]
+    lib.q38b_row_bytes.argtypes = [u32, i32]
+    lib.q38b_row_bytes.restype = sz
+    lib.q38b_q8k_bytes.argtypes = [i32]
+    lib.q38b_q8k_bytes.restype = sz
+    lib.q38b_quantize_q8k.argtypes = [vp, vp, ll, i32, i32, vp, ll, vp]
+    lib.q38b_gemv_q8k.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
+    lib.q38b_swiglu_q8k.argtypes = [vp, vp, vp, ll, i32, i32, vp, vp, ll, vp]
+    lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
+    _LIB = lib
+    return lib
+
+
+def status_string(status):
+    return load_library().q38b_status_string(int(status)).decode()
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Context:
+    """One per process and GPU (q38b_ctx)."""
+
+    def __init__(self, device=0):
+        self.lib = load_library()
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        self.device = torch.device("cuda", device)
+        h = C.c_void_p()
+        rc = self.lib.q38b_ctx_create(device, C.byref(h))
+        if rc:
+            raise Q38BError(rc, "q38b_ctx_create")
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.q38b_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _rc(self, rc, what):
+        if rc:
+            raise Q38BError(rc, what)
+
+    def check(self):
+        """Synchronises the current stream and raises if a kernel reported a bounded wait that ran out."""
+        self._rc(self.lib.q38b_ctx_check(self.h, _stream()), "q38b_ctx_check")
+
+    def set_pdl(self, enabled):
+        self._rc(self.lib.q38b_ctx_set_pdl(self.h, int(bool(enabled))), "q38b_ctx_set_pdl")
+
+    # ---- activations -------------------------------------------------------------------------
+    def quantize_q8k(self, x, out=None):
+        """x float32 [nb, K] (row stride = x.stride(0)) -> uint8 [nb, K/256*292] of Q8_K blocks."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+        nb, K = x.shape
+        if out is None:
+            out = torch.empty((nb, K // 256 * F.Q8K_BLOCK_BYTES), dtype=torch.uint8, device=x.device)
+        self._rc(self.lib.q38b_quantize_q8k(self.h, x.data_ptr(), x.stride(0), K, nb, out.data_ptr(),
+                                            out.stride(0) // F.Q8K_BLOCK_BYTES, _stream()), "q38b_quantize_q8k")
+        return out
+
+    def swiglu_q8k(self, g, u, want_h=True, want_q=True):
+        """h = silu(g) * u for float32 [nb, n]; returns (h or None, q8k blocks or None)."""
+        assert g.shape == u.shape and g.stride() == u.stride() and g.stride(1) == 1
+        nb, n = g.shape
+        h = torch.empty_like(g) if want_h else None
+        q = torch.empty((nb, n // 256 * F.Q8K_BLOCK_BYTES), dtype=torch.uint8, device=g.device) if want_q else None
+        if h is not None:
+            assert h.stride() == g.stride()
+        self._rc(self.lib.q38b_swiglu_q8k(self.h, g.data_ptr(), u.data_ptr(), g.stride(0), n, nb,
+                                          h.data_ptr() if h is not None else None,
+                                          q.data_ptr() if q is not None else None,
+                                          (q.stride(0) // F.Q8K_BLOCK_BYTES) if q is not None else 0, _stream()),
+                 "q38b_swiglu_q8k")
+        return h, q
+
+    # ---- matvec ------------------------------------------------------------------------------
+    def gemv(self, fmt, W, xq, K, out=None, accumulate=False, M=None):
+        """W uint8 [M, row_bytes]; xq uint8 [nb, K/256*292]; returns y float32 [nb, M] (y[c, r])."""
+        f = F.get(fmt)
+        assert W.is_cuda and W.dtype == torch.uint8 and W.dim() == 2 and W.stride(1) == 1
+        M = W.shape[0] if M is None else M
+        nb = xq.shape[0]
+        if out is None:
+            out = torch.empty((nb, M), dtype=torch.float32, device=W.device)
+        self._rc(self.lib.q38b_gemv_q8k(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, xq.data_ptr(),
+                                        xq.stride(0) // F.Q8K_BLOCK_BYTES, nb, out.data_ptr(), out.stride(0),
+                                        int(bool(accumulate)), _stream()), "q38b_gemv_q8k")
+        return out
+
+    def gemv_raw(self, type_id, W_ptr, row_bytes, K, M, xq_ptr, x_stride, nb, y_ptr, y_ld, accumulate=0):
+        """Unchecked pass-through to q38b_gemv_q8k; returns the status code."""
+        return self.lib.q38b_gemv_q8k(self.h, type_id, W_ptr, row_bytes, K, M, xq_ptr, x_stride, nb, y_ptr, y_ld,
+                                      accumulate, _stream())
+
+    def dequant_rows(self, fmt, W, K, kind=OUT_F32):
+        f = F.get(fmt)
+        rows = W.shape[0]
+        out = torch.empty((rows, K), dtype=_OUT_DTYPES[kind], device=W.device)
+        self._rc(self.lib.q38b_dequant_rows(self.h, f.type_id, W.data_ptr(), W.stride(0), K, rows, out.data_ptr(), kind,
+                                            _stream()), "q38b_dequant_rows")
+        return out

@@ -1,0 +1,210 @@
+// q38b_act.cuh -- activation-side kernels (Q8_K quantizer, SwiGLU) and the exact row dequantizer.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "q38b_decode.cuh"
+
+namespace q38b {
+
+#define Q38B_CODEBOOK_QUALIFIER __device__ const
+#include "codebooks.inc"
+#undef Q38B_CODEBOOK_QUALIFIER
+
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_min_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// One warp writes one ggml Q8_K block from 256 floats held 8 per lane (lane l: elements 8l..8l+7).
+// Same arithmetic as quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381): the first element of largest
+// magnitude, signed, maps to -127 (iscale = -127 / max); q = min(127, round-half-even(iscale * x));
+// bsums per 16 elements; d = 1 / iscale; an all-zero block is all zero bytes.
+__device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t* blk) {
+    const int lane = threadIdx.x & 31;
+    float am = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(v[e]));
+    am = warp_max_f(am);
+    uint32_t w0 = 0, w1 = 0;
+    int s8 = 0;
+    float d = 0.0f;
+    if (am != 0.0f) {
+        int idx = 256;
+        float mine = 0.0f;
+#pragma unroll
+        for (int e = 7; e >= 0; e--)
+            if (fabsf(v[e]) == am) { idx = 8 * lane + e; mine = v[e]; }
+        const int first = warp_min_i(idx);
+        const float mx = __shfl_sync(0xffffffffu, mine, first >> 3);
+        const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int q = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
+            s8 += q;
+            if (e < 4) w0 |= (uint32_t)(q & 0xFF) << (8 * e);
+            else w1 |= (uint32_t)(q & 0xFF) << (8 * (e - 4));
+        }
+        d = __fdiv_rn(1.0f, iscale);
+    }
+    uint32_t* qs = (uint32_t*)(blk + 4);   // blocks are 4-byte aligned (292 = 4 * 73)
+    qs[2 * lane] = w0;
+    qs[2 * lane + 1] = w1;
+    const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+    if ((lane & 1) == 0) ((int16_t*)(blk + 260))[lane >> 1] = (int16_t)s16;
+    if (lane == 0) *(float*)blk = d;
+}
+
+constexpr int ACT_WARPS = 8;
+
+__global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(const float* __restrict__ x, long long x_ld, int K,
+                                                                       int n_rows, uint8_t* __restrict__ out,
+                                                                       long long out_stride) {
+    const int nsb = K >> 8;
+    const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
+    if (blk >= (long long)n_rows * nsb) return;
+    const int r = (int)(blk / nsb), sb = (int)(blk % nsb), lane = threadIdx.x & 31;
+    const float* src = x + (size_t)r * x_ld + (size_t)sb * 256 + 8 * lane;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = src[e];
+    q8k_block_from_regs(v, out + ((size_t)r * out_stride + sb) * 292);
+}
+
+// h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u.
+__global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
+                                                                     long long ld, int n, int n_rows, float* __restrict__ h,
+                                                                     uint8_t* __restrict__ out, long long out_stride) {
+    const int nsb = n >> 8;
+    const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
+    if (blk >= (long long)n_rows * nsb) return;
+    const int r = (int)(blk / nsb), sb = (int)(blk % nsb), lane = threadIdx.x & 31;
+    const size_t off = (size_t)r * ld + (size_t)sb * 256 + 8 * lane;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float gv = g[off + e];
+        v[e] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), u[off + e]);
+    }
+    if (h) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) h[off + e] = v[e];
+    }
+    if (out) q8k_block_from_regs(v, out + ((size_t)r * out_stride + sb) * 292);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exact dequantizer: one thread per 32-weight sub-block.  Float operations are the ones of
+// dequantize_row_ref (src/quant/quant_ref.cpp:57-103, 165-225, 284-308) in the same order, each
+// individually rounded (no fused multiply-add), so fp32 outputs are bit-identical to it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t g_u16(const uint8_t* p) { return *(const uint16_t*)p; }
+__device__ __forceinline__ uint32_t g_u32a2(const uint8_t* p) { return g_u16(p) | (g_u16(p + 2) << 16); }
+__device__ __forceinline__ float g_f16(const uint8_t* p) { return __half2float(__ushort_as_half((unsigned short)g_u16(p))); }
+
+template <int FMT>
+__device__ __forceinline__ void dequant_sub(const uint8_t* b, int s, float (&y)[32]) {
+    if (FMT == T_Q8_0) {
+        const uint8_t* q = b + 34 * s;
+        const float d = g_f16(q);
+#pragma unroll
+        for (int j = 0; j < 32; j++) y[j] = __fmul_rn((float)(int8_t)q[2 + j], d);
+    } else if (FMT == T_Q4_K || FMT == T_Q5_K) {
+        const float d = g_f16(b), mn = g_f16(b + 2);
+        const uint8_t* sc = b + 4;
+        int scv, mv;
+        if (s < 4) { scv = sc[s] & 63; mv = sc[s + 4] & 63; }
+        else { scv = (sc[s + 4] & 0xF) | ((sc[s - 4] >> 6) << 4); mv = (sc[s + 4] >> 4) | ((sc[s] >> 6) << 4); }
+        const float d1 = __fmul_rn(d, (float)scv), m1 = __fmul_rn(mn, (float)mv);
+        const uint8_t* q = b + (FMT == T_Q5_K ? 48 : 16) + 32 * (s >> 1);
+#pragma unroll
+        for (int l = 0; l < 32; l++) {
+            int v = (s & 1) ? (q[l] >> 4) : (q[l] & 0xF);
+            if (FMT == T_Q5_K) v += ((b[16 + l] >> s) & 1) << 4;
+            y[l] = __fsub_rn(__fmul_rn(d1, (float)v), m1);
+        }
+    } else if (FMT == T_Q6_K) {
+        const float d = g_f16(b + 208);
+        const int h = s >> 2, j = s & 3;
+        const uint8_t* ql = b + 64 * h + 32 * (j & 1);
+        const uint8_t* qh = b + 128 + 32 * h;
+        const int8_t* sc = (const int8_t*)(b + 192 + 8 * h + 2 * j);
+#pragma unroll
+        for (int l = 0; l < 32; l++) {
+            const int q = (int)(((ql[l] >> (4 * (j >> 1))) & 0xF) | (((qh[l] >> (2 * j)) & 3) << 4)) - 32;
+            y[l] = __fmul_rn(__fmul_rn(d, (float)sc[l >> 4]), (float)q);
+        }
+    } else if (FMT == T_IQ3_XXS) {
+        const float d = g_f16(b);
+        const uint32_t aux = g_u32a2(b + 66 + 4 * s);
+        const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(aux >> 28))), 0.5f);
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t s7 = (aux >> (7 * l)) & 127u;
+            const uint32_t sg = s7 | ((uint32_t)(__popc(s7) & 1) << 7);
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const uint32_t gw = q38b_iq3xxs_grid[b[2 + 8 * s + 2 * l + hh]];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    y[8 * l + 4 * hh + j] = __fmul_rn(__fmul_rn(db, (float)((gw >> (8 * j)) & 0xFF)), ((sg >> (4 * hh + j)) & 1) ? -1.f : 1.f);
+            }
+        }
+    } else if (FMT == T_IQ3_S) {
+        const float d = g_f16(b);
+        const uint32_t ls = (b[106 + (s >> 1)] >> (4 * (s & 1))) & 0xF;
+        const float db = __fmul_rn(d, (float)(1 + 2 * (int)ls));
+        const uint32_t qh = b[66 + s];
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t sg = b[74 + 4 * s + l];
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const uint32_t idx = b[2 + 8 * s + 2 * l + hh] | (((qh >> (2 * l + hh)) & 1u) << 8);
+                const uint32_t gw = q38b_iq3s_grid[idx];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    y[8 * l + 4 * hh + j] = __fmul_rn(__fmul_rn(db, (float)((gw >> (8 * j)) & 0xFF)), ((sg >> (4 * hh + j)) & 1) ? -1.f : 1.f);
+            }
+        }
+    } else if (FMT == T_IQ4_XS) {
+        const float d = g_f16(b);
+        const uint32_t sh = g_u16(b + 2);
+        const int ls = (int)(((b[4 + (s >> 1)] >> (4 * (s & 1))) & 0xF) | (((sh >> (2 * s)) & 3) << 4));
+        const float dl = __fmul_rn(d, (float)(ls - 32));
+        const uint8_t* q = b + 8 + 16 * s;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            y[j] = __fmul_rn(dl, (float)q38b_iq4nl_levels[q[j] & 0xF]);
+            y[j + 16] = __fmul_rn(dl, (float)q38b_iq4nl_levels[q[j] >> 4]);
+        }
+    }
+}
+
+template <int FMT, int KIND>
+__global__ void __launch_bounds__(128) dequant_rows_kernel(const uint8_t* __restrict__ W, long long row_bytes, int K, int rows,
+                                                            void* __restrict__ out) {
+    const int nsub = K >> 5;
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (long long)rows * nsub) return;
+    const int r = (int)(id / nsub), sub = (int)(id % nsub);
+    const uint8_t* blk = W + (size_t)r * row_bytes + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES;
+    float y[32];
+    dequant_sub<FMT>(blk, sub & 7, y);
+    const size_t o = (size_t)r * K + (size_t)sub * 32;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        if (KIND == 0) ((float*)out)[o + j] = y[j];
+        else if (KIND == 1) ((__half*)out)[o + j] = __float2half_rn(y[j]);
+        else ((__nv_bfloat16*)out)[o + j] = __float2bfloat16_rn(y[j]);
+    }
+}
+
+}  // namespace q38b

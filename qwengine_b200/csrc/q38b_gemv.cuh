@@ -1,0 +1,220 @@
+// q38b_gemv.cuh -- the decode matvec kernel: y[c][r] (+)= W[r,:] . x_c for 1..8 activation columns.
+//
+// Replaces k_gemv_q8 / gemv_q8n of the reference (src/cuda/gemv.cu:51-125, 215-228).  Shape of the kernel:
+//   * persistent CTAs (one per SM): a producer warp plus NGROUPS groups of 8 consumer warps;
+//   * the weight rows stream HBM -> shared memory through 1-D bulk (TMA) copies, one copy per (row, K-chunk) into
+//     a ring of stages per group, completion tracked by mbarriers; GGUF blocks of most formats are only 2-byte
+//     aligned, so each copy moves the 16-byte aligned superset of its row slice and the consumers index from the
+//     remainder;
+//   * a stage holds a 16-row tile; the 8 warps of a group split its half super-blocks, decode them into int8 mma
+//     fragments (q38b_decode.cuh) and keep float partial sums per (row, column); at the end of a tile the 8
+//     partial sums are added in a fixed order through shared memory, so results do not depend on timing;
+//   * activations (Q8_K int8 values and block scales of all columns) and the codebook are staged in shared memory
+//     once per CTA.
+// Every column is computed by the same instructions whatever nb is, so column c of an nb-column call is
+// bit-identical to a 1-column call on that column (the reference promises the same: src/cuda/gemv.cuh:31-34).
+#pragma once
+#include "q38b_decode.cuh"
+#include "q38b_pipe.cuh"
+
+namespace q38b {
+
+constexpr int TILE_ROWS = 16;
+constexpr int GROUP_WARPS = 8;
+constexpr int GROUP_THREADS = GROUP_WARPS * 32;
+constexpr int MAX_STAGES = 6;
+constexpr int Q8K_BYTES = 292;   // float d | int8 qs[256] | int16 bsums[16]  (src/quant/quant_formats.h:95)
+
+struct GemvArgs {
+    const uint8_t* W;        // [M] rows, row_bytes apart, GGUF blocks
+    long long row_bytes;
+    const uint8_t* xq;       // Q8_K blocks; column c starts at xq + c * x_stride * 292
+    long long x_stride;      // blocks between columns
+    float* y;                // y[c * y_ld + r]
+    long long y_ld;
+    int* status;             // device status word (OR of ST_* bits)
+    const uint32_t* codebook;   // device copy of the format's codebook (or nullptr)
+    int K, M, nb, accumulate;
+    int nsb;                 // super-blocks per row
+    int n_tiles;
+    int chunk_sb;            // super-blocks per K-chunk (last chunk may be shorter)
+    int n_chunks;
+    int n_stages;
+    int slot_stride;         // bytes per row slot inside a stage (multiple of 16)
+    int cb_rep_log2;         // log2 of codebook replicas
+    // shared-memory offsets (bytes from the 128-byte aligned base)
+    int off_actd, off_actq, off_cb, off_red, off_stage;
+    int stage_bytes;         // TILE_ROWS * slot_stride
+};
+
+template <int FMT, int NGROUPS>
+__global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kernel(const GemvArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    uint64_t* bars = (uint64_t*)smem;                       // full[NGROUPS][MAX_STAGES], empty[NGROUPS][MAX_STAGES]
+    volatile int* abort_flag = (volatile int*)(smem + 8 * 2 * NGROUPS * MAX_STAGES);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int g = 0; g < NGROUPS; g++)
+            for (int s = 0; s < a.n_stages; s++) {
+                mbar_init(smem_u32(&bars[g * MAX_STAGES + s]), TILE_ROWS);                        // full: one arrival per row copy
+                mbar_init(smem_u32(&bars[(NGROUPS + g) * MAX_STAGES + s]), GROUP_WARPS);          // empty: one per consumer warp
+            }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const int packed_row = a.nsb * Unit<FMT>::BLOCK_BYTES;
+    const int chunk_bytes_full = a.chunk_sb * Unit<FMT>::BLOCK_BYTES;
+
+    if (warp == 0) {
+        // ---------------- producer: weights do not depend on earlier kernels, start at once ----------------
+        if (lane < TILE_ROWS) {
+            const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
+            const uintptr_t safe_end = w_end & ~(uintptr_t)15;
+            int item[NGROUPS];
+            bool more = true;
+            for (int g = 0; g < NGROUPS; g++) item[g] = 0;
+            for (int it = 0; more; it++) {
+                more = false;
+                for (int g = 0; g < NGROUPS; g++) {
+                    const int tile = blockIdx.x + gridDim.x * (g + NGROUPS * (it / a.n_chunks));
+                    if (tile >= a.n_tiles) continue;
+                    more = true;
+                    const int chunk = it % a.n_chunks;
+                    const int stage = item[g] % a.n_stages;
+                    const uint32_t use = (uint32_t)(item[g] / a.n_stages);
+                    item[g]++;
+                    const uint32_t full = smem_u32(&bars[g * MAX_STAGES + stage]);
+                    const uint32_t empty = smem_u32(&bars[(NGROUPS + g) * MAX_STAGES + stage]);
+                    mbar_wait_bounded(empty, (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+                    const int row = tile * TILE_ROWS + lane;
+                    if (row >= a.M) { mbar_arrive(full); continue; }
+                    const int sb0 = chunk * a.chunk_sb;
+                    const int len = (sb0 + a.chunk_sb <= a.nsb ? chunk_bytes_full : (a.nsb - sb0) * Unit<FMT>::BLOCK_BYTES);
+                    const uintptr_t src = (uintptr_t)a.W + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+                    const uintptr_t lo = src & ~(uintptr_t)15;
+                    uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
+                    uint8_t* slot = smem + a.off_stage + (size_t)(g * a.n_stages + stage) * a.stage_bytes + (size_t)lane * a.slot_stride;
+                    if (hi > safe_end) {
+                        // the last bytes of the tensor do not fill a 16-byte unit: fetch them with plain loads
+                        hi = safe_end > lo ? safe_end : lo;
+                        for (uintptr_t p = hi; p < src + len; p += 2)
+                            if (p >= src) *(uint16_t*)(slot + (p - lo)) = *(const uint16_t*)p;
+                    }
+                    const uint32_t bytes = (uint32_t)(hi - lo);
+                    if (bytes) {
+                        mbar_arrive_expect_tx(full, bytes);
+                        bulk_copy_g2s(smem_u32(slot), (const void*)lo, bytes, full);
+                    } else {
+                        mbar_arrive(full);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int ctid = tid - 32;                       // 0 .. NGROUPS*256-1
+    const int grp = ctid / GROUP_THREADS;
+    const int gw = (ctid % GROUP_THREADS) >> 5;      // warp inside the group
+    const int gtid = ctid % GROUP_THREADS;
+    const int g = lane >> 2, t = lane & 3;
+
+    // stage the codebook (replicated so that lane l reads bank l) and the activations
+    float* actd = (float*)(smem + a.off_actd);       // [nsb][8]
+    uint8_t* actq = smem + a.off_actq;               // [nb][K], staged order
+    uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
+    constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
+    if (CBN > 0) {
+        const int rep = 1 << a.cb_rep_log2;
+        for (int i = ctid; i < CBN * rep; i += NGROUPS * GROUP_THREADS) cbw[i] = a.codebook[i >> a.cb_rep_log2];
+    }
+    pdl_wait_prior();   // activations come from the previous kernel of the stream
+    for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS) {
+        const int sb = i >> 3, c = i & 7;
+        actd[i] = c < a.nb ? *(const float*)(a.xq + ((size_t)c * a.x_stride + sb) * Q8K_BYTES) : 0.0f;
+    }
+    for (int i = ctid; i < a.nb * (a.K / 4); i += NGROUPS * GROUP_THREADS) {
+        const int c = i / (a.K / 4), w = i % (a.K / 4);       // word w of column c
+        const int sb = w >> 6, wi = w & 63;
+        const uint32_t v = *(const uint32_t*)(a.xq + ((size_t)c * a.x_stride + sb) * Q8K_BYTES + 4 + 4 * wi);
+        uint8_t* dst = actq + (size_t)c * a.K + sb * 256;
+        if (FMT == T_IQ4_XS) {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int k = 4 * wi + b;
+                dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)(v >> (8 * b));
+            }
+        } else {
+            *(uint32_t*)(dst + 4 * wi) = v;
+        }
+    }
+    named_bar_sync(15, NGROUPS * GROUP_THREADS);
+
+    Codebook cb;
+    cb.words = cbw;
+    cb.rep_log2 = a.cb_rep_log2;
+    cb.lane_word = (uint32_t)lane & ((1u << a.cb_rep_log2) - 1u);
+
+    float* red = (float*)(smem + a.off_red) + (size_t)grp * 2 * GROUP_THREADS * 4;
+    const bool bvalid = g < a.nb;
+    const uint8_t* bq_col = actq + (size_t)(bvalid ? g : 0) * a.K;
+
+    int item = 0;
+    for (int ti = 0;; ti++) {
+        const int tile = blockIdx.x + gridDim.x * (grp + NGROUPS * ti);
+        if (tile >= a.n_tiles) break;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const int rowA = tile * TILE_ROWS + g, rowB = rowA + 8;
+        for (int chunk = 0; chunk < a.n_chunks; chunk++, item++) {
+            const int stage = item % a.n_stages;
+            const uint32_t use = (uint32_t)(item / a.n_stages);
+            const uint32_t full = smem_u32(&bars[grp * MAX_STAGES + stage]);
+            const uint32_t empty = smem_u32(&bars[(NGROUPS + grp) * MAX_STAGES + stage]);
+            mbar_wait_bounded(full, use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            const int sb0 = chunk * a.chunk_sb;
+            const int nsb_c = min(a.chunk_sb, a.nsb - sb0);
+            const uint8_t* st = smem + a.off_stage + (size_t)(grp * a.n_stages + stage) * a.stage_bytes;
+            const uintptr_t srcA = (uintptr_t)a.W + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+            const uintptr_t srcB = srcA + 8 * (uintptr_t)a.row_bytes;
+            const uint8_t* baseA = st + (size_t)g * a.slot_stride + (srcA & 15);
+            const uint8_t* baseB = st + (size_t)(g + 8) * a.slot_stride + (srcB & 15);
+            for (int u = gw; u < 2 * nsb_c; u += GROUP_WARPS) {
+                const int sbi = u >> 1, h = u & 1;
+                const int gsb = sb0 + sbi;
+                ActLane al;
+                al.q = bq_col + gsb * 256;
+                al.valid = bvalid;
+                const float2 dx = *(const float2*)(actd + gsb * 8 + 2 * t);
+                al.dx0 = dx.x;
+                al.dx1 = dx.y;
+                Unit<FMT>::run(baseA + sbi * Unit<FMT>::BLOCK_BYTES, baseB + sbi * Unit<FMT>::BLOCK_BYTES, h, al, cb, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty);
+        }
+        // add the 8 warps' partial sums in warp order and store the tile
+        float* rbuf = red + (size_t)(ti & 1) * GROUP_THREADS * 4;
+        *(float4*)(rbuf + (gw * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        named_bar_sync(1 + grp, GROUP_THREADS);
+        if (gtid < 128) {
+            const int ls = gtid & 31, i = gtid >> 5;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < GROUP_WARPS; w++) v += rbuf[(w * 32 + ls) * 4 + i];
+            const int row = tile * TILE_ROWS + (ls >> 2) + 8 * (i >> 1);
+            const int col = 2 * (ls & 3) + (i & 1);
+            if (row < a.M && col < a.nb) {
+                float* yo = a.y + (size_t)col * a.y_ld + row;
+                *yo = a.accumulate ? *yo + v : v;
+            }
+        }
+    }
+}
+
+}  // namespace q38b

@@ -1,0 +1,145 @@
+// CPU emulation of one consumer warp of the matvec kernel, for the GPU-free unit test of the
+// fragment builders in qwengine_b200/csrc/q38b_decode.cuh.  32 host threads play the 32 lanes;
+// mma.sync and shuffles are rendezvous points that apply the PTX fragment layouts.  The test
+// lays a 16-row tile out in memory exactly as the kernel's stage holds it (each row at its own
+// slot, shifted by the low 4 bits of its global address) and runs every half super-block.
+#include <pthread.h>
+
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "../../qwengine_b200/csrc/q38b_decode.cuh"
+
+namespace {
+thread_local int tl_lane = 0;
+pthread_barrier_t g_bar;
+uint32_t g_a[32][4], g_b[32][2], g_sh[32];
+}  // namespace
+
+namespace q38b {
+int emul_lane() { return tl_lane; }
+
+void emul_mma(int (&c)[4], const uint32_t* a, int n_a, const uint32_t* b, int n_b) {
+    const int lane = tl_lane;
+    for (int i = 0; i < n_a; i++) g_a[lane][i] = a[i];
+    for (int i = 0; i < n_b; i++) g_b[lane][i] = b[i];
+    pthread_barrier_wait(&g_bar);
+    const int kdim = n_b * 16;
+    const int g = lane >> 2, t = lane & 3;
+    for (int ci = 0; ci < 4; ci++) {
+        const int m = g + 8 * (ci >> 1), n = 2 * t + (ci & 1);
+        int sum = 0;
+        for (int k = 0; k < kdim; k++) {
+            // A[m][k]: held by lane (m % 8) * 4 + (k % 16) / 4, register (m / 8) + 2 * (k / 16), byte k % 4
+            const int la = (m & 7) * 4 + ((k & 15) >> 2), ra = (m >> 3) + 2 * (k >> 4);
+            const int lb = n * 4 + ((k & 15) >> 2), rb = k >> 4;
+            const int av = (int8_t)(g_a[la][ra] >> (8 * (k & 3)));
+            const int bv = (int8_t)(g_b[lb][rb] >> (8 * (k & 3)));
+            sum += av * bv;
+        }
+        c[ci] += sum;
+    }
+    pthread_barrier_wait(&g_bar);
+}
+
+uint32_t emul_shfl(uint32_t v, int src) {
+    g_sh[tl_lane] = v;
+    pthread_barrier_wait(&g_bar);
+    const uint32_t r = g_sh[src & 31];
+    pthread_barrier_wait(&g_bar);
+    return r;
+}
+}  // namespace q38b
+
+using namespace q38b;
+
+namespace {
+struct Job {
+    int fmt, K, nb, rep_log2;
+    const uint8_t* stage;       // 16 slots
+    int slot_stride;
+    const int* row_shift;       // per row: low 4 address bits
+    const uint8_t* actq;        // [nb][K] staged order
+    const float* actd;          // [nsb][8]
+    const uint32_t* cb;         // replicated codebook
+    float* y;                   // [16][8]
+};
+struct LaneArg { const Job* job; int lane; };
+
+template <int FMT>
+void run_lane(const Job& j, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    Codebook cb{j.cb, j.rep_log2, (uint32_t)lane & ((1u << j.rep_log2) - 1u)};
+    float acc[4] = {0, 0, 0, 0};
+    const uint8_t* baseA = j.stage + (size_t)g * j.slot_stride + j.row_shift[g];
+    const uint8_t* baseB = j.stage + (size_t)(g + 8) * j.slot_stride + j.row_shift[g + 8];
+    const bool valid = g < j.nb;
+    const int nsb = j.K / 256;
+    for (int u = 0; u < 2 * nsb; u++) {
+        const int sb = u >> 1, h = u & 1;
+        ActLane al;
+        al.q = j.actq + (size_t)(valid ? g : 0) * j.K + sb * 256;
+        al.valid = valid;
+        al.dx0 = j.actd[sb * 8 + 2 * t];
+        al.dx1 = j.actd[sb * 8 + 2 * t + 1];
+        Unit<FMT>::run(baseA + sb * Unit<FMT>::BLOCK_BYTES, baseB + sb * Unit<FMT>::BLOCK_BYTES, h, al, cb, acc);
+    }
+    for (int i = 0; i < 4; i++) j.y[(g + 8 * (i >> 1)) * 8 + 2 * t + (i & 1)] = acc[i];
+}
+
+void* lane_main(void* v) {
+    const LaneArg* la = (const LaneArg*)v;
+    tl_lane = la->lane;
+    const Job& j = *la->job;
+    switch (j.fmt) {
+        case T_Q8_0: run_lane<T_Q8_0>(j, la->lane); break;
+        case T_Q4_K: run_lane<T_Q4_K>(j, la->lane); break;
+        case T_Q5_K: run_lane<T_Q5_K>(j, la->lane); break;
+        case T_Q6_K: run_lane<T_Q6_K>(j, la->lane); break;
+        case T_IQ3_XXS: run_lane<T_IQ3_XXS>(j, la->lane); break;
+        case T_IQ3_S: run_lane<T_IQ3_S>(j, la->lane); break;
+        case T_IQ4_XS: run_lane<T_IQ4_XS>(j, la->lane); break;
+    }
+    return nullptr;
+}
+}  // namespace
+
+#define Q38B_CODEBOOK_QUALIFIER static const
+#include "../../qwengine_b200/csrc/codebooks.inc"
+
+// W: 16 packed rows of GGUF blocks; xq: Q8_K blocks [nb][K/256]; addr_lo: pretend low address bits of row 0
+// (row r then sits at (addr_lo + r * row_bytes) & 15 inside its slot); y: [16][8].
+extern "C" int emul_tile(int fmt, int K, const uint8_t* W, const uint8_t* xq, int nb, int addr_lo, int rep_log2, float* y) {
+    const int bb = block_bytes(fmt), nsb = K / 256, row_bytes = nsb * bb;
+    if (!bb) return -1;
+    const int slot = (row_bytes + 32 + 15) / 16 * 16 + 16;
+    std::vector<uint8_t> stage((size_t)16 * slot + 64, 0xA5);
+    uint8_t* st = (uint8_t*)(((uintptr_t)stage.data() + 15) & ~(uintptr_t)15);
+    int shift[16];
+    for (int r = 0; r < 16; r++) {
+        shift[r] = (addr_lo + r * row_bytes) & 15;
+        memcpy(st + (size_t)r * slot + shift[r], W + (size_t)r * row_bytes, row_bytes);
+    }
+    std::vector<uint8_t> actq((size_t)8 * K, 0);
+    std::vector<float> actd((size_t)nsb * 8, 0.f);
+    for (int c = 0; c < nb; c++)
+        for (int sb = 0; sb < nsb; sb++) {
+            const uint8_t* blk = xq + ((size_t)c * nsb + sb) * 292;
+            memcpy(&actd[sb * 8 + c], blk, 4);
+            for (int k = 0; k < 256; k++) actq[(size_t)c * K + sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
+        }
+    const int entries = fmt == T_IQ3_XXS ? 256 : fmt == T_IQ3_S ? 512 : 0;
+    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) << rep_log2);
+    for (size_t i = 0; i < ((size_t)entries << rep_log2); i++)
+        cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> rep_log2] : q38b_iq3s_grid[i >> rep_log2];
+    Job job{fmt, K, nb, rep_log2, st, slot, shift, actq.data(), actd.data(), cb.data(), y};
+    pthread_barrier_init(&g_bar, nullptr, 32);
+    pthread_t th[32];
+    LaneArg la[32];
+    for (int l = 0; l < 32; l++) { la[l] = {&job, l}; pthread_create(&th[l], nullptr, lane_main, &la[l]); }
+    for (int l = 0; l < 32; l++) pthread_join(th[l], nullptr);
+    pthread_barrier_destroy(&g_bar);
+    return 0;
+}

@@ -1,0 +1,44 @@
+"""GPU-free check of the tensor-core fragment builders (qwengine_b200/csrc/q38b_decode.cuh): the header is
+compiled for the host with 32 threads playing the lanes of a warp (tests/host_emul/emul_decode.cpp) and a 16-row
+tile is compared with the oracle."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import oracle
+from qwengine_b200 import formats as F, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def emul(tmp_path_factory):
+    so = str(tmp_path_factory.mktemp("emul") / "libemul.so")
+    src = os.path.join(ROOT, "tests", "host_emul", "emul_decode.cpp")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-fPIC", "-shared", "-o", so, src, "-lpthread"], check=True)
+    lib = C.CDLL(so)
+    u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+    lib.emul_tile.argtypes = [C.c_int, C.c_int, u8p, u8p, C.c_int, C.c_int, C.c_int, f32p]
+    return lib
+
+
+@pytest.mark.parametrize("name", list(F.FORMATS))
+@pytest.mark.parametrize("nb,addr_lo,rep_log2", [(1, 0, 5), (7, 8, 3), (8, 2, 0)])
+def test_tile_matches_oracle(emul, name, nb, addr_lo, rep_log2):
+    f = F.get(name)
+    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8}.get(name, 2):
+        addr_lo = 0   # the format's loads need this alignment (the C ABI rejects anything else)
+    K = 768
+    w = synth.make_weights(f, 16, K, seed=3, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    x = synth.make_activations(nb, K, seed=4) * (np.arange(nb, dtype=np.float32)[:, None] + 1)
+    xq = oracle.port.quantize_q8k(x)
+    y = np.zeros((16, 8), np.float32)
+    assert emul.emul_tile(f.type_id, K, w.reshape(-1), xq.reshape(-1), nb, addr_lo, rep_log2, y.reshape(-1)) == 0
+    for c in range(nb):
+        ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[c], K)
+        assert np.max(np.abs(y[:, c] - ref) / mag) < 1e-6
+    assert not y[:, nb:].any()
