@@ -81,25 +81,28 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, int M, int nb, Plan* p)
         a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
         a.off_stage = a.off_red + NGROUPS * 2 * GROUP_THREADS * 16;
         const int avail = budget - a.off_stage;
-        for (int n_chunks = 1; n_chunks <= nsb; n_chunks++) {
-            int cs = (nsb + n_chunks - 1) / n_chunks;
-            if (n_chunks > 1) cs = std::min(nsb, align_up(cs, 4));
-            int slot = align_up(cs * bb + 32, 16);
-            while (slot % 128 != bank_skew) slot += 16;
-            const int stage = TILE_ROWS * slot;
-            if (stage > 56 * 1024 && cs > 4) continue;
-            int stages = avail / (NGROUPS * stage);
-            if (stages < 2) continue;
-            a.chunk_sb = cs;
-            a.n_chunks = (nsb + cs - 1) / cs;
-            a.n_stages = std::min(stages, 4);
-            a.slot_stride = slot;
-            a.stage_bytes = stage;
-            p->smem = a.off_stage + NGROUPS * a.n_stages * stage + 128;
-            const int ctas_needed = (a.n_tiles + NGROUPS - 1) / NGROUPS;
-            p->grid = std::max(1, std::min(ctx->sm_count, ctas_needed));
-            return Q38B_OK;
-        }
+        // K-chunk sizes to try: the whole row, then fewer super-blocks, multiples of 4 first (8 half super-blocks
+        // per 4 keep the 8 warps of a group evenly loaded)
+        for (int pass = 0; pass < 2; pass++)
+            for (int cs = nsb; cs >= 1; cs--) {
+                const bool even = cs == nsb || cs % 4 == 0;
+                if (even != (pass == 0)) continue;
+                int slot = align_up(cs * bb + 32, 16);
+                while (slot % 128 != bank_skew) slot += 16;
+                const int stage = TILE_ROWS * slot;
+                if (stage > 56 * 1024 && cs > 1) continue;
+                const int stages = avail / (NGROUPS * stage);
+                if (stages < 2) continue;
+                a.chunk_sb = cs;
+                a.n_chunks = (nsb + cs - 1) / cs;
+                a.n_stages = std::min(stages, 4);
+                a.slot_stride = slot;
+                a.stage_bytes = stage;
+                p->smem = a.off_stage + NGROUPS * a.n_stages * stage + 128;
+                const int ctas_needed = (a.n_tiles + NGROUPS - 1) / NGROUPS;
+                p->grid = std::max(1, std::min(ctx->sm_count, ctas_needed));
+                return Q38B_OK;
+            }
         if (!cb_entries) break;
     }
     return Q38B_ERR_NOMEM;
