@@ -1,0 +1,340 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode weight pass (27B-shaped, 64 layers + output head, 12.5 GB of GGUF blocks).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one full pass over all 353 weight matrices for one token (nb = 1): Q8_K quantisation, matvec,
+SwiGLU, matvec ..., replayed as a CUDA graph by the C++ planner.  `value` is weight bytes streamed per second
+summed over all ranks (the pass is row-sharded over the ranks and the output slices are all-gathered, so the
+total work is fixed: strong scaling).  Synthetic seeded weights stand in for the model file.
+The single JSON line also carries the nb = 7 pass, the end-to-end number through the host-buffer C ABI, a live
+roofline measurement of the dominant kernel and the reference's AVX2 kernels timed on this box's host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_weight_pass_stream_bandwidth"
+UNIT = "GB/s"
+HBM_NOMINAL_GBS = 8000.0
+# dram__bytes_read + dram__bytes_write of one 17408 x 5120 IQ3_XXS matvec launch divided by its GGUF bytes, from the
+# ncu capture summarised in profiles/gemv_iq3xxs_17408x5120_nb1.md
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0011
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own AVX2 kernels (oracle/_ref) on a bounded sample of the same pass
+# ---------------------------------------------------------------------------------------------------------------
+def cpu_sample_specs():
+    from qwengine_b200 import decode_pass as dp
+    specs = dp.all_specs(n_layers=4, head=False)                      # 3 DeltaNet layers + 1 attention layer
+    specs.append(dp.MatSpec("lm_head_slice", "Q6_K", dp.VOCAB // 16, dp.HIDDEN))
+    return specs
+
+
+def cpu_run(seconds_budget=None, steps=None, warmup=1):
+    """Times the reference CPU kernels; returns dict(value GB/s, cores, kind, sample, ms_per_step, steps)."""
+    import oracle
+    from qwengine_b200 import formats as F, synth
+    cores = len(os.sched_getaffinity(0))
+    impl = oracle.ref if oracle.ref is not None else None
+    kind = "reference" if impl is not None else "port"
+    specs = cpu_sample_specs()
+    rng = np.random.Generator(np.random.PCG64(99))
+    mats = []
+    for s in specs:
+        f = F.get(s.fmt)
+        w = rng.integers(0, 256, size=(s.M, f.row_bytes(s.K)), dtype=np.uint8)   # timing does not depend on the values
+        xq = oracle.port.quantize_q8k(synth.make_activations(1, s.K, seed=s.K))
+        mats.append((f, w, xq, s.K))
+    nbytes = sum(m[1].nbytes for m in mats)
+
+    def one_pass():
+        t = 0.0
+        for f, w, xq, K in mats:
+            if impl is not None:
+                t += impl.gemv(f.type_id, w, xq, K, threads=cores)[1]
+            else:
+                t0 = time.perf_counter()
+                oracle.port.gemv(f.type_id, w, xq, K)
+                t += time.perf_counter() - t0
+        return t
+
+    for _ in range(max(1, warmup)):
+        one_pass()
+    times = []
+    t_start = time.perf_counter()
+    while True:
+        times.append(one_pass())
+        if steps is not None and len(times) >= steps:
+            break
+        if steps is None and time.perf_counter() - t_start > seconds_budget:
+            break
+    sec = sum(times) / len(times)
+    return {"value": round(nbytes / sec / 1e9, 2), "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"layers 0-3 (8 Q4_K, 8 IQ3_XXS, 4 IQ4_XS matrices) + 1/16 of the Q6_K head = {nbytes / 1e6:.0f} MB per "
+                      f"pass, nb=1, {len(times)} timed passes",
+            "ms_per_step": sec * 1e3, "steps": len(times)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_run(steps=max(1, args.steps), warmup=max(1, args.warmup))
+    line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": r["steps"],
+            "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "decode_weight_pass_27b_shape", "nb": 1, "arm": "reference AVX2 CPU kernels, bounded sample"},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------------
+_FP16_FIELDS = {"Q8_0": (0,), "Q4_K": (0, 2), "Q5_K": (0, 2), "Q6_K": (208,), "IQ3_XXS": (0,), "IQ3_S": (0,), "IQ4_XS": (0,)}
+
+
+def device_weights(torch, spec, rows, seed, scale):
+    """Random valid blocks generated on the device: uniform bytes, fp16 super-scales |N(0,1)| * scale."""
+    from qwengine_b200 import formats as F
+    f = F.get(spec.fmt)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    nblk = spec.K // f.block_elems
+    w = torch.randint(0, 256, (rows, nblk, f.block_bytes), dtype=torch.uint8, device="cuda", generator=g)
+    from qwengine_b200 import synth
+    d0 = None
+    for off in _FP16_FIELDS[f.name]:
+        d = torch.randn((rows, nblk), device="cuda", generator=g).abs() * scale
+        if off == 2 and f.name in synth.ZERO_MEAN_DMIN:
+            d = d0 * synth.ZERO_MEAN_DMIN[f.name]          # zero-mean weights: see synth.ZERO_MEAN_DMIN
+        d0 = d
+        w[:, :, off:off + 2] = d.to(torch.float16).view(torch.uint8).view(rows, nblk, 2)
+    return w.view(rows, nblk * f.block_bytes)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import qwengine_b200 as q
+    from qwengine_b200 import build as qbuild, decode_pass as dp, formats as F
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if rank == 0:
+        qbuild.build()
+    if world > 1:
+        dist.barrier()
+    ctx = q.Context(local)
+    if world > 1:
+        idbuf = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            import ctypes as C
+            raw = (C.c_ubyte * 128)()
+            ctx._rc(ctx.lib.q38b_comm_unique_id(raw), "q38b_comm_unique_id")
+            idbuf.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+        dist.broadcast(idbuf, 0)
+        host_id = bytes(idbuf.cpu().tolist())
+        ctx._rc(ctx.lib.q38b_comm_init(ctx.h, world, rank, host_id), "q38b_comm_init")
+
+    n_layers = args.layers
+    ps = q.Pass(ctx, max_nb=7)
+    counter = [0]
+
+    def make_matrix(spec, rows):
+        counter[0] += 1
+        w = device_weights(torch, spec, rows, seed=1000 * counter[0] + rank, scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
+        return ps.matrix_device(spec.fmt, w, spec.K)
+
+    io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world)
+    local_bytes = ps.weight_bytes
+    total_bytes = dp.total_weight_bytes(n_layers, True)
+    xin = ps.buffer_tensor(io["in_buf"])
+    x0 = torch.randn((7, dp.HIDDEN), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(nb, steps, warmup):
+        for _ in range(warmup):
+            xin.copy_(x0)
+            ps.run(nb)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            ps.run(nb)
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    warm = max(3, args.warmup)
+    with ClockSampler(local) as clocks:
+        ms1 = timed(1, args.steps, warm)
+    ms7 = timed(7, max(3, args.steps // 2), 3)
+    ctx.check()
+    logits = ps.buffer_tensor(io["out_buf"])
+    finite = bool(torch.isfinite(logits[:7]).all().item())
+
+    # end to end through the host-buffer entry point: pinned staging, H2D of the token's hidden state, the pass,
+    # D2H of the logits, synchronise -- every step
+    xh = np.ascontiguousarray(x0[:1].cpu().numpy())
+    yh = np.empty((1, io["out_len"]), np.float32)
+    for _ in range(3):
+        ps.run_host(1, io["in_buf"], xh, io["out_buf"], 0, yh)
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ps.run_host(1, io["in_buf"], xh, io["out_buf"], 0, yh)
+    sync_all()
+    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_ms.item())
+
+    # roofline of the dominant kernel (IQ3_XXS gate / up matvec: 35 % of the bytes), measured live: one launch per
+    # distinct resident matrix (128 matrices, 4.4 GB in total at one GPU: far larger than L2), CUDA events on the stream
+    spec = dp.MatSpec("roof", "IQ3_XXS", dp.FF, dp.HIDDEN)
+    rows = spec.M // world
+    f = F.get(spec.fmt)
+    mats = [device_weights(torch, spec, rows, seed=50000 + i, scale=1.4e-4) for i in range(max(8, 64 // world))]
+    xq = ctx.quantize_q8k(x0[:1].contiguous())
+    yb = torch.empty((1, rows), device="cuda")
+    for w in mats:
+        ctx.gemv(f, w, xq, spec.K, out=yb)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 4
+    e0.record()
+    for _ in range(reps):
+        for w in mats:
+            ctx.gemv(f, w, xq, spec.K, out=yb)
+    e1.record()
+    torch.cuda.synchronize()
+    kern_us = e0.elapsed_time(e1) * 1e3 / (reps * len(mats))
+    alg_bytes = rows * f.row_bytes(spec.K)
+    peak, peak_kind = measured_peak()
+    achieved = alg_bytes / kern_us / 1e3
+    roofline = {"bound": "hbm", "kernel": "gemv_kernel<IQ3_XXS> 17408x5120/%d nb=1" % world, "achieved": round(achieved, 1),
+                "peak": peak, "peak_source": peak_kind + " copy bandwidth", "unit": UNIT, "frac": round(achieved / peak, 4),
+                "frac_of_nominal_8TBps": round(achieved / HBM_NOMINAL_GBS, 4), "us_per_launch": round(kern_us, 2),
+                "algorithmic_bytes_per_launch": alg_bytes,
+                "traffic": int(alg_bytes * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE)}
+
+    line = None
+    if rank == 0:
+        value = total_bytes / ms1 / 1e6
+        cpu = cpu_run(seconds_budget=12.0) if (world == 1 and not args.no_cpu) else None
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": round(ms1, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "decode_weight_pass_27b_shape", "layers": n_layers, "matrices": len(dp.all_specs(n_layers)),
+                       "weight_bytes": total_bytes, "nb": 1, "parallelism": f"row-shard x{world} + all-gather",
+                       "cache": "12.5 GB of weights per pass, far larger than L2; no flush needed", "outputs_finite": finite},
+            "tokens_per_s": round(1e3 / ms1, 1),
+            "frac_of_nominal_8TBps": round(value / world / HBM_NOMINAL_GBS, 4),
+            "nb7": {"ms_per_step": round(ms7, 4), "value": round(total_bytes / ms7 / 1e6, 1), "tokens_per_s": round(7e3 / ms7, 1),
+                    "time_vs_nb1": round(ms7 / ms1, 3)},
+            "e2e": {"value": round(total_bytes / e2e_ms / 1e6, 1), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": int(xh.nbytes), "d2h_bytes_per_step": int(yh.nbytes)},
+            "gpu_launches": ps.kernel_count * args.steps,
+            "roofline": roofline,
+            "clocks": clocks.summary(),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    ps.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=64, help="number of layers of the pass (64 = the benchmark configuration)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -82,6 +82,48 @@ int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g_dev, const float* u_dev, long 
 int q38b_dequant_rows(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int rows, void* out_dev,
                       int out_kind, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * All-HBM planner.  Replaces the reference's residency planner and split upload (plan_residency,
+ * src/runtime/planner.cpp:91-163; SplitMat / upload_split, src/runtime/engine.h:55-85, engine.cpp:594-629): every
+ * matrix is resident in HBM, row-sharded over the ranks (one process per GPU): rank g of G owns rows
+ * [g*M/G, (g+1)*M/G).  A pass is a recorded sequence of quantize / matvec / SwiGLU / all-gather steps over
+ * activation buffers that the pass owns; it replays as one CUDA graph (the decode_batch loop of
+ * src/runtime/engine.cpp:1770-1849 reduced to its linear algebra).
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct q38b_pass q38b_pass;
+
+/* Multi-GPU: rank 0 makes a 128-byte id, every rank passes it to q38b_comm_init (NCCL underneath). */
+int q38b_comm_unique_id(void* id128);
+int q38b_comm_init(q38b_ctx* ctx, int n_ranks, int rank, const void* id128);
+
+int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out);
+void q38b_pass_destroy(q38b_pass* pass);
+/* Activation buffers owned by the pass; both return a buffer id >= 0 or a negative q38b_status. */
+int q38b_pass_buffer_f32(q38b_pass* pass, int n);     /* fp32 [max_nb][n] */
+int q38b_pass_buffer_q8k(q38b_pass* pass, int K);     /* Q8_K blocks [max_nb][K/256] */
+void* q38b_pass_buffer_ptr(q38b_pass* pass, int buffer);
+/* Resident matrices; return a matrix id >= 0.  _upload copies this rank's row shard of a host matrix of M rows into
+ * HBM, packed (M divisible by n_shards);
+ * _device adopts rows that are already on the device (M_local rows, not copied, not freed). */
+int q38b_pass_matrix_upload(q38b_pass* pass, uint32_t type, const void* W_host, size_t row_bytes, int K, int M, int shard,
+                            int n_shards);
+int q38b_pass_matrix_device(q38b_pass* pass, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M_local);
+/* Steps, appended in execution order.  Offsets and counts are in floats per column. */
+int q38b_pass_op_quantize(q38b_pass* pass, int src_f32, int src_off, int K, int dst_q8k);
+int q38b_pass_op_gemv(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
+int q38b_pass_op_swiglu(q38b_pass* pass, int g_f32, int g_off, int u_f32, int u_off, int n, int dst_q8k);
+/* In-place all-gather over the ranks: rank g holds [off + g*count, off + (g+1)*count) of every column. */
+int q38b_pass_op_allgather(q38b_pass* pass, int buf_f32, int off, int count_per_rank);
+/* Runs the recorded steps for nb columns (1..max_nb) on `stream`; the first run for each nb captures the graph. */
+int q38b_pass_run(q38b_pass* pass, int nb, void* stream);
+/* End to end with host buffers: copies x_host [nb][x_len] into buffer `in_f32`, runs, copies [nb][y_len] of buffer
+ * `out_f32` (from float offset out_off) back to y_host and synchronises. */
+int q38b_pass_run_host(q38b_pass* pass, int nb, int in_f32, const float* x_host, int x_len, int out_f32, int out_off,
+                       float* y_host, int y_len, void* stream);
+/* Weight bytes one run streams from HBM on this rank (sum over the matvec steps). */
+long long q38b_pass_weight_bytes(const q38b_pass* pass);
+int q38b_pass_kernel_count(const q38b_pass* pass);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,26 @@ def load_library():
     lib.q38b_gemv_q8k.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_swiglu_q8k.argtypes = [vp, vp, vp, ll, i32, i32, vp, vp, ll, vp]
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
+    lib.q38b_comm_unique_id.argtypes = [vp]
+    lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
+    lib.q38b_pass_create.argtypes = [vp, i32, C.POINTER(vp)]
+    lib.q38b_pass_destroy.argtypes = [vp]
+    lib.q38b_pass_destroy.restype = None
+    lib.q38b_pass_buffer_f32.argtypes = [vp, i32]
+    lib.q38b_pass_buffer_q8k.argtypes = [vp, i32]
+    lib.q38b_pass_buffer_ptr.argtypes = [vp, i32]
+    lib.q38b_pass_buffer_ptr.restype = vp
+    lib.q38b_pass_matrix_upload.argtypes = [vp, u32, vp, sz, i32, i32, i32, i32]
+    lib.q38b_pass_matrix_device.argtypes = [vp, u32, vp, sz, i32, i32]
+    lib.q38b_pass_op_quantize.argtypes = [vp, i32, i32, i32, i32]
+    lib.q38b_pass_op_gemv.argtypes = [vp, i32, i32, i32, i32]
+    lib.q38b_pass_op_swiglu.argtypes = [vp, i32, i32, i32, i32, i32, i32]
+    lib.q38b_pass_op_allgather.argtypes = [vp, i32, i32, i32]
+    lib.q38b_pass_run.argtypes = [vp, i32, vp]
+    lib.q38b_pass_run_host.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, i32, vp]
+    lib.q38b_pass_weight_bytes.argtypes = [vp]
+    lib.q38b_pass_weight_bytes.restype = ll
+    lib.q38b_pass_kernel_count.argtypes = [vp]
     _LIB = lib
     return lib
 
@@ -94,6 +114,8 @@ class Context:
 
     def _rc(self, rc, what):
         if rc:
+            if rc == -4:
+                what += f" [cudaError {self.lib.q38b_last_cuda_error(self.h)}]"
             raise Q38BError(rc, what)
 
     def check(self):
@@ -155,3 +177,89 @@ class Context:
         self._rc(self.lib.q38b_dequant_rows(self.h, f.type_id, W.data_ptr(), W.stride(0), K, rows, out.data_ptr(), kind,
                                             _stream()), "q38b_dequant_rows")
         return out
+
+
+class Pass:
+    """Recorded decode pass over resident matrices (q38b_pass): the all-HBM planner's run-time object."""
+
+    def __init__(self, ctx, max_nb=1):
+        self.ctx, self.lib, self.max_nb = ctx, ctx.lib, max_nb
+        h = C.c_void_p()
+        ctx._rc(self.lib.q38b_pass_create(ctx.h, max_nb, C.byref(h)), "q38b_pass_create")
+        self.h = h
+        self._keep = []          # device tensors adopted with matrix_device stay alive with the pass
+        self._sizes = {}
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.q38b_pass_destroy(self.h)
+            self.h = None
+
+    def _id(self, rc, what):
+        if rc < 0:
+            raise Q38BError(rc, what)
+        return rc
+
+    def buffer_f32(self, n):
+        i = self._id(self.lib.q38b_pass_buffer_f32(self.h, n), "q38b_pass_buffer_f32")
+        self._sizes[i] = n
+        return i
+
+    def buffer_q8k(self, K):
+        return self._id(self.lib.q38b_pass_buffer_q8k(self.h, K), "q38b_pass_buffer_q8k")
+
+    def buffer_tensor(self, buf):
+        """A torch view [max_nb, n] of an fp32 buffer of the pass (no copy)."""
+        n = self._sizes[buf]
+        ptr = self.lib.q38b_pass_buffer_ptr(self.h, buf)
+        return _tensor_from_ptr(ptr, (self.max_nb, n), self.ctx.device)
+
+    def matrix_upload(self, fmt, w_host, K, shard=0, n_shards=1):
+        """w_host: numpy uint8 [M, row_bytes] in host memory; uploads rows of this shard."""
+        f = F.get(fmt)
+        M, rb = w_host.shape
+        return self._id(self.lib.q38b_pass_matrix_upload(self.h, f.type_id, w_host.ctypes.data, rb, K, M, shard, n_shards),
+                        "q38b_pass_matrix_upload")
+
+    def matrix_device(self, fmt, W, K):
+        f = F.get(fmt)
+        self._keep.append(W)
+        return self._id(self.lib.q38b_pass_matrix_device(self.h, f.type_id, W.data_ptr(), W.stride(0), K, W.shape[0]),
+                        "q38b_pass_matrix_device")
+
+    def quantize(self, src, off, K, dst):
+        self.ctx._rc(self.lib.q38b_pass_op_quantize(self.h, src, off, K, dst), "q38b_pass_op_quantize")
+
+    def gemv(self, mat, src_q, dst, off=0):
+        self.ctx._rc(self.lib.q38b_pass_op_gemv(self.h, mat, src_q, dst, off), "q38b_pass_op_gemv")
+
+    def swiglu(self, g, g_off, u, u_off, n, dst_q):
+        self.ctx._rc(self.lib.q38b_pass_op_swiglu(self.h, g, g_off, u, u_off, n, dst_q), "q38b_pass_op_swiglu")
+
+    def allgather(self, buf, off, count):
+        self.ctx._rc(self.lib.q38b_pass_op_allgather(self.h, buf, off, count), "q38b_pass_op_allgather")
+
+    def run(self, nb=1):
+        self.ctx._rc(self.lib.q38b_pass_run(self.h, nb, _stream()), "q38b_pass_run")
+
+    def run_host(self, nb, in_buf, x_host, out_buf, out_off, y_host):
+        """x_host, y_host: C-contiguous numpy float32 [nb, len]; host to device and back inside the call."""
+        self.ctx._rc(self.lib.q38b_pass_run_host(self.h, nb, in_buf, x_host.ctypes.data, x_host.shape[1], out_buf, out_off,
+                                                 y_host.ctypes.data, y_host.shape[1], _stream()), "q38b_pass_run_host")
+
+    @property
+    def weight_bytes(self):
+        return int(self.lib.q38b_pass_weight_bytes(self.h))
+
+    @property
+    def kernel_count(self):
+        return int(self.lib.q38b_pass_kernel_count(self.h))
+
+
+def _tensor_from_ptr(ptr, shape, device):
+    """Wraps device memory owned by the library as a float32 torch tensor (via __cuda_array_interface__)."""
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+    return torch.as_tensor(h, device=device)

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq38b200.so")
-SOURCES = ["q38b_api.cu"]
+SOURCES = ["q38b_api.cu", "q38b_plan.cu"]
 
 
 def _stale():
@@ -26,7 +26,7 @@ def build(verbose=False, force=False):
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
            "-Xcompiler", "-fPIC,-O2", "-shared", "-ccbin", "g++",
-           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcudart"]
+           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcudart", "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v,-warn-spills")
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -8,20 +8,10 @@
 
 #include "../../include/q38b200.h"
 #include "q38b_act.cuh"
+#include "q38b_internal.h"
 #include "q38b_gemv.cuh"
 
 using namespace q38b;
-
-struct q38b_ctx {
-    int device = 0;
-    int sm_count = 0;
-    int smem_optin = 0;
-    int last_cuda = 0;
-    int pdl = 1;
-    int* d_status = nullptr;
-    uint32_t* d_cb_iq3xxs = nullptr;
-    uint32_t* d_cb_iq3s = nullptr;
-};
 
 namespace {
 

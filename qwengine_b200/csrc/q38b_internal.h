@@ -1,0 +1,16 @@
+// q38b_internal.h -- host-side state shared by the translation units of libq38b200.so.
+#pragma once
+#include <cstdint>
+
+struct q38b_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    int last_cuda = 0;
+    int pdl = 1;
+    int* d_status = nullptr;
+    uint32_t* d_cb_iq3xxs = nullptr;
+    uint32_t* d_cb_iq3s = nullptr;
+    void* comm = nullptr;   // ncclComm_t when q38b_comm_init was called
+    int n_ranks = 1, rank = 0;
+};

@@ -1,0 +1,314 @@
+// q38b_plan.cu -- the all-HBM planner: resident row-sharded matrices, pass recording, CUDA-graph replay,
+// NCCL all-gather of output slices (NCCL is bound at run time with dlopen so that single-GPU users need no NCCL).
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/q38b200.h"
+#include "q38b_internal.h"
+
+namespace {
+
+// ---- minimal NCCL binding -------------------------------------------------------------------------------------
+typedef struct { char internal[128]; } NcclId;
+typedef int (*FnGetUniqueId)(NcclId*);
+typedef int (*FnCommInitRank)(void**, int, NcclId, int);
+typedef int (*FnAllGather)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*FnGroup)();
+typedef int (*FnCommDestroy)(void*);
+struct Nccl {
+    void* lib = nullptr;
+    FnGetUniqueId get_id = nullptr;
+    FnCommInitRank init_rank = nullptr;
+    FnAllGather all_gather = nullptr;
+    FnGroup group_start = nullptr, group_end = nullptr;
+    FnCommDestroy destroy = nullptr;
+    bool ok() const { return lib && get_id && init_rank && all_gather && group_start && group_end; }
+};
+Nccl& nccl() {
+    static Nccl n;
+    if (!n.lib) {
+        n.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!n.lib) n.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (n.lib) {
+            n.get_id = (FnGetUniqueId)dlsym(n.lib, "ncclGetUniqueId");
+            n.init_rank = (FnCommInitRank)dlsym(n.lib, "ncclCommInitRank");
+            n.all_gather = (FnAllGather)dlsym(n.lib, "ncclAllGather");
+            n.group_start = (FnGroup)dlsym(n.lib, "ncclGroupStart");
+            n.group_end = (FnGroup)dlsym(n.lib, "ncclGroupEnd");
+            n.destroy = (FnCommDestroy)dlsym(n.lib, "ncclCommDestroy");
+        }
+    }
+    return n;
+}
+constexpr int NCCL_FLOAT = 7;
+
+enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER };
+struct Op { int kind, a, b, c, d, n, off; };
+struct Buf { void* ptr; int n; bool q8k; };
+struct Mat { uint32_t type; const void* W; size_t row_bytes; int K, M; bool owned; };
+
+}  // namespace
+
+struct q38b_pass {
+    q38b_ctx* ctx = nullptr;
+    int max_nb = 1;
+    std::vector<Buf> bufs;
+    std::vector<Mat> mats;
+    std::vector<Op> ops;
+    cudaGraphExec_t graphs[9] = {};
+    cudaStream_t cap_stream = nullptr;   // capture happens here: the caller's stream may be the legacy default stream
+    float* pin_in = nullptr;
+    float* pin_out = nullptr;
+    size_t pin_in_n = 0, pin_out_n = 0;
+};
+
+#define PASS_CUDA(p, call)                                \
+    do {                                                  \
+        cudaError_t e_ = (call);                          \
+        if (e_ != cudaSuccess) {                          \
+            (p)->ctx->last_cuda = (int)e_;                \
+            return Q38B_ERR_CUDA;                         \
+        }                                                 \
+    } while (0)
+
+namespace {
+bool is_f32(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && !p->bufs[id].q8k; }
+bool is_q8k(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && p->bufs[id].q8k; }
+
+int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
+    q38b_ctx* ctx = p->ctx;
+    for (const Op& o : p->ops) {
+        int rc = Q38B_OK;
+        switch (o.kind) {
+            case OP_QUANT: {
+                const Buf& s = p->bufs[o.a];
+                const Buf& d = p->bufs[o.b];
+                rc = q38b_quantize_q8k(ctx, (const float*)s.ptr + o.off, s.n, o.n, nb, d.ptr, d.n / 256, st);
+                break;
+            }
+            case OP_GEMV: {
+                const Mat& m = p->mats[o.a];
+                const Buf& s = p->bufs[o.b];
+                const Buf& d = p->bufs[o.c];
+                rc = q38b_gemv_q8k(ctx, m.type, m.W, m.row_bytes, m.K, m.M, s.ptr, s.n / 256, nb, (float*)d.ptr + o.off, d.n, 0, st);
+                break;
+            }
+            case OP_SWIGLU: {
+                const Buf& g = p->bufs[o.a];
+                const Buf& u = p->bufs[o.b];
+                const Buf& d = p->bufs[o.c];
+                if (g.n != u.n) return Q38B_ERR_ARG;
+                rc = q38b_swiglu_q8k(ctx, (const float*)g.ptr + o.off, (const float*)u.ptr + o.d, g.n, o.n, nb, nullptr, d.ptr,
+                                     d.n / 256, st);
+                break;
+            }
+            case OP_GATHER: {
+                if (ctx->n_ranks <= 1) break;
+                Nccl& n = nccl();
+                if (!n.ok() || !ctx->comm) return Q38B_ERR_ARG;
+                const Buf& b = p->bufs[o.a];
+                if (n.group_start()) return Q38B_ERR_CUDA;
+                for (int c = 0; c < nb; c++) {
+                    float* base = (float*)b.ptr + (size_t)c * b.n + o.off;
+                    if (n.all_gather(base + (size_t)ctx->rank * o.n, base, (size_t)o.n, NCCL_FLOAT, ctx->comm, st)) return Q38B_ERR_CUDA;
+                }
+                if (n.group_end()) return Q38B_ERR_CUDA;
+                break;
+            }
+        }
+        if (rc != Q38B_OK) return rc;
+    }
+    return Q38B_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int q38b_comm_unique_id(void* id128) {
+    if (!id128) return Q38B_ERR_ARG;
+    Nccl& n = nccl();
+    if (!n.ok()) return Q38B_ERR_UNSUPPORTED;
+    NcclId id;
+    if (n.get_id(&id)) return Q38B_ERR_CUDA;
+    memcpy(id128, &id, 128);
+    return Q38B_OK;
+}
+
+int q38b_comm_init(q38b_ctx* ctx, int n_ranks, int rank, const void* id128) {
+    if (!ctx || !id128 || n_ranks < 1 || rank < 0 || rank >= n_ranks) return Q38B_ERR_ARG;
+    Nccl& n = nccl();
+    if (!n.ok()) return Q38B_ERR_UNSUPPORTED;
+    NcclId id;
+    memcpy(&id, id128, 128);
+    void* comm = nullptr;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return Q38B_ERR_CUDA;
+    if (n.init_rank(&comm, n_ranks, id, rank)) return Q38B_ERR_CUDA;
+    ctx->comm = comm;
+    ctx->n_ranks = n_ranks;
+    ctx->rank = rank;
+    return Q38B_OK;
+}
+
+int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out) {
+    if (!ctx || !out || max_nb < 1 || max_nb > 8) return Q38B_ERR_ARG;
+    q38b_pass* p = new (std::nothrow) q38b_pass;
+    if (!p) return Q38B_ERR_NOMEM;
+    p->ctx = ctx;
+    p->max_nb = max_nb;
+    *out = p;
+    return Q38B_OK;
+}
+
+void q38b_pass_destroy(q38b_pass* p) {
+    if (!p) return;
+    for (auto& g : p->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& b : p->bufs) if (b.ptr) cudaFree(b.ptr);
+    for (auto& m : p->mats) if (m.owned && m.W) cudaFree((void*)m.W);
+    if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
+    if (p->pin_in) cudaFreeHost(p->pin_in);
+    if (p->pin_out) cudaFreeHost(p->pin_out);
+    delete p;
+}
+
+int q38b_pass_buffer_f32(q38b_pass* p, int n) {
+    if (!p || n < 1) return Q38B_ERR_ARG;
+    void* ptr = nullptr;
+    PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * n * sizeof(float)));
+    PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * n * sizeof(float)));
+    p->bufs.push_back({ptr, n, false});
+    return (int)p->bufs.size() - 1;
+}
+
+int q38b_pass_buffer_q8k(q38b_pass* p, int K) {
+    if (!p || K < 256 || K % 256) return Q38B_ERR_ARG;
+    void* ptr = nullptr;
+    PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * (K / 256) * 292));
+    PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * (K / 256) * 292));
+    p->bufs.push_back({ptr, K, true});
+    return (int)p->bufs.size() - 1;
+}
+
+void* q38b_pass_buffer_ptr(q38b_pass* p, int id) { return p && id >= 0 && id < (int)p->bufs.size() ? p->bufs[id].ptr : nullptr; }
+
+int q38b_pass_matrix_device(q38b_pass* p, uint32_t type, const void* W, size_t row_bytes, int K, int M) {
+    if (!p || !W || M < 1) return Q38B_ERR_ARG;
+    if (!q38b_format_supported(type)) return Q38B_ERR_UNSUPPORTED;
+    if (row_bytes < q38b_row_bytes(type, K) || !q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
+    if ((uintptr_t)W & 15) return Q38B_ERR_ALIGN;
+    p->mats.push_back({type, W, row_bytes, K, M, false});
+    return (int)p->mats.size() - 1;
+}
+
+int q38b_pass_matrix_upload(q38b_pass* p, uint32_t type, const void* W_host, size_t row_bytes, int K, int M, int shard,
+                            int n_shards) {
+    if (!p || !W_host || M < 1 || n_shards < 1 || shard < 0 || shard >= n_shards || M % n_shards) return Q38B_ERR_ARG;
+    if (!q38b_format_supported(type)) return Q38B_ERR_UNSUPPORTED;
+    const size_t packed = q38b_row_bytes(type, K);
+    if (!packed || row_bytes < packed) return Q38B_ERR_ARG;
+    const int rows = M / n_shards;
+    // the shard starts on a 16-byte boundary of a packed copy: rows are packed on upload
+    void* dev = nullptr;
+    PASS_CUDA(p, cudaMalloc(&dev, (size_t)rows * packed + 16));
+    const uint8_t* src = (const uint8_t*)W_host + (size_t)shard * rows * row_bytes;
+    PASS_CUDA(p, cudaMemcpy2D(dev, packed, src, row_bytes, packed, rows, cudaMemcpyHostToDevice));
+    p->mats.push_back({type, dev, packed, K, rows, true});
+    return (int)p->mats.size() - 1;
+}
+
+int q38b_pass_op_quantize(q38b_pass* p, int src, int off, int K, int dst) {
+    if (!p || !is_f32(p, src) || !is_q8k(p, dst) || K % 256 || off < 0 || off + K > p->bufs[src].n || p->bufs[dst].n < K) return Q38B_ERR_ARG;
+    p->ops.push_back({OP_QUANT, src, dst, 0, 0, K, off});
+    return Q38B_OK;
+}
+
+int q38b_pass_op_gemv(q38b_pass* p, int mat, int src, int dst, int off) {
+    if (!p || mat < 0 || mat >= (int)p->mats.size() || !is_q8k(p, src) || !is_f32(p, dst)) return Q38B_ERR_ARG;
+    const Mat& m = p->mats[mat];
+    if (p->bufs[src].n < m.K || off < 0 || off + m.M > p->bufs[dst].n) return Q38B_ERR_ARG;
+    p->ops.push_back({OP_GEMV, mat, src, dst, 0, 0, off});
+    return Q38B_OK;
+}
+
+int q38b_pass_op_swiglu(q38b_pass* p, int g, int g_off, int u, int u_off, int n, int dst) {
+    if (!p || !is_f32(p, g) || !is_f32(p, u) || !is_q8k(p, dst) || n % 256 || g_off < 0 || u_off < 0) return Q38B_ERR_ARG;
+    if (g_off + n > p->bufs[g].n || u_off + n > p->bufs[u].n || p->bufs[dst].n < n || p->bufs[g].n != p->bufs[u].n) return Q38B_ERR_ARG;
+    p->ops.push_back({OP_SWIGLU, g, u, dst, u_off, n, g_off});
+    return Q38B_OK;
+}
+
+int q38b_pass_op_allgather(q38b_pass* p, int buf, int off, int count) {
+    if (!p || !is_f32(p, buf) || off < 0 || count < 1) return Q38B_ERR_ARG;
+    const int ranks = p->ctx->n_ranks > 1 ? p->ctx->n_ranks : 1;
+    if (off + (long long)count * ranks > p->bufs[buf].n) return Q38B_ERR_ARG;
+    p->ops.push_back({OP_GATHER, buf, 0, 0, 0, count, off});
+    return Q38B_OK;
+}
+
+int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
+    if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!p->graphs[nb]) {
+        cudaGraph_t g = nullptr;
+        if (!p->cap_stream) PASS_CUDA(p, cudaStreamCreateWithFlags(&p->cap_stream, cudaStreamNonBlocking));
+        PASS_CUDA(p, cudaStreamBeginCapture(p->cap_stream, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue(p, nb, p->cap_stream);
+        const cudaError_t e = cudaStreamEndCapture(p->cap_stream, &g);
+        if (rc != Q38B_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) { p->ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+        const cudaError_t ei = cudaGraphInstantiate(&p->graphs[nb], g, 0);
+        cudaGraphDestroy(g);
+        if (ei != cudaSuccess) { p->ctx->last_cuda = (int)ei; p->graphs[nb] = nullptr; return Q38B_ERR_CUDA; }
+    }
+    PASS_CUDA(p, cudaGraphLaunch(p->graphs[nb], st));
+    return Q38B_OK;
+}
+
+int q38b_pass_run_host(q38b_pass* p, int nb, int in_buf, const float* x_host, int x_len, int out_buf, int out_off,
+                       float* y_host, int y_len, void* stream) {
+    if (!p || !x_host || !y_host || nb < 1 || nb > p->max_nb || !is_f32(p, in_buf) || !is_f32(p, out_buf)) return Q38B_ERR_ARG;
+    if (x_len < 1 || x_len > p->bufs[in_buf].n || out_off < 0 || y_len < 1 || out_off + y_len > p->bufs[out_buf].n) return Q38B_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t need_in = (size_t)p->max_nb * x_len, need_out = (size_t)p->max_nb * y_len;
+    if (p->pin_in_n < need_in) {
+        if (p->pin_in) cudaFreeHost(p->pin_in);
+        PASS_CUDA(p, cudaMallocHost(&p->pin_in, need_in * sizeof(float)));
+        p->pin_in_n = need_in;
+    }
+    if (p->pin_out_n < need_out) {
+        if (p->pin_out) cudaFreeHost(p->pin_out);
+        PASS_CUDA(p, cudaMallocHost(&p->pin_out, need_out * sizeof(float)));
+        p->pin_out_n = need_out;
+    }
+    memcpy(p->pin_in, x_host, (size_t)nb * x_len * sizeof(float));
+    const Buf& bi = p->bufs[in_buf];
+    const Buf& bo = p->bufs[out_buf];
+    PASS_CUDA(p, cudaMemcpy2DAsync(bi.ptr, (size_t)bi.n * 4, p->pin_in, (size_t)x_len * 4, (size_t)x_len * 4, nb, cudaMemcpyHostToDevice, st));
+    const int rc = q38b_pass_run(p, nb, stream);
+    if (rc != Q38B_OK) return rc;
+    PASS_CUDA(p, cudaMemcpy2DAsync(p->pin_out, (size_t)y_len * 4, (const float*)bo.ptr + out_off, (size_t)bo.n * 4, (size_t)y_len * 4, nb,
+                                   cudaMemcpyDeviceToHost, st));
+    PASS_CUDA(p, cudaStreamSynchronize(st));
+    memcpy(y_host, p->pin_out, (size_t)nb * y_len * sizeof(float));
+    return Q38B_OK;
+}
+
+long long q38b_pass_weight_bytes(const q38b_pass* p) {
+    if (!p) return 0;
+    long long b = 0;
+    for (const Op& o : p->ops)
+        if (o.kind == OP_GEMV) b += (long long)p->mats[o.a].M * (long long)q38b_row_bytes(p->mats[o.a].type, p->mats[o.a].K);
+    return b;
+}
+
+int q38b_pass_kernel_count(const q38b_pass* p) {
+    if (!p) return 0;
+    int n = 0;
+    for (const Op& o : p->ops) n += o.kind != OP_GATHER;
+    return n;
+}
+
+}  // extern "C"

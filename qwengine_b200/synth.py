@@ -16,7 +16,12 @@ _FP16_FIELDS = {
 }
 
 
-def make_weights(fmt, M: int, K: int, seed: int, scale: float = 1e-3) -> np.ndarray:
+# Q4_K / Q5_K weights are d*sc*q - dmin*m with unsigned q, sc, m: with dmin = ZERO_MEAN_DMIN * d their mean over
+# uniformly random quants is zero, which keeps a chain of matvecs from amplifying the mean of its input.
+ZERO_MEAN_DMIN = {"Q4_K": 7.5, "Q5_K": 15.5}
+
+
+def make_weights(fmt, M: int, K: int, seed: int, scale: float = 1e-3, zero_mean: bool = False) -> np.ndarray:
     """Returns a uint8 array [M, row_bytes] of random valid blocks."""
     f = F.get(fmt)
     rng = np.random.Generator(np.random.PCG64(seed))
@@ -24,6 +29,9 @@ def make_weights(fmt, M: int, K: int, seed: int, scale: float = 1e-3) -> np.ndar
     w = rng.integers(0, 256, size=(M, nblk, f.block_bytes), dtype=np.uint8)
     for off in _FP16_FIELDS[f.name]:
         d = (np.abs(rng.standard_normal((M, nblk), dtype=np.float32)) * np.float32(scale)).astype(np.float16)
+        if zero_mean and off == 2 and f.name in ZERO_MEAN_DMIN:
+            d0 = w[:, :, 0:2].copy().view(np.float16).reshape(M, nblk).astype(np.float32)
+            d = (d0 * np.float32(ZERO_MEAN_DMIN[f.name])).astype(np.float16)
         w[:, :, off:off + 2] = d.view(np.uint8).reshape(M, nblk, 2)
     return w.reshape(M, nblk * f.block_bytes)
 
