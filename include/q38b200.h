@@ -51,6 +51,12 @@ int q38b_last_cuda_error(const q38b_ctx* ctx);
 const char* q38b_status_string(int status);
 /* Enable (1, default) or disable (0) programmatic dependent launch between consecutive kernels of a stream. */
 int q38b_ctx_set_pdl(q38b_ctx* ctx, int enabled);
+/* Single-column calls (nb = 1) normally run a dedicated dp4a kernel whose float summation order differs from the
+ * tensor-core kernel used for nb >= 2 (both are exact in their integer parts and agree to ~1e-7).  With this option
+ * set to 1, nb = 1 also runs the tensor-core kernel, so that every column of an nb-column call is bit-identical to
+ * the one-column call, as gemv_q8n promises (src/cuda/gemv.cuh:31-34).  Columns of calls with nb >= 2 are always
+ * bit-identical to each other across nb. */
+int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled);
 
 /* Replaces gemv_q8_supported (src/cuda/gemv.cu:206-213): 1 if `type` has a matvec kernel here. */
 int q38b_format_supported(uint32_t type);
@@ -66,8 +72,8 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x_dev, long long x_ld, int K, 
 
 /* Replaces gemv_q8n / gemv_q8 (src/cuda/gemv.cu:215-233) with Q8_K activations as the CPU kernels take them
  * (vec_dot_n_fn, src/cpu/cpu_kernels.h:19-22): y_dev[c * y_ld + r] (+)= W[r,:] . x_c for r < M, c < nb (1..8).
- * Column c of the activations starts q8k_stride blocks after column c - 1.  Each column's result is bit-identical
- * to a one-column call.  W_dev must be 16-byte aligned. */
+ * Column c of the activations starts q8k_stride blocks after column c - 1.  Column results do not depend on nb for
+ * nb >= 2 (and for nb = 1 too after q38b_ctx_set_uniform_columns).  W_dev must be 16-byte aligned. */
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* q8k_dev,
                   long long q8k_stride, int nb, float* y_dev, long long y_ld, int accumulate, void* stream);
 

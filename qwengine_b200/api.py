@@ -44,6 +44,7 @@ def load_library():
     lib.q38b_ctx_check.argtypes = [vp, vp]
     lib.q38b_last_cuda_error.argtypes = [vp]
     lib.q38b_ctx_set_pdl.argtypes = [vp, i32]
+    lib.q38b_ctx_set_uniform_columns.argtypes = [vp, i32]
     lib.q38b_status_string.argtypes = [i32]
     lib.q38b_status_string.restype = C.c_char_p
     lib.q38b_format_supported.argtypes = [u32]
@@ -121,6 +122,9 @@ class Context:
     def check(self):
         """Synchronises the current stream and raises if a kernel reported a bounded wait that ran out."""
         self._rc(self.lib.q38b_ctx_check(self.h, _stream()), "q38b_ctx_check")
+
+    def set_uniform_columns(self, enabled):
+        self._rc(self.lib.q38b_ctx_set_uniform_columns(self.h, int(bool(enabled))), "q38b_ctx_set_uniform_columns")
 
     def set_pdl(self, enabled):
         self._rc(self.lib.q38b_ctx_set_pdl(self.h, int(bool(enabled))), "q38b_ctx_set_pdl")

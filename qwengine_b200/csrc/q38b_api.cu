@@ -10,6 +10,7 @@
 #include "q38b_act.cuh"
 #include "q38b_internal.h"
 #include "q38b_gemv.cuh"
+#include "q38b_gemv1.cuh"
 
 using namespace q38b;
 
@@ -121,6 +122,91 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     return Q38B_OK;
 }
 
+constexpr int G1_WARPS = 16;
+
+struct Plan1 {
+    Gemv1Args a;
+    int grid;
+    int smem;
+};
+
+// Shared-memory carve-up of the single-column kernel: barriers | activation scales | activations | codebook |
+// per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
+int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, Plan1* p) {
+    const int bb = block_bytes((int)type);
+    const int nsb = K / 256;
+    const int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
+    const int budget = ctx->smem_optin - 128;
+    Gemv1Args& a = p->a;
+    a.nsb = nsb;
+    a.n_slices = (nsb + 3) / 4;
+    a.n_tiles = (M + G1_ROWS - 1) / G1_ROWS;
+    a.off_actd = 2048;
+    a.off_actq = a.off_actd + a.n_slices * 4 * 32;
+    a.off_cb = a.off_actq + a.n_slices * 1024;
+    const int packed = nsb * bb;
+    // stage shape: 8 whole rows in one bulk copy when the rows are packed and small enough, else 8 per-row copies of a
+    // K-chunk of `chunk_slices` slices (bulk copies are issue-rate limited: keep each above ~2 KB)
+    const int target = 24 * 1024;
+    if ((long long)row_bytes == packed && G1_ROWS * packed <= target) {
+        a.contiguous = 1;
+        a.chunk_slices = a.n_slices;
+        a.slot_stride = packed;
+        a.stage_bytes = align_up(G1_ROWS * packed + 64, 128);
+    } else {
+        a.contiguous = 0;
+        int cs = std::max(1, std::min(a.n_slices, (target / G1_ROWS - 32) / (4 * bb)));
+        const int nch = (a.n_slices + cs - 1) / cs;
+        cs = (a.n_slices + nch - 1) / nch;          // even chunks
+        a.chunk_slices = cs;
+        a.slot_stride = align_up(cs * 4 * bb + 32, 16);
+        a.stage_bytes = align_up(G1_ROWS * a.slot_stride + 64, 128);
+    }
+    a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
+    const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 2;
+    for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= 0; rep_log2 -= (rep_log2 == 5 ? 2 : 3)) {
+        a.cb_rep_log2 = rep_log2;
+        a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
+        for (int stages = G1_MAX_STAGES; stages >= min_stages; stages--) {
+            // tile buffers: a warp can run at most (stages + warps) units ahead of a tile that is still being finished
+            const int tb = (G1_WARPS + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;
+            if (tb > G1_MAX_TILEBUF) continue;
+            a.off_stage = align_up(a.off_red + tb * a.n_slices * G1_ROWS * 4, 128);
+            if (a.off_stage + stages * a.stage_bytes > budget) continue;
+            a.n_stages = stages;
+            a.n_tilebuf = tb;
+            p->smem = a.off_stage + stages * a.stage_bytes + 128;
+            p->grid = std::max(1, std::min(ctx->sm_count, a.n_tiles));
+            return Q38B_OK;
+        }
+        if (!cb_entries) break;
+    }
+    return Q38B_ERR_NOMEM;
+}
+
+template <int FMT>
+int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
+    auto kern = gemv1_kernel<FMT, G1_WARPS>;
+    static int configured_device = -1;
+    if (configured_device != ctx->device) {
+        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin));
+        configured_device = ctx->device;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)p.grid);
+    cfg.blockDim = dim3(32 * (1 + G1_WARPS));
+    cfg.dynamicSmemBytes = (size_t)p.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p.a));
+    return Q38B_OK;
+}
+
 template <int KIND>
 int launch_dequant(q38b_ctx* ctx, uint32_t type, const uint8_t* W, long long rb, int K, int rows, void* out, cudaStream_t st) {
     const long long n = (long long)rows * (K / 32);
@@ -194,6 +280,12 @@ int q38b_ctx_check(q38b_ctx* ctx, void* stream) {
 
 int q38b_last_cuda_error(const q38b_ctx* ctx) { return ctx ? ctx->last_cuda : 0; }
 
+int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->uniform_columns = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+
 int q38b_ctx_set_pdl(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->pdl = enabled ? 1 : 0;
@@ -253,6 +345,35 @@ int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes,
     if (row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
     const int al = format_alignment(type);
     if (((uintptr_t)W & 15) || (row_bytes % al) || ((uintptr_t)q8k & 3) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (nb == 1 && !ctx->uniform_columns) {
+        // single column: the dp4a kernel (one lane per 32- or 64-weight granule)
+        Plan1 p1;
+        memset(&p1, 0, sizeof(p1));
+        const int rc1 = plan_gemv1(ctx, type, K, M, row_bytes, &p1);
+        if (rc1 == Q38B_OK) {
+            Gemv1Args& g = p1.a;
+            g.W = (const uint8_t*)W;
+            g.row_bytes = (long long)row_bytes;
+            g.xq = (const uint8_t*)q8k;
+            g.y = y;
+            g.status = ctx->d_status;
+            g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+            g.K = K;
+            g.M = M;
+            g.accumulate = accumulate ? 1 : 0;
+            switch (type) {
+                case T_Q8_0: return launch_gemv1<T_Q8_0>(ctx, p1, st);
+                case T_Q4_K: return launch_gemv1<T_Q4_K>(ctx, p1, st);
+                case T_Q5_K: return launch_gemv1<T_Q5_K>(ctx, p1, st);
+                case T_Q6_K: return launch_gemv1<T_Q6_K>(ctx, p1, st);
+                case T_IQ3_XXS: return launch_gemv1<T_IQ3_XXS>(ctx, p1, st);
+                case T_IQ3_S: return launch_gemv1<T_IQ3_S>(ctx, p1, st);
+                case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
+                default: return Q38B_ERR_UNSUPPORTED;
+            }
+        }
+    }
     Plan p;
     memset(&p, 0, sizeof(p));
     int rc = plan_gemv(ctx, type, K, M, nb, &p);
@@ -270,7 +391,6 @@ int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes,
     a.M = M;
     a.nb = nb;
     a.accumulate = accumulate ? 1 : 0;
-    cudaStream_t st = (cudaStream_t)stream;
     switch (type) {
         case T_Q8_0: return launch_gemv<T_Q8_0>(ctx, p, st);
         case T_Q4_K: return launch_gemv<T_Q4_K>(ctx, p, st);

@@ -1,0 +1,256 @@
+// q38b_gemv1.cuh -- single-column decode matvec: y[r] (+)= W[r,:] . x.
+//
+// Same streaming scheme as gemv_kernel (persistent CTA per SM, producer warp, 1-D bulk copies of each row slice's
+// 16-byte aligned superset into a ring of stages guarded by mbarriers), but the stage is small -- 8 rows x one
+// 1024-weight slice -- and belongs to ONE consumer warp: lane l owns granule l of the slice, holds its int8
+// activations in registers for all 8 rows and runs the dp4a decoders of q38b_decode1.cuh.  Stage k goes to warp
+// k % W, so the warps never synchronise with each other except through the per-tile reduction:
+// each (tile, slice) writes its 8 row sums to its own slot and arrives on the tile's mbarrier; the warp that took
+// the tile's last slice waits for the others, adds the slices in order (deterministic) and stores y.
+#pragma once
+#include "q38b_decode1.cuh"
+#include "q38b_pipe.cuh"
+
+namespace q38b {
+
+constexpr int G1_ROWS = 8;           // rows per stage / tile
+constexpr int G1_MAX_STAGES = 64;
+constexpr int G1_MAX_TILEBUF = 64;
+
+struct Gemv1Args {
+    const uint8_t* W;
+    long long row_bytes;
+    const uint8_t* xq;      // Q8_K blocks of the single column
+    float* y;
+    int* status;
+    const uint32_t* codebook;
+    int K, M, accumulate;
+    int nsb;                // super-blocks per row
+    int n_slices;           // ceil(nsb / 4)
+    int n_tiles;            // ceil(M / 8)
+    int n_stages;
+    int chunk_slices;       // slices per stage (K-chunk); n_chunks = ceil(n_slices / chunk_slices)
+    int n_chunks;
+    int contiguous;         // 1: a stage is 8 whole packed rows, fetched by one bulk copy
+    int slot_stride;        // bytes between the rows of a stage (row_bytes when contiguous)
+    int stage_bytes;
+    int n_tilebuf;
+    int cb_rep_log2;
+    int off_actd, off_actq, off_cb, off_red, off_stage;
+};
+
+template <int FMT, int NWARPS>
+__global__ void __launch_bounds__(32 * (1 + NWARPS), 1) gemv1_kernel(const Gemv1Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    uint64_t* full = (uint64_t*)smem;                        // [G1_MAX_STAGES]
+    uint64_t* empty = full + G1_MAX_STAGES;                  // [G1_MAX_STAGES]
+    uint64_t* tbar = empty + G1_MAX_STAGES;                  // [G1_MAX_TILEBUF]
+    volatile int* abort_flag = (volatile int*)(tbar + G1_MAX_TILEBUF);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int BB = Unit<FMT>::BLOCK_BYTES;
+    constexpr int SLICE_BYTES = 4 * BB;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), a.chunk_slices); }
+        for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&tbar[t]), a.n_slices);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const int my_tiles = a.n_tiles > (int)blockIdx.x ? (a.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int n_items = my_tiles * a.n_chunks;       // stages this CTA streams
+    const int packed_row = a.nsb * BB;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane < G1_ROWS) {
+            const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
+            const uintptr_t safe_end = w_end & ~(uintptr_t)15;
+            int ti = 0, chunk = 0;
+            for (int item = 0; item < n_items; item++) {
+                const int stage = item % a.n_stages;
+                const uint32_t use = (uint32_t)(item / a.n_stages);
+                const uint32_t fb = smem_u32(&full[stage]);
+                mbar_wait_bounded(smem_u32(&empty[stage]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+                const int row0 = ((int)blockIdx.x + (int)gridDim.x * ti) * G1_ROWS;
+                uint8_t* sbase = smem + a.off_stage + (size_t)stage * a.stage_bytes;
+                // what this lane copies: the whole tile (lane 0, contiguous rows) or its own row's chunk
+                uintptr_t src = 0;
+                long long len = 0;
+                uint8_t* slot = sbase;
+                if (a.contiguous) {
+                    if (lane == 0) {
+                        src = (uintptr_t)a.W + (uintptr_t)row0 * a.row_bytes;
+                        len = (long long)min(G1_ROWS, a.M - row0) * a.row_bytes;
+                    }
+                } else if (row0 + lane < a.M) {
+                    const int off = chunk * a.chunk_slices * SLICE_BYTES;
+                    src = (uintptr_t)a.W + (uintptr_t)(row0 + lane) * a.row_bytes + (uintptr_t)off;
+                    len = min(a.chunk_slices * SLICE_BYTES, packed_row - off);
+                    slot = sbase + (size_t)lane * a.slot_stride;
+                }
+                if (len <= 0) {
+                    mbar_arrive(fb);
+                } else {
+                    const uintptr_t lo = src & ~(uintptr_t)15;
+                    uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
+                    if (hi > safe_end) {   // the tensor's last bytes do not fill a 16-byte unit: plain loads
+                        hi = safe_end > lo ? safe_end : lo;
+                        for (uintptr_t p = hi; p < src + len; p += 2)
+                            if (p >= src) *(uint16_t*)(slot + (p - lo)) = *(const uint16_t*)p;
+                    }
+                    const uint32_t bytes = (uint32_t)(hi - lo);
+                    if (bytes) {
+                        mbar_arrive_expect_tx(fb, bytes);
+                        bulk_copy_g2s(smem_u32(slot), (const void*)lo, bytes, fb);
+                    } else {
+                        mbar_arrive(fb);
+                    }
+                }
+                if (++chunk == a.n_chunks) { chunk = 0; ti++; }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int cw = warp - 1;
+    const int ctid = tid - 32;
+    float* actd = (float*)(smem + a.off_actd);       // [nsb][8], column 0 used
+    uint8_t* actq = smem + a.off_actq;               // [n_slices * 1024] staged order
+    uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
+    constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
+    if (CBN > 0) {
+        const int rep = 1 << a.cb_rep_log2;
+        for (int i = ctid; i < CBN * rep; i += NWARPS * 32) cbw[i] = a.codebook[i >> a.cb_rep_log2];
+    }
+    pdl_wait_prior();
+    for (int i = ctid; i < a.n_slices * 4; i += NWARPS * 32)
+        actd[i * 8] = i < a.nsb ? *(const float*)(a.xq + (size_t)i * Q8K_BYTES) : 0.0f;
+    for (int i = ctid; i < a.n_slices * 256; i += NWARPS * 32) {   // word i of the (zero padded) activation vector
+        const int sb = i >> 6, wi = i & 63;
+        const uint32_t v = sb < a.nsb ? *(const uint32_t*)(a.xq + (size_t)sb * Q8K_BYTES + 4 + 4 * wi) : 0u;
+        uint8_t* dst = actq + sb * 256;
+        if (FMT == T_IQ4_XS) {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int k = 4 * wi + b;
+                dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)(v >> (8 * b));
+            }
+        } else {
+            *(uint32_t*)(dst + 4 * wi) = v;
+        }
+    }
+    named_bar_sync(15, NWARPS * 32);
+
+    Codebook cb;
+    cb.words = cbw;
+    cb.rep_log2 = a.cb_rep_log2;
+    cb.lane_word = (uint32_t)lane & ((1u << a.cb_rep_log2) - 1u);
+    float* red = (float*)(smem + a.off_red);         // [n_tilebuf][n_slices][8]
+
+    constexpr int LPR = Gran<FMT>::LANES_PER_ROW;    // 32, or 16 when two rows share a warp pass
+    constexpr int PASSES = G1_ROWS * LPR / 32;       // row passes per stage: 8 or 4
+    const int sub = LPR == 32 ? 0 : (lane >> 4);     // which of the two rows of a pass this lane works on
+
+    const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
+    for (int unit = cw; unit < n_units; unit += NWARPS) {
+        const int ti = unit / a.n_slices, slice = unit - ti * a.n_slices;
+        const int chunk = slice / a.chunk_slices, cslice = slice - chunk * a.chunk_slices;
+        const int item = ti * a.n_chunks + chunk;
+        const int stage = item % a.n_stages;
+        const uint32_t use = (uint32_t)(item / a.n_stages);
+        typename Gran<FMT>::Acts acts;
+        Gran<FMT>::load_acts(acts, actq + slice * 1024, actd + slice * 32, lane);
+        // granules past the end of the row (K not a multiple of 1024) contribute nothing
+        const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
+        const bool live = gran_sb < a.nsb;
+        mbar_wait_bounded(smem_u32(&full[stage]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+        const int tile = (int)blockIdx.x + (int)gridDim.x * ti;
+        const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes + (size_t)cslice * SLICE_BYTES;
+        // address of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
+        const uintptr_t src0 = (uintptr_t)a.W + (uintptr_t)(tile * G1_ROWS) * a.row_bytes +
+                               (uintptr_t)(a.contiguous ? 0 : chunk * a.chunk_slices * SLICE_BYTES);
+        float acc[PASSES];
+#pragma unroll
+        for (int ps = 0; ps < PASSES; ps++) {
+            const int r = LPR == 32 ? ps : 2 * ps + sub;
+            const uint8_t* rowp = st + (size_t)r * a.slot_stride + ((src0 + (a.contiguous ? 0 : (uintptr_t)r * a.row_bytes)) & 15);
+            const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
+            acc[ps] = live ? v : 0.0f;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
+            const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
+            const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
+            mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
+        }
+
+        // sum over the lanes of each row: halving butterfly, then plain butterflies
+        float rowsum;   // lanes with the same (lane & mask) end up with the sum of one row
+        if (LPR == 32) {
+            // 8 accumulators (rows 0..7) over 32 lanes
+            float v4[4], v2[2];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float keep = (lane & 16) ? acc[i + 4] : acc[i], give = (lane & 16) ? acc[i] : acc[i + 4];
+                v4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float keep = (lane & 8) ? v4[i + 2] : v4[i], give = (lane & 8) ? v4[i] : v4[i + 2];
+                v2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+            }
+            {
+                const float keep = (lane & 4) ? v2[1] : v2[0], give = (lane & 4) ? v2[0] : v2[1];
+                rowsum = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+            }
+            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
+            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
+            // lane holds row ((lane>>4)&1)*4 + ((lane>>3)&1)*2 + ((lane>>2)&1)
+        } else {
+            // 4 accumulators (row 2*ps + sub) over the 16 lanes of each half warp
+            float v2[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float keep = (lane & 8) ? acc[i + 2] : acc[i], give = (lane & 8) ? acc[i] : acc[i + 2];
+                v2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+            }
+            {
+                const float keep = (lane & 4) ? v2[1] : v2[0], give = (lane & 4) ? v2[0] : v2[1];
+                rowsum = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+            }
+            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
+            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
+            // lane holds pass ps = ((lane>>3)&1)*2 + ((lane>>2)&1), row 2*ps + sub
+        }
+        const int tslot = ti % a.n_tilebuf;
+        float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
+        if ((lane & 3) == 0) {
+            const int r = LPR == 32 ? (((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1))
+                                    : (2 * (((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)) + sub);
+            rslot[r] = rowsum;
+        }
+        __syncwarp();
+        const uint32_t tb = smem_u32(&tbar[tslot]);
+        if (lane == 0) mbar_arrive(tb);
+        if (slice == a.n_slices - 1) {
+            // this warp finishes the tile: wait for the other slices, add them in slice order
+            mbar_wait_bounded(tb, (uint32_t)(ti / a.n_tilebuf) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            const int row = tile * G1_ROWS + lane;
+            if (lane < G1_ROWS && row < a.M) {
+                const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
+                float v = 0.0f;
+                for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];
+                a.y[row] = a.accumulate ? a.y[row] + v : v;
+            }
+            __syncwarp();
+        }
+    }
+}
+
+}  // namespace q38b

@@ -8,6 +8,7 @@ struct q38b_ctx {
     int smem_optin = 0;
     int last_cuda = 0;
     int pdl = 1;
+    int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     int* d_status = nullptr;
     uint32_t* d_cb_iq3xxs = nullptr;
     uint32_t* d_cb_iq3s = nullptr;

@@ -143,3 +143,72 @@ extern "C" int emul_tile(int fmt, int K, const uint8_t* W, const uint8_t* xq, in
     pthread_barrier_destroy(&g_bar);
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Single-column path (q38b_decode1.cuh): the lanes run one after the other, there is no warp-collective step.
+// ---------------------------------------------------------------------------------------------------------------
+#include "../../qwengine_b200/csrc/q38b_decode1.cuh"
+
+namespace {
+template <int FMT>
+void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* actq, const float* actd, const Codebook* cbs, float* y) {
+    constexpr int LPR = Gran<FMT>::LANES_PER_ROW;
+    const int nsb = K / 256, n_slices = (nsb + 3) / 4;
+    for (int r = 0; r < n_rows; r++) {
+        float sum = 0;
+        for (int s = 0; s < n_slices; s++) {
+            float ssum = 0;
+            for (int lane = 0; lane < LPR; lane++) {
+                tl_lane = lane;
+                const int gran_sb = s * 4 + (LPR == 32 ? (lane >> 3) : (lane >> 2));
+                if (gran_sb >= nsb) continue;
+                typename Gran<FMT>::Acts acts;
+                Gran<FMT>::load_acts(acts, actq + s * 1024, actd + s * 32, lane);
+                ssum += Gran<FMT>::dot(rowp[r] + (size_t)s * 4 * Unit<FMT>::BLOCK_BYTES, acts, cbs[lane], lane);
+            }
+            sum += ssum;
+        }
+        y[r] = sum;
+    }
+}
+}  // namespace
+
+// W: n_rows packed rows; xq: Q8_K blocks of one column; y[n_rows].
+extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const uint8_t* xq, int addr_lo, int rep_log2, float* y) {
+    const int bb = block_bytes(fmt), nsb = K / 256, row_bytes = nsb * bb, n_slices = (nsb + 3) / 4;
+    if (!bb) return -1;
+    const int slot = (row_bytes + 64 + 15) / 16 * 16;
+    std::vector<uint8_t> stage((size_t)n_rows * slot + 64, 0x5A);
+    uint8_t* st = (uint8_t*)(((uintptr_t)stage.data() + 15) & ~(uintptr_t)15);
+    std::vector<const uint8_t*> rowp(n_rows);
+    for (int r = 0; r < n_rows; r++) {
+        uint8_t* p = st + (size_t)r * slot + ((addr_lo + r * row_bytes) & 15);
+        memcpy(p, W + (size_t)r * row_bytes, row_bytes);
+        rowp[r] = p;
+    }
+    std::vector<uint8_t> actq((size_t)n_slices * 1024 + 64, 0);
+    uint8_t* aq = (uint8_t*)(((uintptr_t)actq.data() + 15) & ~(uintptr_t)15);
+    std::vector<float> actd((size_t)n_slices * 32, 0.f);
+    for (int sb = 0; sb < nsb; sb++) {
+        const uint8_t* blk = xq + (size_t)sb * 292;
+        memcpy(&actd[sb * 8], blk, 4);
+        for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
+    }
+    const int entries = fmt == T_IQ3_XXS ? 256 : fmt == T_IQ3_S ? 512 : 0;
+    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) << rep_log2);
+    for (size_t i = 0; i < ((size_t)entries << rep_log2); i++)
+        cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> rep_log2] : q38b_iq3s_grid[i >> rep_log2];
+    Codebook cbs[32];
+    for (int l = 0; l < 32; l++) cbs[l] = Codebook{cb.data(), rep_log2, (uint32_t)l & ((1u << rep_log2) - 1u)};
+    switch (fmt) {
+        case T_Q8_0: run_slices<T_Q8_0>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q4_K: run_slices<T_Q4_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q5_K: run_slices<T_Q5_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q6_K: run_slices<T_Q6_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ3_XXS: run_slices<T_IQ3_XXS>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ3_S: run_slices<T_IQ3_S>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ4_XS: run_slices<T_IQ4_XS>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        default: return -1;
+    }
+    return 0;
+}

@@ -42,3 +42,22 @@ def test_tile_matches_oracle(emul, name, nb, addr_lo, rep_log2):
         ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[c], K)
         assert np.max(np.abs(y[:, c] - ref) / mag) < 1e-6
     assert not y[:, nb:].any()
+
+
+@pytest.mark.parametrize("name", list(F.FORMATS))
+@pytest.mark.parametrize("K,addr_lo,rep_log2", [(1024, 0, 5), (1280, 8, 3), (2048, 2, 0)])
+def test_single_column_granules_match_oracle(emul, name, K, addr_lo, rep_log2):
+    """The dp4a granule decoders of the nb = 1 kernel (q38b_decode1.cuh), lane by lane on the host."""
+    f = F.get(name)
+    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8}.get(name, 2):
+        addr_lo = 0
+    u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+    emul.emul_gemv1.argtypes = [C.c_int, C.c_int, u8p, C.c_int, u8p, C.c_int, C.c_int, f32p]
+    M = 6
+    w = synth.make_weights(f, M, K, seed=13, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    xq = oracle.port.quantize_q8k(synth.make_activations(1, K, seed=14))
+    y = np.zeros(M, np.float32)
+    assert emul.emul_gemv1(f.type_id, K, w.reshape(-1), M, xq.reshape(-1), addr_lo, rep_log2, y) == 0
+    ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[0], K)
+    assert np.max(np.abs(y - ref) / mag) < 1e-6
