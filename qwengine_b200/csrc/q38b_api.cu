@@ -122,7 +122,11 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     return Q38B_OK;
 }
 
-constexpr int G1_WARPS = 16;
+constexpr int G1_WARPS = 8;
+constexpr int G1_SMEM_BUDGET = 113 * 1024;   // two CTAs per SM (228 KB of shared memory per SM, 1 KB reserved per CTA)
+
+// rows per tile: 8 for the thin formats, 4 for the fat ones (keeps a stage near 16-24 KB)
+constexpr int g1_rows(int fmt) { return (fmt == T_Q5_K || fmt == T_Q6_K || fmt == T_Q8_0) ? 4 : 8; }
 
 struct Plan1 {
     Gemv1Args a;
@@ -136,7 +140,8 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
     const int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
-    const int budget = ctx->smem_optin - 128;
+    const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128;
+    const int G1_ROWS = g1_rows((int)type);
     Gemv1Args& a = p->a;
     a.nsb = nsb;
     a.n_slices = (nsb + 3) / 4;
@@ -147,7 +152,7 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
     const int packed = nsb * bb;
     // stage shape: 8 whole rows in one bulk copy when the rows are packed and small enough, else 8 per-row copies of a
     // K-chunk of `chunk_slices` slices (bulk copies are issue-rate limited: keep each above ~2 KB)
-    const int target = 24 * 1024;
+    const int target = 28 * 1024;
     if ((long long)row_bytes == packed && G1_ROWS * packed <= target) {
         a.contiguous = 1;
         a.chunk_slices = a.n_slices;
@@ -163,7 +168,7 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
         a.stage_bytes = align_up(G1_ROWS * a.slot_stride + 64, 128);
     }
     a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
-    const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 2;
+    const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 1;
     for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= 0; rep_log2 -= (rep_log2 == 5 ? 2 : 3)) {
         a.cb_rep_log2 = rep_log2;
         a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
@@ -176,7 +181,7 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
             a.n_stages = stages;
             a.n_tilebuf = tb;
             p->smem = a.off_stage + stages * a.stage_bytes + 128;
-            p->grid = std::max(1, std::min(ctx->sm_count, a.n_tiles));
+            p->grid = std::max(1, std::min(2 * ctx->sm_count, a.n_tiles));
             return Q38B_OK;
         }
         if (!cb_entries) break;
@@ -186,10 +191,11 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
 
 template <int FMT>
 int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    auto kern = gemv1_kernel<FMT, G1_WARPS>;
+    auto kern = gemv1_kernel<FMT, G1_WARPS, g1_rows(FMT)>;
     static int configured_device = -1;
     if (configured_device != ctx->device) {
-        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin));
+        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G1_SMEM_BUDGET));
+        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
         configured_device = ctx->device;
     }
     cudaLaunchConfig_t cfg;

@@ -42,9 +42,9 @@ Q38B_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t sh) {   // (hi:lo) 
 
 // 8 bytes from a 2-byte aligned address: three aligned words and two funnel shifts
 Q38B_HD void ld_8_a2(const uint8_t* p, uint32_t& lo, uint32_t& hi) {
-    const uintptr_t a = (uintptr_t)p;
-    const uint32_t* w = (const uint32_t*)(a & ~(uintptr_t)3);
-    const uint32_t sh = (uint32_t)(a & 2) * 8;
+    const uint32_t mis = (uint32_t)((uintptr_t)p & 2);
+    const uint32_t* w = (const uint32_t*)(p - mis);   // pointer minus integer: the address space stays known
+    const uint32_t sh = mis * 8;
     const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
     lo = funnel_r(w0, w1, sh);
     hi = funnel_r(w1, w2, sh);

@@ -49,8 +49,8 @@ struct GemvArgs {
 
 template <int FMT, int NGROUPS>
 __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kernel(const GemvArgs a) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
+    uint8_t* smem = smem_raw;
     uint64_t* bars = (uint64_t*)smem;                       // full[NGROUPS][MAX_STAGES], empty[NGROUPS][MAX_STAGES]
     volatile int* abort_flag = (volatile int*)(smem + 8 * 2 * NGROUPS * MAX_STAGES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

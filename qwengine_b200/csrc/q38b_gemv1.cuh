@@ -13,7 +13,6 @@
 
 namespace q38b {
 
-constexpr int G1_ROWS = 8;           // rows per stage / tile
 constexpr int G1_MAX_STAGES = 64;
 constexpr int G1_MAX_TILEBUF = 64;
 
@@ -39,10 +38,13 @@ struct Gemv1Args {
     int off_actd, off_actq, off_cb, off_red, off_stage;
 };
 
-template <int FMT, int NWARPS>
-__global__ void __launch_bounds__(32 * (1 + NWARPS), 1) gemv1_kernel(const Gemv1Args a) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+// ROWS = rows per tile and stage (8 for the thin formats, 4 for the fat ones); two CTAs share an SM so that the
+// prologue of one (or of the next kernel of the stream) overlaps the streaming of the other.
+template <int FMT, int NWARPS, int ROWS>
+__global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1Args a) {
+    constexpr int G1_ROWS = ROWS;
+    extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
+    uint8_t* smem = smem_raw;
     uint64_t* full = (uint64_t*)smem;                        // [G1_MAX_STAGES]
     uint64_t* empty = full + G1_MAX_STAGES;                  // [G1_MAX_STAGES]
     uint64_t* tbar = empty + G1_MAX_STAGES;                  // [G1_MAX_TILEBUF]
@@ -190,51 +192,41 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 1) gemv1_kernel(const Gemv1
             mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
         }
 
-        // sum over the lanes of each row: halving butterfly, then plain butterflies
-        float rowsum;   // lanes with the same (lane & mask) end up with the sum of one row
-        if (LPR == 32) {
-            // 8 accumulators (rows 0..7) over 32 lanes
-            float v4[4], v2[2];
+        // sum over the lanes of each row: halving butterflies (each step halves the values a lane holds), then plain ones
+        float rowsum;
+        int myrow = 0;      // the row whose sum this lane ends up with
+        {
+            float v[PASSES];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float keep = (lane & 16) ? acc[i + 4] : acc[i], give = (lane & 16) ? acc[i] : acc[i + 4];
-                v4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
-            }
+            for (int i = 0; i < PASSES; i++) v[i] = acc[i];
+            constexpr int TOP = LPR == 32 ? 16 : 8;    // highest lane bit inside one row's lane set
+            int n = PASSES, bit = TOP;
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const float keep = (lane & 8) ? v4[i + 2] : v4[i], give = (lane & 8) ? v4[i] : v4[i + 2];
-                v2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-            }
-            {
-                const float keep = (lane & 4) ? v2[1] : v2[0], give = (lane & 4) ? v2[0] : v2[1];
-                rowsum = keep + __shfl_xor_sync(0xffffffffu, give, 4);
-            }
-            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
-            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
-            // lane holds row ((lane>>4)&1)*4 + ((lane>>3)&1)*2 + ((lane>>2)&1)
-        } else {
-            // 4 accumulators (row 2*ps + sub) over the 16 lanes of each half warp
-            float v2[2];
+            for (int step = 0; step < 3; step++) {
+                if (n > 1) {
+                    const int h = n >> 1;
+                    const bool up = (lane & bit) != 0;
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const float keep = (lane & 8) ? acc[i + 2] : acc[i], give = (lane & 8) ? acc[i] : acc[i + 2];
-                v2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+                    for (int i = 0; i < 4; i++) {
+                        if (i < h) {
+                            const float keep = up ? v[i + h] : v[i], give = up ? v[i] : v[i + h];
+                            v[i] = keep + __shfl_xor_sync(0xffffffffu, give, bit);
+                        }
+                    }
+                    if (up) myrow += h;
+                    n = h;
+                    bit >>= 1;
+                }
             }
-            {
-                const float keep = (lane & 4) ? v2[1] : v2[0], give = (lane & 4) ? v2[0] : v2[1];
-                rowsum = keep + __shfl_xor_sync(0xffffffffu, give, 4);
-            }
-            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 2);
-            rowsum += __shfl_xor_sync(0xffffffffu, rowsum, 1);
-            // lane holds pass ps = ((lane>>3)&1)*2 + ((lane>>2)&1), row 2*ps + sub
+            rowsum = v[0];
+            for (; bit > 0; bit >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, bit);
+            if (LPR == 16) myrow = 2 * myrow + sub;
         }
         const int tslot = ti % a.n_tilebuf;
         float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
-        if ((lane & 3) == 0) {
-            const int r = LPR == 32 ? (((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1))
-                                    : (2 * (((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)) + sub);
-            rslot[r] = rowsum;
-        }
+        // one lane per row writes: the lanes whose low bits (those folded by the plain butterflies) are zero
+        constexpr int LOW_MASK = (LPR == 32 ? 32 : 16) / PASSES - 1;
+        if ((lane & LOW_MASK) == 0) rslot[myrow] = rowsum;
         __syncwarp();
         const uint32_t tb = smem_u32(&tbar[tslot]);
         if (lane == 0) mbar_arrive(tb);
