@@ -201,6 +201,16 @@ def run_ours(args):
         host_id = bytes(idbuf.cpu().tolist())
         ctx._rc(ctx.lib.q38b_comm_init(ctx.h, world, rank, host_id), "q38b_comm_init")
 
+    def exchange(handle):
+        """All ranks' 64-byte IPC handles, in rank order."""
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+        out = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(out, mine)
+        return [bytes(t.cpu().tolist()) for t in out]
+
+    if world > 1 and args.gather == "peer":
+        ctx.peer_connect(world, rank, exchange(ctx.peer_flags_handle()))
+
     n_layers = args.layers
     ps = q.Pass(ctx, max_nb=7)
     counter = [0]
@@ -210,7 +220,7 @@ def run_ours(args):
         w = device_weights(torch, spec, rows, seed=1000 * counter[0] + rank, scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
         return ps.matrix_device(spec.fmt, w, spec.K)
 
-    io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world)
+    io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world, gather=args.gather, exchange=exchange)
     local_bytes = ps.weight_bytes
     total_bytes = dp.total_weight_bytes(n_layers, True)
     xin = ps.buffer_tensor(io["in_buf"])
@@ -300,7 +310,7 @@ def run_ours(args):
             "ms_per_step": round(ms1, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8", "data": "synthetic",
             "config": {"workload": "decode_weight_pass_27b_shape", "layers": n_layers, "matrices": len(dp.all_specs(n_layers)),
-                       "weight_bytes": total_bytes, "nb": 1, "parallelism": f"row-shard x{world} + all-gather",
+                       "weight_bytes": total_bytes, "nb": 1, "parallelism": f"row-shard x{world}" + (f" + {args.gather} gather" if world > 1 else ""),
                        "cache": "12.5 GB of weights per pass, far larger than L2; no flush needed", "outputs_finite": finite},
             "tokens_per_s": round(1e3 / ms1, 1),
             "frac_of_nominal_8TBps": round(value / world / HBM_NOMINAL_GBS, 4),
@@ -328,6 +338,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=64, help="number of layers of the pass (64 = the benchmark configuration)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="multi-GPU output exchange: fused peer stores or NCCL")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -77,6 +77,13 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x_dev, long long x_ld, int K, 
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* q8k_dev,
                   long long q8k_stride, int nb, float* y_dev, long long y_ld, int accumulate, void* stream);
 
+/* The same matvec with a fused all-gather for row-sharded matrices: every result is also stored at the same position
+ * of n_peers (0..7) output buffers that live on other GPUs (peer-mapped pointers, see q38b_peer_*), so that after
+ * q38b_peer_barrier every GPU holds the outputs of all shards.  No counterpart in the reference (single GPU). */
+int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M,
+                          const void* q8k_dev, long long q8k_stride, int nb, float* y_dev, long long y_ld, int accumulate,
+                          float* const* y_peers, int n_peers, void* stream);
+
 /* Replaces swiglu_rows + the requantisation for the down projection (src/cuda/ops.cu:126-141, 946-949; CPU:
  * src/runtime/engine.cpp:177-182, 1646): h = silu(g) * u for n_rows rows of n (row stride ld floats), written as
  * fp32 to h_dev (may be NULL) and as Q8_K blocks to q8k_dev (may be NULL). n must be a multiple of 256. */
@@ -102,6 +109,17 @@ typedef struct q38b_pass q38b_pass;
 int q38b_comm_unique_id(void* id128);
 int q38b_comm_init(q38b_ctx* ctx, int n_ranks, int rank, const void* id128);
 
+/* Peer-store gather (low-latency alternative to the NCCL all-gather; no counterpart in the single-GPU reference).
+ * Device memory of one process is made visible to the others with CUDA IPC handles (64 bytes each, exchanged by the
+ * caller, e.g. over torch.distributed).  q38b_peer_flags_handle creates and exports this rank's flag words;
+ * q38b_peer_connect takes the n_ranks handles of all ranks (64 * n_ranks bytes, rank order);
+ * q38b_peer_barrier enqueues a one-warp kernel that signals every peer and waits (bounded) for all of them. */
+int q38b_peer_export(q38b_ctx* ctx, const void* dev_ptr, void* handle64);
+int q38b_peer_import(q38b_ctx* ctx, const void* handle64, void** dev_ptr);
+int q38b_peer_flags_handle(q38b_ctx* ctx, void* handle64);
+int q38b_peer_connect(q38b_ctx* ctx, int n_ranks, int rank, const void* handles);
+int q38b_peer_barrier(q38b_ctx* ctx, void* stream);
+
 int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out);
 void q38b_pass_destroy(q38b_pass* pass);
 /* Activation buffers owned by the pass; both return a buffer id >= 0 or a negative q38b_status. */
@@ -118,6 +136,12 @@ int q38b_pass_matrix_device(q38b_pass* pass, uint32_t type, const void* W_dev, s
 int q38b_pass_op_quantize(q38b_pass* pass, int src_f32, int src_off, int K, int dst_q8k);
 int q38b_pass_op_gemv(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
 int q38b_pass_op_swiglu(q38b_pass* pass, int g_f32, int g_off, int u_f32, int u_off, int n, int dst_q8k);
+/* Peer-store gather: export a buffer / connect it to the same buffer of all ranks (64 * n_ranks handle bytes, rank
+ * order).  Matvec steps whose destination buffer is connected push their outputs to every peer; q38b_pass_op_barrier
+ * then makes them usable on all ranks.  One barrier may cover several matvecs. */
+int q38b_pass_buffer_handle(q38b_pass* pass, int buffer, void* handle64);
+int q38b_pass_buffer_connect(q38b_pass* pass, int buffer, int n_ranks, const void* handles);
+int q38b_pass_op_barrier(q38b_pass* pass);
 /* In-place all-gather over the ranks: rank g holds [off + g*count, off + (g+1)*count) of every column. */
 int q38b_pass_op_allgather(q38b_pass* pass, int buf_f32, int off, int count_per_rank);
 /* Runs the recorded steps for nb columns (1..max_nb) on `stream`; the first run for each nb captures the graph. */

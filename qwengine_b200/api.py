@@ -58,6 +58,12 @@ def load_library():
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
+    lib.q38b_peer_flags_handle.argtypes = [vp, vp]
+    lib.q38b_peer_connect.argtypes = [vp, i32, i32, vp]
+    lib.q38b_peer_barrier.argtypes = [vp, vp]
+    lib.q38b_pass_buffer_handle.argtypes = [vp, i32, vp]
+    lib.q38b_pass_buffer_connect.argtypes = [vp, i32, i32, vp]
+    lib.q38b_pass_op_barrier.argtypes = [vp]
     lib.q38b_pass_create.argtypes = [vp, i32, C.POINTER(vp)]
     lib.q38b_pass_destroy.argtypes = [vp]
     lib.q38b_pass_destroy.restype = None
@@ -122,6 +128,14 @@ class Context:
     def check(self):
         """Synchronises the current stream and raises if a kernel reported a bounded wait that ran out."""
         self._rc(self.lib.q38b_ctx_check(self.h, _stream()), "q38b_ctx_check")
+
+    def peer_flags_handle(self):
+        raw = (C.c_ubyte * 64)()
+        self._rc(self.lib.q38b_peer_flags_handle(self.h, raw), "q38b_peer_flags_handle")
+        return bytes(raw)
+
+    def peer_connect(self, n_ranks, rank, handles):
+        self._rc(self.lib.q38b_peer_connect(self.h, n_ranks, rank, b"".join(handles)), "q38b_peer_connect")
 
     def set_uniform_columns(self, enabled):
         self._rc(self.lib.q38b_ctx_set_uniform_columns(self.h, int(bool(enabled))), "q38b_ctx_set_uniform_columns")
@@ -239,6 +253,20 @@ class Pass:
 
     def swiglu(self, g, g_off, u, u_off, n, dst_q):
         self.ctx._rc(self.lib.q38b_pass_op_swiglu(self.h, g, g_off, u, u_off, n, dst_q), "q38b_pass_op_swiglu")
+
+    def buffer_handle(self, buf):
+        """64-byte CUDA IPC handle of a buffer of the pass (bytes)."""
+        raw = (C.c_ubyte * 64)()
+        self.ctx._rc(self.lib.q38b_pass_buffer_handle(self.h, buf, raw), "q38b_pass_buffer_handle")
+        return bytes(raw)
+
+    def buffer_connect(self, buf, handles):
+        """handles: list of the 64-byte handles of this buffer on every rank, in rank order."""
+        blob = b"".join(handles)
+        self.ctx._rc(self.lib.q38b_pass_buffer_connect(self.h, buf, len(handles), blob), "q38b_pass_buffer_connect")
+
+    def barrier(self):
+        self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")
 
     def allgather(self, buf, off, count):
         self.ctx._rc(self.lib.q38b_pass_op_allgather(self.h, buf, off, count), "q38b_pass_op_allgather")

@@ -269,6 +269,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
 void q38b_ctx_destroy(q38b_ctx* ctx) {
     if (!ctx) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_flags) cudaFree(ctx->d_flags);
     delete ctx;
 }
 
@@ -345,7 +346,15 @@ int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g, const float* u, long long ld,
 
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* q8k,
                   long long q8k_stride, int nb, float* y, long long y_ld, int accumulate, void* stream) {
+    return q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, K, M, q8k, q8k_stride, nb, y, y_ld, accumulate, nullptr, 0, stream);
+}
+
+int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* q8k,
+                          long long q8k_stride, int nb, float* y, long long y_ld, int accumulate, float* const* y_peers,
+                          int n_peers, void* stream) {
     if (!ctx || !W || !q8k || !y) return Q38B_ERR_ARG;
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return Q38B_ERR_ARG;
+    for (int i = 0; i < n_peers; i++) if (!y_peers[i] || ((uintptr_t)y_peers[i] & 3)) return Q38B_ERR_ARG;
     if (!known_format(type)) return Q38B_ERR_UNSUPPORTED;
     if (K <= 0 || K % 256 || M < 1 || nb < 1 || nb > 8 || y_ld < M || q8k_stride < K / 256) return Q38B_ERR_ARG;
     if (row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
@@ -363,6 +372,8 @@ int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes,
             g.row_bytes = (long long)row_bytes;
             g.xq = (const uint8_t*)q8k;
             g.y = y;
+            g.n_peers = n_peers;
+            for (int i = 0; i < n_peers; i++) g.y_peer[i] = y_peers[i];
             g.status = ctx->d_status;
             g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
             g.K = K;
@@ -391,6 +402,8 @@ int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes,
     a.x_stride = q8k_stride;
     a.y = y;
     a.y_ld = y_ld;
+    a.n_peers = n_peers;
+    for (int i = 0; i < n_peers; i++) a.y_peer[i] = y_peers[i];
     a.status = ctx->d_status;
     a.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
     a.K = K;

@@ -32,6 +32,8 @@ struct GemvArgs {
     long long x_stride;      // blocks between columns
     float* y;                // y[c * y_ld + r]
     long long y_ld;
+    float* y_peer[7];        // the same output position in the other GPUs' buffers (peer stores), n_peers used
+    int n_peers;
     int* status;             // device status word (OR of ST_* bits)
     const uint32_t* codebook;   // device copy of the format's codebook (or nullptr)
     int K, M, nb, accumulate;
@@ -211,7 +213,9 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             const int col = 2 * (ls & 3) + (i & 1);
             if (row < a.M && col < a.nb) {
                 float* yo = a.y + (size_t)col * a.y_ld + row;
-                *yo = a.accumulate ? *yo + v : v;
+                const float out = a.accumulate ? *yo + v : v;
+                *yo = out;
+                for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][(size_t)col * a.y_ld + row] = out;
             }
         }
     }

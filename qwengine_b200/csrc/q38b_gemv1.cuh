@@ -21,6 +21,8 @@ struct Gemv1Args {
     long long row_bytes;
     const uint8_t* xq;      // Q8_K blocks of the single column
     float* y;
+    float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
+    int n_peers;
     int* status;
     const uint32_t* codebook;
     int K, M, accumulate;
@@ -238,7 +240,9 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                 const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
                 float v = 0.0f;
                 for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];
-                a.y[row] = a.accumulate ? a.y[row] + v : v;
+                const float out = a.accumulate ? a.y[row] + v : v;
+                a.y[row] = out;
+                for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][row] = out;   // fused all-gather: push to every peer
             }
             __syncwarp();
         }

@@ -14,4 +14,8 @@ struct q38b_ctx {
     uint32_t* d_cb_iq3s = nullptr;
     void* comm = nullptr;   // ncclComm_t when q38b_comm_init was called
     int n_ranks = 1, rank = 0;
+    // peer-store gather: flags[0..7] written by the peers, [8] = this rank's barrier count
+    uint32_t* d_flags = nullptr;
+    uint32_t* peer_flags[8] = {};
+    int peers_connected = 0;
 };

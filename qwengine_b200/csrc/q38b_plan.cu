@@ -46,10 +46,34 @@ Nccl& nccl() {
 }
 constexpr int NCCL_FLOAT = 7;
 
-enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER };
+enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER, OP_BARRIER };
 struct Op { int kind, a, b, c, d, n, off; };
-struct Buf { void* ptr; int n; bool q8k; };
+struct Buf { void* ptr; int n; bool q8k; void* peer[8]; int n_peer_ranks; };
 struct Mat { uint32_t type; const void* W; size_t row_bytes; int K, M; bool owned; };
+
+struct PeerPtrs { uint32_t* p[8]; };
+constexpr int ST_PEER_TIMEOUT = 16;
+
+// Cross-GPU barrier of the peer-store gather.  Runs after the matvecs whose outputs were pushed to the peers: the
+// kernel boundary plus the system fence make those stores visible before the flag.  Lane g signals GPU g with this
+// rank's barrier count and waits (bounded, ~2 s of SM clocks) until GPU g's count has reached it.
+__global__ void peer_barrier_kernel(uint32_t* local, PeerPtrs peers, int n, int rank, int* status) {
+    const int lane = threadIdx.x;
+    uint32_t e = 0;
+    if (lane == 0) { e = local[8] + 1u; local[8] = e; }
+    e = __shfl_sync(0xffffffffu, e, 0);
+    if (lane < n && lane != rank) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.p[lane] + rank), "r"(e) : "memory");
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local + lane) : "memory");
+            if ((int)(v - e) >= 0) break;
+            if (clock64() - t0 > 4000000000LL) { atomicOr(status, ST_PEER_TIMEOUT); break; }
+        }
+    }
+}
 
 }  // namespace
 
@@ -94,7 +118,12 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
                 const Mat& m = p->mats[o.a];
                 const Buf& s = p->bufs[o.b];
                 const Buf& d = p->bufs[o.c];
-                rc = q38b_gemv_q8k(ctx, m.type, m.W, m.row_bytes, m.K, m.M, s.ptr, s.n / 256, nb, (float*)d.ptr + o.off, d.n, 0, st);
+                float* peers[7];
+                int np = 0;
+                for (int r = 0; r < d.n_peer_ranks; r++)
+                    if (r != ctx->rank && d.peer[r]) peers[np++] = (float*)d.peer[r] + o.off;
+                rc = q38b_gemv_q8k_scatter(ctx, m.type, m.W, m.row_bytes, m.K, m.M, s.ptr, s.n / 256, nb, (float*)d.ptr + o.off, d.n, 0,
+                                           peers, np, st);
                 break;
             }
             case OP_SWIGLU: {
@@ -106,6 +135,9 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
                                      d.n / 256, st);
                 break;
             }
+            case OP_BARRIER:
+                rc = q38b_peer_barrier(ctx, st);
+                break;
             case OP_GATHER: {
                 if (ctx->n_ranks <= 1) break;
                 Nccl& n = nccl();
@@ -153,6 +185,87 @@ int q38b_comm_init(q38b_ctx* ctx, int n_ranks, int rank, const void* id128) {
     return Q38B_OK;
 }
 
+int q38b_peer_export(q38b_ctx* ctx, const void* dev_ptr, void* handle64) {
+    if (!ctx || !dev_ptr || !handle64) return Q38B_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    cudaError_t e = cudaIpcGetMemHandle(&h, (void*)dev_ptr);
+    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    memcpy(handle64, &h, 64);
+    return Q38B_OK;
+}
+
+int q38b_peer_import(q38b_ctx* ctx, const void* handle64, void** dev_ptr) {
+    if (!ctx || !handle64 || !dev_ptr) return Q38B_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    return Q38B_OK;
+}
+
+int q38b_peer_flags_handle(q38b_ctx* ctx, void* handle64) {
+    if (!ctx || !handle64) return Q38B_ERR_ARG;
+    if (!ctx->d_flags) {
+        cudaError_t e = cudaMalloc(&ctx->d_flags, 16 * sizeof(uint32_t));
+        if (e == cudaSuccess) e = cudaMemset(ctx->d_flags, 0, 16 * sizeof(uint32_t));
+        if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    }
+    return q38b_peer_export(ctx, ctx->d_flags, handle64);
+}
+
+int q38b_peer_connect(q38b_ctx* ctx, int n_ranks, int rank, const void* handles) {
+    if (!ctx || !handles || n_ranks < 2 || n_ranks > 8 || rank < 0 || rank >= n_ranks || !ctx->d_flags) return Q38B_ERR_ARG;
+    for (int r = 0; r < n_ranks; r++) {
+        if (r == rank) { ctx->peer_flags[r] = ctx->d_flags; continue; }
+        void* ptr = nullptr;
+        const int rc = q38b_peer_import(ctx, (const char*)handles + 64 * r, &ptr);
+        if (rc != Q38B_OK) return rc;
+        ctx->peer_flags[r] = (uint32_t*)ptr;
+    }
+    ctx->n_ranks = n_ranks;
+    ctx->rank = rank;
+    ctx->peers_connected = 1;
+    return Q38B_OK;
+}
+
+int q38b_peer_barrier(q38b_ctx* ctx, void* stream) {
+    if (!ctx) return Q38B_ERR_ARG;
+    if (ctx->n_ranks <= 1) return Q38B_OK;
+    if (!ctx->peers_connected) return Q38B_ERR_ARG;
+    PeerPtrs pp;
+    for (int r = 0; r < 8; r++) pp.p[r] = ctx->peer_flags[r];
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->d_flags, pp, ctx->n_ranks, ctx->rank, ctx->d_status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    return Q38B_OK;
+}
+
+int q38b_pass_buffer_handle(q38b_pass* p, int buf, void* handle64) {
+    if (!p || buf < 0 || buf >= (int)p->bufs.size()) return Q38B_ERR_ARG;
+    return q38b_peer_export(p->ctx, p->bufs[buf].ptr, handle64);
+}
+
+int q38b_pass_buffer_connect(q38b_pass* p, int buf, int n_ranks, const void* handles) {
+    if (!p || buf < 0 || buf >= (int)p->bufs.size() || !handles || n_ranks < 2 || n_ranks > 8) return Q38B_ERR_ARG;
+    Buf& b = p->bufs[buf];
+    for (int r = 0; r < n_ranks; r++) {
+        if (r == p->ctx->rank) { b.peer[r] = b.ptr; continue; }
+        void* ptr = nullptr;
+        const int rc = q38b_peer_import(p->ctx, (const char*)handles + 64 * r, &ptr);
+        if (rc != Q38B_OK) return rc;
+        b.peer[r] = ptr;
+    }
+    b.n_peer_ranks = n_ranks;
+    return Q38B_OK;
+}
+
+int q38b_pass_op_barrier(q38b_pass* p) {
+    if (!p) return Q38B_ERR_ARG;
+    p->ops.push_back({OP_BARRIER, 0, 0, 0, 0, 0, 0});
+    return Q38B_OK;
+}
+
 int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out) {
     if (!ctx || !out || max_nb < 1 || max_nb > 8) return Q38B_ERR_ARG;
     q38b_pass* p = new (std::nothrow) q38b_pass;
@@ -179,7 +292,7 @@ int q38b_pass_buffer_f32(q38b_pass* p, int n) {
     void* ptr = nullptr;
     PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * n * sizeof(float)));
     PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * n * sizeof(float)));
-    p->bufs.push_back({ptr, n, false});
+    p->bufs.push_back({ptr, n, false, {}, 0});
     return (int)p->bufs.size() - 1;
 }
 
@@ -188,7 +301,7 @@ int q38b_pass_buffer_q8k(q38b_pass* p, int K) {
     void* ptr = nullptr;
     PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * (K / 256) * 292));
     PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * (K / 256) * 292));
-    p->bufs.push_back({ptr, K, true});
+    p->bufs.push_back({ptr, K, true, {}, 0});
     return (int)p->bufs.size() - 1;
 }
 
@@ -307,7 +420,7 @@ long long q38b_pass_weight_bytes(const q38b_pass* p) {
 int q38b_pass_kernel_count(const q38b_pass* p) {
     if (!p) return 0;
     int n = 0;
-    for (const Op& o : p->ops) n += o.kind != OP_GATHER;
+    for (const Op& o : p->ops) n += (o.kind != OP_GATHER) && (o.kind != OP_BARRIER || p->ctx->n_ranks > 1);
     return n;
 }
 

@@ -61,10 +61,13 @@ def total_weight_bytes(n_layers=N_LAYERS, head=True):
     return sum(m.nbytes for m in all_specs(n_layers, head))
 
 
-def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1):
+def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather="peer", exchange=None):
     """Records the pass on `ps` (qwengine_b200.Pass).
 
     make_matrix(spec, rows) -> matrix id for this rank's shard of `rows` rows (rows = spec.M // world).
+    world > 1: gather = "peer" pushes every output slice into the peers' buffers from the matvec kernel and
+    synchronises with one cross-GPU barrier per group of matvecs (exchange(handle_bytes) -> list of all ranks' handles
+    is needed to connect the buffers); gather = "nccl" records an NCCL all-gather after every matvec.
     Returns dict(in_buf, out_buf, out_len).
     """
     x = ps.buffer_f32(HIDDEN)              # residual-stream stand-in: input of every layer
@@ -75,13 +78,21 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1):
     gu = ps.buffer_f32(2 * FF)             # gate | up
     hq = ps.buffer_q8k(FF)
     logits = ps.buffer_f32(VOCAB) if head else None
+    peer = world > 1 and gather == "peer"
+    if peer:
+        for b in [x, big, kv, gu] + ([logits] if head else []):
+            ps.buffer_connect(b, exchange(ps.buffer_handle(b)))
 
     def matvec(spec, src_q, dst, off):
         rows = spec.M // world
         mid = make_matrix(spec, rows)
         ps.gemv(mid, src_q, dst, off + rank * rows)
-        if world > 1:
+        if world > 1 and not peer:
             ps.allgather(dst, off, rows)
+
+    def sync():
+        if peer:
+            ps.barrier()
 
     for il in range(n_layers):
         attn, mats = layer_specs(il)
@@ -94,17 +105,22 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1):
         else:
             matvec(mats[0], xq, big, 0)
             proj_out = mats[1]
+        sync()
         ps.quantize(big, 0, INNER, iq)
         matvec(proj_out, iq, x, 0)
+        sync()
         ps.quantize(x, 0, HIDDEN, xq)
         gate, up, down = mats[-3:]
         matvec(gate, xq, gu, 0)
         matvec(up, xq, gu, FF)
+        sync()
         ps.swiglu(gu, 0, gu, FF, FF, hq)
         matvec(down, hq, x, 0)
+        sync()
     if head:
         ps.quantize(x, 0, HIDDEN, xq)
         matvec(MatSpec("lm_head", "Q6_K", VOCAB, HIDDEN), xq, logits, 0)
+        sync()
     return dict(in_buf=x, out_buf=logits if head else x, out_len=VOCAB if head else HIDDEN)
 
 
