@@ -209,7 +209,7 @@ def run_ours(args):
         return [bytes(t.cpu().tolist()) for t in out]
 
     if world > 1 and args.gather == "peer":
-        ctx.peer_connect(world, rank, exchange(ctx.peer_flags_handle()))
+        ctx.peer_connect(world, rank, exchange(ctx.peer_arena_create()))
 
     n_layers = args.layers
     ps = q.Pass(ctx, max_nb=7)
@@ -220,7 +220,7 @@ def run_ours(args):
         w = device_weights(torch, spec, rows, seed=1000 * counter[0] + rank, scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
         return ps.matrix_device(spec.fmt, w, spec.K)
 
-    io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world, gather=args.gather, exchange=exchange)
+    io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world, gather=args.gather)
     local_bytes = ps.weight_bytes
     total_bytes = dp.total_weight_bytes(n_layers, True)
     xin = ps.buffer_tensor(io["in_buf"])

@@ -111,12 +111,13 @@ int q38b_comm_init(q38b_ctx* ctx, int n_ranks, int rank, const void* id128);
 
 /* Peer-store gather (low-latency alternative to the NCCL all-gather; no counterpart in the single-GPU reference).
  * Device memory of one process is made visible to the others with CUDA IPC handles (64 bytes each, exchanged by the
- * caller, e.g. over torch.distributed).  q38b_peer_flags_handle creates and exports this rank's flag words;
- * q38b_peer_connect takes the n_ranks handles of all ranks (64 * n_ranks bytes, rank order);
+ * caller, e.g. over torch.distributed).  q38b_peer_arena_create allocates this rank's arena (flag words plus room for
+ * the fp32 buffers of passes created afterwards: every rank must create the same buffers in the same order) and
+ * exports it; q38b_peer_connect takes the handles of all ranks (64 * n_ranks bytes, rank order);
  * q38b_peer_barrier enqueues a one-warp kernel that signals every peer and waits (bounded) for all of them. */
 int q38b_peer_export(q38b_ctx* ctx, const void* dev_ptr, void* handle64);
 int q38b_peer_import(q38b_ctx* ctx, const void* handle64, void** dev_ptr);
-int q38b_peer_flags_handle(q38b_ctx* ctx, void* handle64);
+int q38b_peer_arena_create(q38b_ctx* ctx, size_t bytes, void* handle64);
 int q38b_peer_connect(q38b_ctx* ctx, int n_ranks, int rank, const void* handles);
 int q38b_peer_barrier(q38b_ctx* ctx, void* stream);
 
@@ -136,12 +137,11 @@ int q38b_pass_matrix_device(q38b_pass* pass, uint32_t type, const void* W_dev, s
 int q38b_pass_op_quantize(q38b_pass* pass, int src_f32, int src_off, int K, int dst_q8k);
 int q38b_pass_op_gemv(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
 int q38b_pass_op_swiglu(q38b_pass* pass, int g_f32, int g_off, int u_f32, int u_off, int n, int dst_q8k);
-/* Peer-store gather: export a buffer / connect it to the same buffer of all ranks (64 * n_ranks handle bytes, rank
- * order).  Matvec steps whose destination buffer is connected push their outputs to every peer; q38b_pass_op_barrier
- * then makes them usable on all ranks.  One barrier may cover several matvecs. */
-int q38b_pass_buffer_handle(q38b_pass* pass, int buffer, void* handle64);
-int q38b_pass_buffer_connect(q38b_pass* pass, int buffer, int n_ranks, const void* handles);
+/* After q38b_peer_connect the fp32 buffers of a pass live in the arena and matvec steps push their outputs to every
+ * peer; q38b_pass_op_barrier then makes them usable on all ranks.  One barrier may cover several matvecs. */
 int q38b_pass_op_barrier(q38b_pass* pass);
+/* 0: matvec steps of this pass keep their outputs local even when the context is peer-connected (default 1). */
+int q38b_pass_set_peer_store(q38b_pass* pass, int enabled);
 /* In-place all-gather over the ranks: rank g holds [off + g*count, off + (g+1)*count) of every column. */
 int q38b_pass_op_allgather(q38b_pass* pass, int buf_f32, int off, int count_per_rank);
 /* Runs the recorded steps for nb columns (1..max_nb) on `stream`; the first run for each nb captures the graph. */

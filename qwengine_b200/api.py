@@ -58,12 +58,11 @@ def load_library():
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
-    lib.q38b_peer_flags_handle.argtypes = [vp, vp]
+    lib.q38b_peer_arena_create.argtypes = [vp, sz, vp]
     lib.q38b_peer_connect.argtypes = [vp, i32, i32, vp]
     lib.q38b_peer_barrier.argtypes = [vp, vp]
-    lib.q38b_pass_buffer_handle.argtypes = [vp, i32, vp]
-    lib.q38b_pass_buffer_connect.argtypes = [vp, i32, i32, vp]
     lib.q38b_pass_op_barrier.argtypes = [vp]
+    lib.q38b_pass_set_peer_store.argtypes = [vp, i32]
     lib.q38b_pass_create.argtypes = [vp, i32, C.POINTER(vp)]
     lib.q38b_pass_destroy.argtypes = [vp]
     lib.q38b_pass_destroy.restype = None
@@ -129,9 +128,10 @@ class Context:
         """Synchronises the current stream and raises if a kernel reported a bounded wait that ran out."""
         self._rc(self.lib.q38b_ctx_check(self.h, _stream()), "q38b_ctx_check")
 
-    def peer_flags_handle(self):
+    def peer_arena_create(self, nbytes=256 << 20):
+        """Allocates this rank's peer-visible arena; returns its 64-byte CUDA IPC handle."""
         raw = (C.c_ubyte * 64)()
-        self._rc(self.lib.q38b_peer_flags_handle(self.h, raw), "q38b_peer_flags_handle")
+        self._rc(self.lib.q38b_peer_arena_create(self.h, nbytes, raw), "q38b_peer_arena_create")
         return bytes(raw)
 
     def peer_connect(self, n_ranks, rank, handles):
@@ -254,16 +254,8 @@ class Pass:
     def swiglu(self, g, g_off, u, u_off, n, dst_q):
         self.ctx._rc(self.lib.q38b_pass_op_swiglu(self.h, g, g_off, u, u_off, n, dst_q), "q38b_pass_op_swiglu")
 
-    def buffer_handle(self, buf):
-        """64-byte CUDA IPC handle of a buffer of the pass (bytes)."""
-        raw = (C.c_ubyte * 64)()
-        self.ctx._rc(self.lib.q38b_pass_buffer_handle(self.h, buf, raw), "q38b_pass_buffer_handle")
-        return bytes(raw)
-
-    def buffer_connect(self, buf, handles):
-        """handles: list of the 64-byte handles of this buffer on every rank, in rank order."""
-        blob = b"".join(handles)
-        self.ctx._rc(self.lib.q38b_pass_buffer_connect(self.h, buf, len(handles), blob), "q38b_pass_buffer_connect")
+    def set_peer_store(self, enabled):
+        self.ctx._rc(self.lib.q38b_pass_set_peer_store(self.h, int(bool(enabled))), "q38b_pass_set_peer_store")
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -15,7 +15,10 @@ struct q38b_ctx {
     void* comm = nullptr;   // ncclComm_t when q38b_comm_init was called
     int n_ranks = 1, rank = 0;
     // peer-store gather: flags[0..7] written by the peers, [8] = this rank's barrier count
-    uint32_t* d_flags = nullptr;
-    uint32_t* peer_flags[8] = {};
+    // One arena per rank holds the flags (first 256 bytes) and every peer-visible activation buffer, so that a single
+    // IPC handle per rank is exchanged and a buffer sits at the same offset on every rank.
+    uint32_t* d_flags = nullptr;      // = arena base
+    uint32_t* peer_flags[8] = {};     // arena bases of all ranks
+    size_t arena_bytes = 0, arena_used = 0;
     int peers_connected = 0;
 };

@@ -48,7 +48,7 @@ constexpr int NCCL_FLOAT = 7;
 
 enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER, OP_BARRIER };
 struct Op { int kind, a, b, c, d, n, off; };
-struct Buf { void* ptr; int n; bool q8k; void* peer[8]; int n_peer_ranks; };
+struct Buf { void* ptr; int n; bool q8k; void* peer[8]; int n_peer_ranks; bool in_arena; };
 struct Mat { uint32_t type; const void* W; size_t row_bytes; int K, M; bool owned; };
 
 struct PeerPtrs { uint32_t* p[8]; };
@@ -84,6 +84,8 @@ struct q38b_pass {
     std::vector<Mat> mats;
     std::vector<Op> ops;
     cudaGraphExec_t graphs[9] = {};
+    size_t arena_mark = (size_t)-1;
+    int peer_store = 1;
     cudaStream_t cap_stream = nullptr;   // capture happens here: the caller's stream may be the legacy default stream
     float* pin_in = nullptr;
     float* pin_out = nullptr;
@@ -120,7 +122,7 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
                 const Buf& d = p->bufs[o.c];
                 float* peers[7];
                 int np = 0;
-                for (int r = 0; r < d.n_peer_ranks; r++)
+                for (int r = 0; p->peer_store && r < d.n_peer_ranks; r++)
                     if (r != ctx->rank && d.peer[r]) peers[np++] = (float*)d.peer[r] + o.off;
                 rc = q38b_gemv_q8k_scatter(ctx, m.type, m.W, m.row_bytes, m.K, m.M, s.ptr, s.n / 256, nb, (float*)d.ptr + o.off, d.n, 0,
                                            peers, np, st);
@@ -204,12 +206,15 @@ int q38b_peer_import(q38b_ctx* ctx, const void* handle64, void** dev_ptr) {
     return Q38B_OK;
 }
 
-int q38b_peer_flags_handle(q38b_ctx* ctx, void* handle64) {
-    if (!ctx || !handle64) return Q38B_ERR_ARG;
+int q38b_peer_arena_create(q38b_ctx* ctx, size_t bytes, void* handle64) {
+    if (!ctx || !handle64 || bytes < 4096) return Q38B_ERR_ARG;
     if (!ctx->d_flags) {
-        cudaError_t e = cudaMalloc(&ctx->d_flags, 16 * sizeof(uint32_t));
-        if (e == cudaSuccess) e = cudaMemset(ctx->d_flags, 0, 16 * sizeof(uint32_t));
+        bytes = (bytes + ((size_t)2 << 20) - 1) & ~(((size_t)2 << 20) - 1);   // whole 2 MB units: an allocation of its own
+        cudaError_t e = cudaMalloc(&ctx->d_flags, bytes);
+        if (e == cudaSuccess) e = cudaMemset(ctx->d_flags, 0, bytes);
         if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+        ctx->arena_bytes = bytes;
+        ctx->arena_used = 256;
     }
     return q38b_peer_export(ctx, ctx->d_flags, handle64);
 }
@@ -241,22 +246,9 @@ int q38b_peer_barrier(q38b_ctx* ctx, void* stream) {
     return Q38B_OK;
 }
 
-int q38b_pass_buffer_handle(q38b_pass* p, int buf, void* handle64) {
-    if (!p || buf < 0 || buf >= (int)p->bufs.size()) return Q38B_ERR_ARG;
-    return q38b_peer_export(p->ctx, p->bufs[buf].ptr, handle64);
-}
-
-int q38b_pass_buffer_connect(q38b_pass* p, int buf, int n_ranks, const void* handles) {
-    if (!p || buf < 0 || buf >= (int)p->bufs.size() || !handles || n_ranks < 2 || n_ranks > 8) return Q38B_ERR_ARG;
-    Buf& b = p->bufs[buf];
-    for (int r = 0; r < n_ranks; r++) {
-        if (r == p->ctx->rank) { b.peer[r] = b.ptr; continue; }
-        void* ptr = nullptr;
-        const int rc = q38b_peer_import(p->ctx, (const char*)handles + 64 * r, &ptr);
-        if (rc != Q38B_OK) return rc;
-        b.peer[r] = ptr;
-    }
-    b.n_peer_ranks = n_ranks;
+int q38b_pass_set_peer_store(q38b_pass* p, int enabled) {
+    if (!p) return Q38B_ERR_ARG;
+    p->peer_store = enabled ? 1 : 0;
     return Q38B_OK;
 }
 
@@ -272,6 +264,7 @@ int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out) {
     if (!p) return Q38B_ERR_NOMEM;
     p->ctx = ctx;
     p->max_nb = max_nb;
+    if (ctx->peers_connected) p->arena_mark = ctx->arena_used;
     *out = p;
     return Q38B_OK;
 }
@@ -279,7 +272,8 @@ int q38b_pass_create(q38b_ctx* ctx, int max_nb, q38b_pass** out) {
 void q38b_pass_destroy(q38b_pass* p) {
     if (!p) return;
     for (auto& g : p->graphs) if (g) cudaGraphExecDestroy(g);
-    for (auto& b : p->bufs) if (b.ptr) cudaFree(b.ptr);
+    for (auto& b : p->bufs) if (b.ptr && !b.in_arena) cudaFree(b.ptr);
+    if (p->arena_mark != (size_t)-1) p->ctx->arena_used = p->arena_mark;   // passes release arena space in LIFO order
     for (auto& m : p->mats) if (m.owned && m.W) cudaFree((void*)m.W);
     if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
     if (p->pin_in) cudaFreeHost(p->pin_in);
@@ -289,10 +283,23 @@ void q38b_pass_destroy(q38b_pass* p) {
 
 int q38b_pass_buffer_f32(q38b_pass* p, int n) {
     if (!p || n < 1) return Q38B_ERR_ARG;
-    void* ptr = nullptr;
-    PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * n * sizeof(float)));
-    PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * n * sizeof(float)));
-    p->bufs.push_back({ptr, n, false, {}, 0});
+    const size_t bytes = (size_t)p->max_nb * n * sizeof(float);
+    q38b_ctx* ctx = p->ctx;
+    Buf b = {nullptr, n, false, {}, 0, false};
+    if (ctx->peers_connected) {
+        // peer-visible: carve from the arena; every rank allocates in the same order, so offsets agree
+        const size_t off = (ctx->arena_used + 255) & ~(size_t)255;
+        if (off + bytes > ctx->arena_bytes) return Q38B_ERR_NOMEM;
+        ctx->arena_used = off + bytes;
+        b.ptr = (char*)ctx->d_flags + off;
+        b.in_arena = true;
+        b.n_peer_ranks = ctx->n_ranks;
+        for (int r = 0; r < ctx->n_ranks; r++) b.peer[r] = (char*)ctx->peer_flags[r] + off;
+    } else {
+        PASS_CUDA(p, cudaMalloc(&b.ptr, bytes));
+    }
+    PASS_CUDA(p, cudaMemset(b.ptr, 0, bytes));
+    p->bufs.push_back(b);
     return (int)p->bufs.size() - 1;
 }
 
@@ -301,7 +308,7 @@ int q38b_pass_buffer_q8k(q38b_pass* p, int K) {
     void* ptr = nullptr;
     PASS_CUDA(p, cudaMalloc(&ptr, (size_t)p->max_nb * (K / 256) * 292));
     PASS_CUDA(p, cudaMemset(ptr, 0, (size_t)p->max_nb * (K / 256) * 292));
-    p->bufs.push_back({ptr, K, true, {}, 0});
+    p->bufs.push_back({ptr, K, true, {}, 0, false});
     return (int)p->bufs.size() - 1;
 }
 

@@ -61,13 +61,13 @@ def total_weight_bytes(n_layers=N_LAYERS, head=True):
     return sum(m.nbytes for m in all_specs(n_layers, head))
 
 
-def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather="peer", exchange=None):
+def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather="peer"):
     """Records the pass on `ps` (qwengine_b200.Pass).
 
     make_matrix(spec, rows) -> matrix id for this rank's shard of `rows` rows (rows = spec.M // world).
     world > 1: gather = "peer" pushes every output slice into the peers' buffers from the matvec kernel and
-    synchronises with one cross-GPU barrier per group of matvecs (exchange(handle_bytes) -> list of all ranks' handles
-    is needed to connect the buffers); gather = "nccl" records an NCCL all-gather after every matvec.
+    synchronises with one cross-GPU barrier per group of matvecs (the context must be peer-connected before the pass
+    is created); gather = "nccl" records an NCCL all-gather after every matvec.
     Returns dict(in_buf, out_buf, out_len).
     """
     x = ps.buffer_f32(HIDDEN)              # residual-stream stand-in: input of every layer
@@ -78,10 +78,9 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
     gu = ps.buffer_f32(2 * FF)             # gate | up
     hq = ps.buffer_q8k(FF)
     logits = ps.buffer_f32(VOCAB) if head else None
-    peer = world > 1 and gather == "peer"
-    if peer:
-        for b in [x, big, kv, gu] + ([logits] if head else []):
-            ps.buffer_connect(b, exchange(ps.buffer_handle(b)))
+    peer = world > 1 and gather == "peer"   # needs Context.peer_connect before the pass is created
+    if hasattr(ps, "set_peer_store"):
+        ps.set_peer_store(peer)
 
     def matvec(spec, src_q, dst, off):
         rows = spec.M // world

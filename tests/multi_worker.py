@@ -111,7 +111,7 @@ def run_gpu():
         idbuf.copy_(torch.tensor(list(raw), dtype=torch.uint8))
     dist.broadcast(idbuf, 0)
     ctx._rc(ctx.lib.q38b_comm_init(ctx.h, world, rank, bytes(idbuf.cpu().tolist())), "q38b_comm_init")
-    ctx.peer_connect(world, rank, exchange(ctx.peer_flags_handle()))
+    ctx.peer_connect(world, rank, exchange(ctx.peer_arena_create()))
     ws = weights()
     outs = {}
     for nb in (1, 3):
@@ -120,7 +120,7 @@ def run_gpu():
             ps = q.Pass(ctx, max_nb=nb)
             w_, r_ = (1, 0) if mode == "single" else (world, rank)
             io = dp.build(ps, lambda spec, rows: ps.matrix_upload(spec.fmt, ws[spec.name], spec.K, shard=r_, n_shards=w_),
-                          n_layers=N_LAYERS, head=False, rank=r_, world=w_, gather=mode, exchange=exchange)
+                          n_layers=N_LAYERS, head=False, rank=r_, world=w_, gather=mode)
             y = np.empty((nb, dp.HIDDEN), np.float32)
             for _ in range(3):      # replays reuse the flags and the buffers
                 ps.run_host(nb, io["in_buf"], x, io["out_buf"], 0, y)
