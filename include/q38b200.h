@@ -95,6 +95,14 @@ int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g_dev, const float* u_dev, long 
 int q38b_dequant_rows(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int rows, void* out_dev,
                       int out_kind, void* stream);
 
+/* Replaces dequant_rows_f16 + gemm_f16 (src/cuda/prefill.cu:802-851; call site Engine::gemm_split,
+ * src/runtime/engine.cpp:2308-2354) by one kernel: Y_dev[t * ldy + r] (+)= sum_k X[t][k] * W[r][k] for t < B tokens,
+ * r < M rows; X_dev is bf16 [B][ldx] (16-byte aligned, ldx a multiple of 8), weights are GGUF blocks dequantized on
+ * the fly to bf16 (each the exact dequantize_row_ref value rounded once) and multiplied on tcgen05 tensor cores with
+ * fp32 accumulation in tensor memory. */
+int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* X_dev,
+                      long long ldx, int B, float* Y_dev, long long ldy, int accumulate, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * All-HBM planner.  Replaces the reference's residency planner and split upload (plan_residency,
  * src/runtime/planner.cpp:91-163; SplitMat / upload_split, src/runtime/engine.h:55-85, engine.cpp:594-629): every

@@ -56,6 +56,7 @@ def load_library():
     lib.q38b_gemv_q8k.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_swiglu_q8k.argtypes = [vp, vp, vp, ll, i32, i32, vp, vp, ll, vp]
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
+    lib.q38b_gemm_prefill.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
     lib.q38b_peer_arena_create.argtypes = [vp, sz, vp]
@@ -187,6 +188,17 @@ class Context:
         """Unchecked pass-through to q38b_gemv_q8k; returns the status code."""
         return self.lib.q38b_gemv_q8k(self.h, type_id, W_ptr, row_bytes, K, M, xq_ptr, x_stride, nb, y_ptr, y_ld,
                                       accumulate, _stream())
+
+    def gemm_prefill(self, fmt, W, X, K, out=None, accumulate=False):
+        """W uint8 [M, row_bytes]; X bfloat16 [B, K]; returns Y float32 [B, M] = X @ dequant(W)^T."""
+        f = F.get(fmt)
+        assert X.dtype == torch.bfloat16 and X.stride(1) == 1
+        M, B = W.shape[0], X.shape[0]
+        if out is None:
+            out = torch.empty((B, M), dtype=torch.float32, device=W.device)
+        self._rc(self.lib.q38b_gemm_prefill(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, X.data_ptr(), X.stride(0), B,
+                                            out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()), "q38b_gemm_prefill")
+        return out
 
     def dequant_rows(self, fmt, W, K, kind=OUT_F32):
         f = F.get(fmt)

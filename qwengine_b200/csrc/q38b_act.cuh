@@ -64,7 +64,7 @@ __device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t
 
 constexpr int ACT_WARPS = 8;
 
-__global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(const float* __restrict__ x, long long x_ld, int K,
+static __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(const float* __restrict__ x, long long x_ld, int K,
                                                                        int n_rows, uint8_t* __restrict__ out,
                                                                        long long out_stride) {
     const int nsb = K >> 8;
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(const floa
 }
 
 // h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u.
-__global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
+static __global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                                                      long long ld, int n, int n_rows, float* __restrict__ h,
                                                                      uint8_t* __restrict__ out, long long out_stride) {
     const int nsb = n >> 8;

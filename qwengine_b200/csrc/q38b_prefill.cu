@@ -1,0 +1,282 @@
+// q38b_prefill.cu -- dequant-on-the-fly prefill GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   Y[t][r] (+)= sum_k X[t][k] * W[r][k]      X bf16 [B][ldx], W GGUF blocks [M rows], Y fp32 [B][ldy]
+//
+// Replaces dequant_rows_f16 + gemm_f16 (cuBLAS) of the reference (src/cuda/prefill.cu:30-85, 802-851) by one kernel:
+// the weights never exist dequantized in global memory.  One CTA owns a 128-row weight tile and up to 512 tokens:
+//   * warps 0-7 (256 threads) decode one 32-weight sub-block each per K-slab of 64 (the exact dequantize_row_ref value,
+//     rounded once to bf16) and store it K-major with the 128-byte swizzle the tensor core expects (operand A);
+//   * one thread streams the matching activation tiles (operand B, 2 x [256 tokens x 64]) with tiled TMA loads
+//     (hardware swizzle, zero fill past the last token; no multicast);
+//   * one thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 256, K = 16) into two fp32 accumulators
+//     in tensor memory (2 x 256 columns) and commits each slab to the stage's "empty" mbarrier;
+//   * warps 0-3 read the accumulators back (tcgen05.ld 32x32b) and store Y, 32 consecutive rows per warp and token.
+// All mbarrier waits are bounded; tensor memory is released before the kernel returns, also after a timeout.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "../../include/q38b200.h"
+#include "q38b_act.cuh"
+#include "q38b_internal.h"
+#include "q38b_pipe.cuh"
+
+using namespace q38b;
+
+namespace {
+
+constexpr int PF_ROWS = 128;       // weight rows per CTA (MMA M)
+constexpr int PF_NTILE = 256;      // tokens per accumulator (MMA N)
+constexpr int PF_KSLAB = 64;       // K elements per stage: one 128-byte swizzle row of bf16
+constexpr int PF_STAGES = 2;
+constexpr int PF_A_BYTES = PF_ROWS * PF_KSLAB * 2;        // 16 KB
+constexpr int PF_B_BYTES = PF_NTILE * PF_KSLAB * 2;       // 32 KB per accumulator
+constexpr int PF_STAGE_BYTES = PF_A_BYTES + 2 * PF_B_BYTES;
+constexpr int PF_THREADS = 320;    // 8 decode warps + TMA warp + MMA warp
+constexpr int PF_SMEM = 1024 + PF_STAGES * PF_STAGE_BYTES + 256;
+
+struct PrefillArgs {
+    const uint8_t* W;
+    long long row_bytes;
+    float* Y;
+    long long ldy;
+    int* status;
+    int K, M, B, accumulate;
+    int n_acc;             // accumulators in use per CTA: 1 (<= 256 tokens in this CTA) or 2
+};
+
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+
+// D format f32, A and B bf16, both K-major, N = 256, M = 128
+constexpr uint32_t PF_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PF_NTILE >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full_a = (uint64_t*)smem;              // [stages] 256 decode threads arrive
+    uint64_t* full_b = full_a + PF_STAGES;           // [stages] TMA bytes
+    uint64_t* empty = full_b + PF_STAGES;            // [stages] tcgen05.commit
+    uint64_t* acc_done = empty + PF_STAGES;          // [1]
+    uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    uint8_t* stages = smem + 1024;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * PF_ROWS;
+    const int tok0 = blockIdx.y * 2 * PF_NTILE;
+    const int n_slabs = a.K / PF_KSLAB;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < PF_STAGES; s++) {
+            mbar_init(smem_u32(&full_a[s]), 256);
+            mbar_init(smem_u32(&full_b[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        mbar_init(smem_u32(acc_done), 1);
+        mbar_fence_init();
+    }
+    if (warp == 9) {   // this warp owns the tensor memory allocation (512 columns = two 128 x 256 fp32 accumulators)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0 && (smem_u32(stages) & 1023u)) atomicOr(a.status, ST_TMEM_TIMEOUT);   // swizzled tiles need 1024-byte alignment
+
+    if (warp < 8) {
+        // ---------------- operand A: decode 128 rows x 64 weights per slab ----------------
+        const int r = tid >> 1, half = tid & 1;                  // row of the tile, which 32-weight half of the slab
+        const int grow = min(row0 + r, a.M - 1);                 // rows past the end repeat the last row (never stored)
+        const uint8_t* wrow = a.W + (size_t)grow * a.row_bytes;
+        for (int slab = 0; slab < n_slabs; slab++) {
+            const int st = slab % PF_STAGES;
+            const uint32_t use = (uint32_t)(slab / PF_STAGES);
+            mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+            const int sub = slab * 2 + half;                     // 32-weight sub-block index within the row
+            float y[32];
+            dequant_sub<FMT>(wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES, sub & 7, y);
+            // row r of the tile: 128 bytes; 16-byte chunk c goes to chunk c ^ (r & 7) (128-byte swizzle)
+            uint8_t* arow = stages + (size_t)st * PF_STAGE_BYTES + (size_t)r * 128;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t p[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(y[8 * c + 2 * j], y[8 * c + 2 * j + 1]);
+                    p[j] = *(const uint32_t*)&v;
+                }
+                const int chunk = (4 * half + c) ^ (r & 7);
+                *(uint4*)(arow + 16 * chunk) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+            fence_proxy_async();                                 // generic-proxy stores -> visible to the tensor core
+            mbar_arrive(smem_u32(&full_a[st]));
+        }
+    } else if (warp == 8) {
+        // ---------------- operand B: activation tiles by TMA ----------------
+        if (lane == 0) {
+            for (int slab = 0; slab < n_slabs; slab++) {
+                const int st = slab % PF_STAGES;
+                const uint32_t use = (uint32_t)(slab / PF_STAGES);
+                mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+                const uint32_t fb = smem_u32(&full_b[st]);
+                mbar_arrive_expect_tx(fb, (uint32_t)(a.n_acc * PF_B_BYTES));
+                uint8_t* b0 = stages + (size_t)st * PF_STAGE_BYTES + PF_A_BYTES;
+                for (int n = 0; n < a.n_acc; n++)
+                    tma_load_2d(smem_u32(b0 + n * PF_B_BYTES), &xmap, slab * PF_KSLAB, tok0 + n * PF_NTILE, fb);
+            }
+        }
+    } else {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            for (int slab = 0; slab < n_slabs; slab++) {
+                const int st = slab % PF_STAGES;
+                const uint32_t use = (uint32_t)(slab / PF_STAGES);
+                mbar_wait_bounded(smem_u32(&full_a[st]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+                mbar_wait_bounded(smem_u32(&full_b[st]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t abase = smem_u32(stages + (size_t)st * PF_STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < PF_KSLAB / 16; k++) {
+                    const uint64_t adesc = umma_desc_sw128(abase + 32 * k);
+                    for (int n = 0; n < a.n_acc; n++) {
+                        const uint64_t bdesc = umma_desc_sw128(abase + PF_A_BYTES + n * PF_B_BYTES + 32 * k);
+                        const uint32_t accum = (slab > 0 || k > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            ::"r"(tmem_base + (uint32_t)(n * PF_NTILE)), "l"(adesc), "l"(bdesc), "r"(PF_IDESC), "r"(accum)
+                            : "memory");
+                    }
+                }
+                // frees the stage once the tensor core has read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(acc_done)) : "memory");
+        }
+    }
+
+    // ---------------- epilogue: warps 0-3 read the accumulators (warp w <-> TMEM lanes 32w..32w+31) ----------------
+    if (warp < 4) {
+        mbar_wait_bounded(smem_u32(acc_done), 0u, abort_flag, a.status, ST_TMEM_TIMEOUT);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = row0 + 32 * warp + lane;
+        const int n_tok = min(a.n_acc * PF_NTILE, a.B - tok0);
+        for (int c0 = 0; c0 < n_tok; c0 += 32) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < a.M) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    if (c0 + j < n_tok) {
+                        float* yo = a.Y + (size_t)(tok0 + c0 + j) * a.ldy + row;
+                        const float val = __uint_as_float(v[j]);
+                        *yo = a.accumulate ? *yo + val : val;
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 9) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+template <int FMT>
+int launch_prefill(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, dim3 grid, cudaStream_t st) {
+    auto kern = prefill_kernel<FMT>;
+    static int configured_device = -1;
+    if (configured_device != ctx->device) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+        configured_device = ctx->device;
+    }
+    kern<<<grid, PF_THREADS, PF_SMEM, st>>>(a, map);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    return Q38B_OK;
+}
+
+}  // namespace
+
+extern "C" int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* X,
+                                 long long ldx, int B, float* Y, long long ldy, int accumulate, void* stream) {
+    if (!ctx || !W || !X || !Y || K <= 0 || K % 256 || M < 1 || B < 1 || ldx < K || ldy < M) return Q38B_ERR_ARG;
+    if (!q38b_format_supported(type)) return Q38B_ERR_UNSUPPORTED;
+    if (row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
+    if (((uintptr_t)W & 1) || (row_bytes & 1) || ((uintptr_t)X & 15) || ((ldx * 2) & 15) || ((uintptr_t)Y & 3)) return Q38B_ERR_ALIGN;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return Q38B_ERR_UNSUPPORTED;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)B};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {PF_KSLAB, PF_NTILE};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)X, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return Q38B_ERR_ARG;
+    PrefillArgs a;
+    a.W = (const uint8_t*)W;
+    a.row_bytes = (long long)row_bytes;
+    a.Y = Y;
+    a.ldy = ldy;
+    a.status = ctx->d_status;
+    a.K = K;
+    a.M = M;
+    a.B = B;
+    a.accumulate = accumulate ? 1 : 0;
+    a.n_acc = B > PF_NTILE ? 2 : 1;
+    const dim3 grid((unsigned)((M + PF_ROWS - 1) / PF_ROWS), (unsigned)((B + 2 * PF_NTILE - 1) / (2 * PF_NTILE)));
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (type) {
+        case T_Q8_0: return launch_prefill<T_Q8_0>(ctx, a, map, grid, st);
+        case T_Q4_K: return launch_prefill<T_Q4_K>(ctx, a, map, grid, st);
+        case T_Q5_K: return launch_prefill<T_Q5_K>(ctx, a, map, grid, st);
+        case T_Q6_K: return launch_prefill<T_Q6_K>(ctx, a, map, grid, st);
+        case T_IQ3_XXS: return launch_prefill<T_IQ3_XXS>(ctx, a, map, grid, st);
+        case T_IQ3_S: return launch_prefill<T_IQ3_S>(ctx, a, map, grid, st);
+        case T_IQ4_XS: return launch_prefill<T_IQ4_XS>(ctx, a, map, grid, st);
+        default: return Q38B_ERR_UNSUPPORTED;
+    }
+}

@@ -1,0 +1,61 @@
+"""Prefill GEMM (tcgen05, weights dequantized on the fly to bf16) against the fp32/double oracle.
+
+Tolerance: |Y - exact| <= 1e-2 * sum_k |w x| per output (the bound set for the bf16 path; the only rounding besides
+fp32 accumulation is one bf16 rounding per weight, 2^-9 relative)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from qwengine_b200 import formats as F, synth
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def check(ctx, name, M, K, B, accumulate=False):
+    f = F.get(name)
+    w = synth.make_weights(f, M, K, seed=400 + M + B, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    x = torch.randn((B, K), generator=torch.Generator().manual_seed(B)).to(torch.bfloat16)
+    wd, xd = torch.from_numpy(w).cuda(), x.cuda()
+    if accumulate:
+        y = torch.full((B, M), 2.0, dtype=torch.float32, device="cuda")
+        ctx.gemm_prefill(f, wd, xd, K, out=y, accumulate=True)
+        y = y - 2.0
+    else:
+        y = ctx.gemm_prefill(f, wd, xd, K)
+    ctx.check()
+    want, mag = oracle.port.matmul_ref(f.type_id, w, x.float().numpy(), K)
+    err = np.abs(y.cpu().numpy().astype(np.float64) - want) / np.where(mag == 0, 1, mag)
+    assert err.max() < TOL, (name, M, K, B, err.max())
+    return err.max()
+
+
+@pytest.mark.parametrize("name", list(F.FORMATS))
+def test_prefill_small_all_formats(ctx, name):
+    check(ctx, name, 128, 512, 64)
+
+
+@pytest.mark.parametrize("M,K,B", [(128, 256, 1), (200, 1024, 300), (384, 2048, 256), (130, 768, 700), (256, 5120, 1024)])
+def test_prefill_shapes(ctx, M, K, B):
+    check(ctx, "IQ3_XXS", M, K, B)
+    check(ctx, "Q4_K", M, K, B)
+
+
+def test_prefill_accumulate_and_stride(ctx):
+    check(ctx, "Q6_K", 128, 512, 40, accumulate=True)
+
+
+def test_prefill_equals_bf16_reference_gemm(ctx):
+    """Against torch: bf16(dequantized weights) x bf16 activations with fp32 accumulation -- same operands, so only the
+    summation order differs."""
+    from qwengine_b200 import api
+    f = F.Q4_K
+    M, K, B = 512, 5120, 512
+    w = torch.from_numpy(synth.make_weights(f, M, K, seed=77)).cuda()
+    x = torch.randn((B, K), device="cuda", dtype=torch.bfloat16)
+    y = ctx.gemm_prefill(f, w, x, K)
+    wb = ctx.dequant_rows(f, w, K, api.OUT_BF16)
+    ref = (x.float() @ wb.float().t())
+    mag = (x.float().abs() @ wb.float().abs().t())
+    assert float(((y - ref).abs() / mag).max()) < 1e-5
