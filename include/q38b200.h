@@ -77,6 +77,13 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x_dev, long long x_ld, int K, 
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* q8k_dev,
                   long long q8k_stride, int nb, float* y_dev, long long y_ld, int accumulate, void* stream);
 
+/* Matvec straight from fp32 activations x_dev[c * x_ld .. + K), the form in which the reference's engine holds them
+ * before quantize_act_q8 + gemv_q8n (src/cuda/gemv.cu:200-204, 215-228): quantizes the nb columns to Q8_K into
+ * `q8k_scratch_dev` (caller-owned device scratch of at least nb * q38b_q8k_bytes(K) bytes) and runs q38b_gemv_q8k. */
+int q38b_gemv_f32(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const float* x_dev,
+                  long long x_ld, int nb, float* y_dev, long long y_ld, int accumulate, void* q8k_scratch_dev,
+                  size_t scratch_bytes, void* stream);
+
 /* The same matvec with a fused all-gather for row-sharded matrices: every result is also stored at the same position
  * of n_peers (0..7) output buffers that live on other GPUs (peer-mapped pointers, see q38b_peer_*), so that after
  * q38b_peer_barrier every GPU holds the outputs of all shards.  No counterpart in the reference (single GPU). */

@@ -56,6 +56,7 @@ def load_library():
     lib.q38b_gemv_q8k.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_swiglu_q8k.argtypes = [vp, vp, vp, ll, i32, i32, vp, vp, ll, vp]
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
+    lib.q38b_gemv_f32.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp, sz, vp]
     lib.q38b_gemm_prefill.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
@@ -182,6 +183,19 @@ class Context:
         self._rc(self.lib.q38b_gemv_q8k(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, xq.data_ptr(),
                                         xq.stride(0) // F.Q8K_BLOCK_BYTES, nb, out.data_ptr(), out.stride(0),
                                         int(bool(accumulate)), _stream()), "q38b_gemv_q8k")
+        return out
+
+    def gemv_f32(self, fmt, W, x, K, scratch=None, out=None, accumulate=False):
+        """Matvec from fp32 activations x [nb, K]; `scratch` is a uint8 device tensor for the Q8_K blocks."""
+        f = F.get(fmt)
+        nb, M = x.shape[0], W.shape[0]
+        if scratch is None:
+            scratch = torch.empty(nb * (K // 256) * F.Q8K_BLOCK_BYTES, dtype=torch.uint8, device=W.device)
+        if out is None:
+            out = torch.empty((nb, M), dtype=torch.float32, device=W.device)
+        self._rc(self.lib.q38b_gemv_f32(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, x.data_ptr(), x.stride(0), nb,
+                                        out.data_ptr(), out.stride(0), int(bool(accumulate)), scratch.data_ptr(), scratch.numel(),
+                                        _stream()), "q38b_gemv_f32")
         return out
 
     def gemv_raw(self, type_id, W_ptr, row_bytes, K, M, xq_ptr, x_stride, nb, y_ptr, y_ld, accumulate=0):

@@ -422,6 +422,15 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     }
 }
 
+int q38b_gemv_f32(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const float* x, long long x_ld,
+                  int nb, float* y, long long y_ld, int accumulate, void* q8k_scratch, size_t scratch_bytes, void* stream) {
+    if (!ctx || !x || !q8k_scratch || nb < 1 || nb > 8 || K <= 0 || K % 256) return Q38B_ERR_ARG;
+    if (scratch_bytes < (size_t)nb * q38b_q8k_bytes(K)) return Q38B_ERR_NOMEM;
+    int rc = q38b_quantize_q8k(ctx, x, x_ld, K, nb, q8k_scratch, K / 256, stream);
+    if (rc != Q38B_OK) return rc;
+    return q38b_gemv_q8k(ctx, type, W, row_bytes, K, M, q8k_scratch, K / 256, nb, y, y_ld, accumulate, stream);
+}
+
 int q38b_dequant_rows(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int rows, void* out, int out_kind,
                       void* stream) {
     if (!ctx || !W || !out || K <= 0 || K % 256 || rows < 1) return Q38B_ERR_ARG;

@@ -164,6 +164,22 @@ def test_row_stride_and_shards(ctx, name):
         assert torch.equal(torch.cat(parts, dim=1), full)
 
 
+@pytest.mark.parametrize("name", ["IQ3_XXS", "Q4_K", "IQ4_XS", "Q8_0"])
+def test_gemv_from_fp32_activations(ctx, name):
+    """q38b_gemv_f32 = quantize into caller scratch + matvec: the same bits as the two calls made separately."""
+    f = F.get(name)
+    M, K = 300, 2048
+    w = dev(synth.make_weights(f, M, K, seed=91, scale=scale_for(name)))
+    for nb in (1, 4):
+        x = dev(synth.make_activations(nb, K, seed=92 + nb))
+        y = ctx.gemv_f32(f, w, x, K)
+        assert torch.equal(y, ctx.gemv(f, w, ctx.quantize_q8k(x), K))
+    small = torch.empty(100, dtype=torch.uint8, device="cuda")
+    with pytest.raises(api.Q38BError):
+        ctx.gemv_f32(f, w, x, K, scratch=small)
+    ctx.check()
+
+
 def test_argument_errors(ctx):
     f = F.IQ3_XXS
     K, M = 512, 16
