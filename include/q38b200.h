@@ -84,6 +84,17 @@ int q38b_gemv_f32(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_by
                   long long x_ld, int nb, float* y_dev, long long y_ld, int accumulate, void* q8k_scratch_dev,
                   size_t scratch_bytes, void* stream);
 
+/* No counterpart in the reference.  q38b_gemv_f32 for callers that may not allocate device memory (an engine that
+ * sized its arena at start-up, code running during stream capture, a loop that must not synchronise): the Q8_K
+ * scratch is a fixed array inside the library, q38b_gemv_f32_static_capacity() bytes (158,848: up to 8 columns of
+ * K = 17408, in general nb * K / 256 <= 544).  Larger requests return Q38B_ERR_NOMEM.  The call allocates nothing.  The
+ * first call on a device looks the array's address up (make it before any stream capture, with the context's device
+ * current).  All calls on a device share the array: calls that may overlap on the GPU (different streams) race, and
+ * the array keeps the last call's blocks. */
+int q38b_gemv_f32_static(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const float* x_dev,
+                         long long x_ld, int nb, float* y_dev, long long y_ld, int accumulate, void* stream);
+size_t q38b_gemv_f32_static_capacity(void);
+
 /* The same matvec with a fused all-gather for row-sharded matrices: every result is also stored at the same position
  * of n_peers (0..7) output buffers that live on other GPUs (peer-mapped pointers, see q38b_peer_*), so that after
  * q38b_peer_barrier every GPU holds the outputs of all shards.  No counterpart in the reference (single GPU). */

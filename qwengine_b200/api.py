@@ -57,6 +57,8 @@ def load_library():
     lib.q38b_swiglu_q8k.argtypes = [vp, vp, vp, ll, i32, i32, vp, vp, ll, vp]
     lib.q38b_dequant_rows.argtypes = [vp, u32, vp, sz, i32, i32, vp, i32, vp]
     lib.q38b_gemv_f32.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp, sz, vp]
+    lib.q38b_gemv_f32_static.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
+    lib.q38b_gemv_f32_static_capacity.restype = sz
     lib.q38b_gemm_prefill.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
@@ -196,6 +198,16 @@ class Context:
         self._rc(self.lib.q38b_gemv_f32(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, x.data_ptr(), x.stride(0), nb,
                                         out.data_ptr(), out.stride(0), int(bool(accumulate)), scratch.data_ptr(), scratch.numel(),
                                         _stream()), "q38b_gemv_f32")
+        return out
+
+    def gemv_f32_static(self, fmt, W, x, K, out=None, accumulate=False):
+        """q38b_gemv_f32_static: like gemv_f32 but the Q8_K scratch is the library's built-in array (no allocation)."""
+        f = F.get(fmt)
+        nb, M = x.shape[0], W.shape[0]
+        assert out is not None, "the caller brings the output buffer: this path allocates nothing"
+        self._rc(self.lib.q38b_gemv_f32_static(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, x.data_ptr(), x.stride(0), nb,
+                                               out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()),
+                 "q38b_gemv_f32_static")
         return out
 
     def gemv_raw(self, type_id, W_ptr, row_bytes, K, M, xq_ptr, x_stride, nb, y_ptr, y_ld, accumulate=0):
