@@ -49,8 +49,16 @@ void q38b_ctx_destroy(q38b_ctx* ctx);
 int q38b_ctx_check(q38b_ctx* ctx, void* stream);
 int q38b_last_cuda_error(const q38b_ctx* ctx);
 const char* q38b_status_string(int status);
-/* Enable (1, default) or disable (0) programmatic dependent launch between consecutive kernels of a stream. */
+/* Programmatic dependent launch lets a matvec start (and prefetch) while the previous KERNEL of the stream drains.  It
+ * is always used between the kernels of a recorded pass.  For direct calls it is off by default, because a direct call
+ * may follow a memcpy that fills its operands, which a programmatic launch does not wait for; 1 turns it on for
+ * direct calls too (only when every matvec follows a kernel), 0 turns it off everywhere. */
 int q38b_ctx_set_pdl(q38b_ctx* ctx, int enabled);
+/* With programmatic dependent launch a matvec may start while the previous kernel of the stream is still running.  Its
+ * activations always wait for that kernel; its weight stream waits too unless this option is 1, which promises that
+ * the weights were written long before (resident model weights).  Passes (q38b_pass_run) stream resident matrices and
+ * set it themselves.  Default 0. */
+int q38b_ctx_set_static_weights(q38b_ctx* ctx, int enabled);
 /* Single-column calls (nb = 1) normally run a dedicated dp4a kernel whose float summation order differs from the
  * tensor-core kernel used for nb >= 2 (both are exact in their integer parts and agree to ~1e-7).  With this option
  * set to 1, nb = 1 also runs the tensor-core kernel, so that every column of an nb-column call is bit-identical to

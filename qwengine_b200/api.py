@@ -45,6 +45,7 @@ def load_library():
     lib.q38b_last_cuda_error.argtypes = [vp]
     lib.q38b_ctx_set_pdl.argtypes = [vp, i32]
     lib.q38b_ctx_set_uniform_columns.argtypes = [vp, i32]
+    lib.q38b_ctx_set_static_weights.argtypes = [vp, i32]
     lib.q38b_status_string.argtypes = [i32]
     lib.q38b_status_string.restype = C.c_char_p
     lib.q38b_format_supported.argtypes = [u32]
@@ -140,6 +141,9 @@ class Context:
 
     def peer_connect(self, n_ranks, rank, handles):
         self._rc(self.lib.q38b_peer_connect(self.h, n_ranks, rank, b"".join(handles)), "q38b_peer_connect")
+
+    def set_static_weights(self, enabled):
+        self._rc(self.lib.q38b_ctx_set_static_weights(self.h, int(bool(enabled))), "q38b_ctx_set_static_weights")
 
     def set_uniform_columns(self, enabled):
         self._rc(self.lib.q38b_ctx_set_uniform_columns(self.h, int(bool(enabled))), "q38b_ctx_set_uniform_columns")

@@ -169,7 +169,7 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
     }
     a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
     const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 1;
-    for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= 0; rep_log2 -= (rep_log2 == 5 ? 2 : 3)) {
+    for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= (cb_entries ? 5 : 0); rep_log2--) {   // this kernel needs all 32 replicas
         a.cb_rep_log2 = rep_log2;
         a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
         for (int stages = G1_MAX_STAGES; stages >= min_stages; stages--) {
@@ -287,6 +287,12 @@ int q38b_ctx_check(q38b_ctx* ctx, void* stream) {
 
 int q38b_last_cuda_error(const q38b_ctx* ctx) { return ctx ? ctx->last_cuda : 0; }
 
+int q38b_ctx_set_static_weights(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->static_weights = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+
 int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->uniform_columns = enabled ? 1 : 0;
@@ -296,6 +302,7 @@ int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled) {
 int q38b_ctx_set_pdl(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->pdl = enabled ? 1 : 0;
+    ctx->pass_pdl = enabled ? 1 : 0;
     return Q38B_OK;
 }
 
@@ -373,6 +380,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
             g.xq = (const uint8_t*)q8k;
             g.y = y;
             g.n_peers = n_peers;
+            g.static_weights = ctx->static_weights;
             for (int i = 0; i < n_peers; i++) g.y_peer[i] = y_peers[i];
             g.status = ctx->d_status;
             g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
@@ -403,6 +411,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     a.y = y;
     a.y_ld = y_ld;
     a.n_peers = n_peers;
+    a.static_weights = ctx->static_weights;
     for (int i = 0; i < n_peers; i++) a.y_peer[i] = y_peers[i];
     a.status = ctx->d_status;
     a.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;

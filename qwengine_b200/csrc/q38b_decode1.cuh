@@ -40,15 +40,55 @@ Q38B_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t sh) {   // (hi:lo) 
 #endif
 }
 
-// 8 bytes from a 2-byte aligned address: three aligned words and two funnel shifts
-Q38B_HD void ld_8_a2(const uint8_t* p, uint32_t& lo, uint32_t& hi) {
-    const uint32_t mis = (uint32_t)((uintptr_t)p & 2);
-    const uint32_t* w = (const uint32_t*)(p - mis);   // pointer minus integer: the address space stays known
+// ---------------------------------------------------------------------------------------------------------------
+// Staged bytes are addressed through SP: on the device a 32-bit shared-space address (loads are ld.shared with
+// immediate offsets, no 64-bit pointer arithmetic and no generic-to-shared conversion per load), on the host a pointer.
+// ---------------------------------------------------------------------------------------------------------------
+#if defined(__CUDA_ARCH__)
+struct SP { uint32_t a; };
+__device__ __forceinline__ SP sp_from(const void* p) { return SP{(uint32_t)__cvta_generic_to_shared(p)}; }
+__device__ __forceinline__ uint32_t sp_low2(SP p) { return p.a & 2u; }
+__device__ __forceinline__ uint32_t sp_ld8(SP p, int o = 0) { uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(p.a + o)); return v; }
+__device__ __forceinline__ int sp_ld8s(SP p, int o = 0) { int v; asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(p.a + o)); return v; }
+__device__ __forceinline__ uint32_t sp_ld16(SP p, int o = 0) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(p.a + o)); return v; }
+__device__ __forceinline__ uint32_t sp_ld32(SP p, int o = 0) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(p.a + o)); return v; }
+__device__ __forceinline__ float sp_ldf(SP p, int o = 0) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(p.a + o)); return v; }
+__device__ __forceinline__ void sp_ld64(SP p, int o, uint32_t& x, uint32_t& y) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(x), "=r"(y) : "r"(p.a + o));
+}
+__device__ __forceinline__ void sp_ld128(SP p, int o, uint32_t (&v)[4]) {
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(p.a + o));
+}
+#else
+struct SP { const uint8_t* a; };
+inline SP sp_from(const void* p) { return SP{(const uint8_t*)p}; }
+inline uint32_t sp_low2(SP p) { return (uint32_t)((uintptr_t)p.a & 2); }
+inline uint32_t sp_ld8(SP p, int o = 0) { return p.a[o]; }
+inline int sp_ld8s(SP p, int o = 0) { return (int8_t)p.a[o]; }
+inline uint32_t sp_ld16(SP p, int o = 0) { uint16_t v; memcpy(&v, p.a + o, 2); return v; }
+inline uint32_t sp_ld32(SP p, int o = 0) { uint32_t v; memcpy(&v, p.a + o, 4); return v; }
+inline float sp_ldf(SP p, int o = 0) { float v; memcpy(&v, p.a + o, 4); return v; }
+inline void sp_ld64(SP p, int o, uint32_t& x, uint32_t& y) { memcpy(&x, p.a + o, 4); memcpy(&y, p.a + o + 4, 4); }
+inline void sp_ld128(SP p, int o, uint32_t (&v)[4]) { memcpy(v, p.a + o, 16); }
+#endif
+Q38B_HD SP operator+(SP p, int o) { return SP{p.a + o}; }
+Q38B_HD SP operator-(SP p, int o) { return SP{p.a - o}; }
+
+// 8 bytes from a 2-byte aligned address: three aligned words and two funnel shifts.  `mis` = address & 2.
+Q38B_HD void sp_ld8b_a2(SP p, uint32_t mis, uint32_t& lo, uint32_t& hi) {
+    const SP w = p - (int)mis;
     const uint32_t sh = mis * 8;
-    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    const uint32_t w0 = sp_ld32(w, 0), w1 = sp_ld32(w, 4), w2 = sp_ld32(w, 8);
     lo = funnel_r(w0, w1, sh);
     hi = funnel_r(w1, w2, sh);
 }
+
+// Codebook replicated 32 x in shared memory: entry e for lane l is the word at base + e * 128 + l * 4.
+struct Codebook1 { SP lane_base; };
+Q38B_HD uint32_t cb1(const Codebook1& cb, uint32_t e_times_128) { return sp_ld32(cb.lane_base + (int)e_times_128); }
+
+// byte k of w, times 128 (the stride of a replicated codebook entry)
+Q38B_HD uint32_t byte_x128(uint32_t w, int k) { return (k == 0 ? (w << 7) : (w >> (8 * k - 7))) & 0x7F80u; }
 
 // what a lane needs from the activations for one slice
 template <int NWORDS> struct ActRegs {
@@ -65,69 +105,75 @@ template <int FMT> struct Gran;
 template <> struct Gran<T_IQ3_XXS> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) a.q[i] = ld_u32(aq + 32 * lane + 4 * i);
-        a.dx = ad[(lane >> 3) * 8] * 0.25f;
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, (lane >> 3) * 32) * 0.25f;
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook& cb, int lane) {
-        const uint8_t* p = row + 98 * (lane >> 3);
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 98 * (lane >> 3);
         const int s = lane & 7;
         uint32_t iw[2];
-        ld_8_a2(p + 2 + 8 * s, iw[0], iw[1]);
-        const uint32_t aux = ld_u16(p + 66 + 4 * s) | (ld_u16(p + 68 + 4 * s) << 16);
+        sp_ld8b_a2(p + (2 + 8 * s), sp_low2(p) ^ 2u, iw[0], iw[1]);   // the indices start 2 bytes into the 2-byte aligned block
+        const uint32_t aux = sp_ld16(p, 66 + 4 * s) | (sp_ld16(p, 68 + 4 * s) << 16);
         int P = 0, N = 0;
 #pragma unroll
         for (int l = 0; l < 4; l++) {
             const uint32_t s7 = (aux >> (7 * l)) & 127u;
             const uint32_t m_lo = sign_mask4(s7);
             const uint32_t m_hi = prmt((uint32_t)popc(s7) * 0x80000000u + s7 * 0x00020408u, 0u, 0xBA98u);
-            const uint32_t w = iw[l >> 1] >> (16 * (l & 1));
-            const uint32_t g0 = cb_lookup(cb, w & 0xFFu), g1 = cb_lookup(cb, (w >> 8) & 0xFFu);
+            const uint32_t w = iw[l >> 1];
+            const uint32_t g0 = cb1(cb, byte_x128(w, 2 * (l & 1))), g1 = cb1(cb, byte_x128(w, 2 * (l & 1) + 1));
             P = dp4a_us(g0, a.q[2 * l], P);
             P = dp4a_us(g1, a.q[2 * l + 1], P);
             N = dp4a_us(g0 & m_lo, a.q[2 * l], N);
             N = dp4a_us(g1 & m_hi, a.q[2 * l + 1], N);
         }
         const int sumi = (int)(2u * (aux >> 28) + 1u) * (P - 2 * N);
-        return fp16_bits_to_float(ld_u16(p)) * a.dx * (float)sumi;
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * (float)sumi;
     }
 };
 
 // ---------------------------------------------------------------------------------------------------------------
-// IQ3_S
+// IQ3_S: 512-entry codebook, 9th index bits in qh, explicit sign bytes
 // ---------------------------------------------------------------------------------------------------------------
 template <> struct Gran<T_IQ3_S> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) a.q[i] = ld_u32(aq + 32 * lane + 4 * i);
-        a.dx = ad[(lane >> 3) * 8];
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, (lane >> 3) * 32);
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook& cb, int lane) {
-        const uint8_t* p = row + 110 * (lane >> 3);
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 110 * (lane >> 3);
         const int s = lane & 7;
         uint32_t iw[2];
-        ld_8_a2(p + 2 + 8 * s, iw[0], iw[1]);
-        const uint32_t qh = ld_u8(p + 66 + s);
-        const uint32_t sg = ld_u16(p + 74 + 4 * s) | (ld_u16(p + 76 + 4 * s) << 16);
-        const uint32_t ls = (ld_u8(p + 106 + (s >> 1)) >> (4 * (s & 1))) & 0xFu;
+        sp_ld8b_a2(p + (2 + 8 * s), sp_low2(p) ^ 2u, iw[0], iw[1]);
+        const uint32_t qh = sp_ld8(p, 66 + s) << 15;               // bit j of qh now sits at bit 15 + j: entry 256 * 128
+        const uint32_t sg = sp_ld16(p, 74 + 4 * s) | (sp_ld16(p, 76 + 4 * s) << 16);
+        const uint32_t ls = (sp_ld8(p, 106 + (s >> 1)) >> (4 * (s & 1))) & 0xFu;
         int P = 0, N = 0;
 #pragma unroll
         for (int l = 0; l < 4; l++) {
-            const uint32_t sb = (sg >> (8 * l)) & 0xFFu;
-            const uint32_t m_lo = sign_mask4(sb & 0xFu), m_hi = sign_mask4(sb >> 4);
-            const uint32_t w = iw[l >> 1] >> (16 * (l & 1));
-            const uint32_t g0 = cb_lookup(cb, (w & 0xFFu) | (((qh >> (2 * l)) & 1u) << 8));
-            const uint32_t g1 = cb_lookup(cb, ((w >> 8) & 0xFFu) | (((qh >> (2 * l + 1)) & 1u) << 8));
+            const uint32_t sb = sg >> (8 * l);
+            const uint32_t m_lo = sign_mask4(sb & 0xFu), m_hi = sign_mask4((sb >> 4) & 0xFu);
+            const uint32_t w = iw[l >> 1];
+            const uint32_t g0 = cb1(cb, byte_x128(w, 2 * (l & 1)) | ((qh >> (2 * l)) & 0x8000u));
+            const uint32_t g1 = cb1(cb, byte_x128(w, 2 * (l & 1) + 1) | ((qh >> (2 * l + 1)) & 0x8000u));
             P = dp4a_us(g0, a.q[2 * l], P);
             P = dp4a_us(g1, a.q[2 * l + 1], P);
             N = dp4a_us(g0 & m_lo, a.q[2 * l], N);
             N = dp4a_us(g1 & m_hi, a.q[2 * l + 1], N);
         }
         const int sumi = (int)(2u * ls + 1u) * (P - 2 * N);
-        return fp16_bits_to_float(ld_u16(p)) * a.dx * (float)sumi;
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * (float)sumi;
     }
 };
 
@@ -137,17 +183,20 @@ template <> struct Gran<T_IQ3_S> {
 template <> struct Gran<T_IQ4_XS> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) a.q[i] = ld_u32(aq + 32 * lane + 4 * i);
-        a.dx = ad[(lane >> 3) * 8];
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, (lane >> 3) * 32);
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook&, int lane) {
-        const uint8_t* p = row + 136 * (lane >> 3);
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
+        const SP p = row + 136 * (lane >> 3);
         const int s = lane & 7;
         uint32_t w[4];
-        ld_u64(p + 8 + 16 * s, w[0], w[1]);
-        ld_u64(p + 16 + 16 * s, w[2], w[3]);
+        sp_ld64(p, 8 + 16 * s, w[0], w[1]);
+        sp_ld64(p, 16 + 16 * s, w[2], w[3]);
         int dot = 0;
 #pragma unroll
         for (int t = 0; t < 4; t++) {
@@ -156,8 +205,8 @@ template <> struct Gran<T_IQ4_XS> {
             dot = dp4a_ss(x0, a.q[2 * t], dot);
             dot = dp4a_ss(x1, a.q[2 * t + 1], dot);
         }
-        const uint32_t hdr = ld_u32(p);            // fp16 d | scales_h
-        const uint32_t sl = ld_u8(p + 4 + (s >> 1));
+        const uint32_t hdr = sp_ld32(p, 0);            // fp16 d | scales_h
+        const uint32_t sl = sp_ld8(p, 4 + (s >> 1));
         const int ls = (int)(((sl >> (4 * (s & 1))) & 0xFu) | ((((hdr >> 16) >> (2 * s)) & 3u) << 4)) - 32;
         return fp16_bits_to_float(hdr & 0xFFFFu) * a.dx * (float)(ls * dot);
     }
@@ -172,28 +221,32 @@ template <int NBITS> struct GranQ45K {
     static constexpr int WORDS = 16, LANES_PER_ROW = 16;
     static constexpr int BB = NBITS == 5 ? 176 : 144, QS = NBITS == 5 ? 48 : 16;
     struct Acts { uint32_t q[16]; float dx; int bs0, bs1; };
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         const int pr = lane & 15;
 #pragma unroll
-        for (int i = 0; i < 16; i++) a.q[i] = ld_u32(aq + 64 * pr + 4 * i);
-        a.dx = ad[(pr >> 2) * 8];
+        for (int i = 0; i < 4; i++) {
+            uint32_t v[4];
+            sp_ld128(aq, 64 * pr + 16 * i, v);
+            a.q[4 * i] = v[0]; a.q[4 * i + 1] = v[1]; a.q[4 * i + 2] = v[2]; a.q[4 * i + 3] = v[3];
+        }
+        a.dx = sp_ldf(ad, (pr >> 2) * 32);
         a.bs0 = 0; a.bs1 = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) { a.bs0 = dp4a_ss(0x01010101u, a.q[i], a.bs0); a.bs1 = dp4a_ss(0x01010101u, a.q[8 + i], a.bs1); }
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook&, int lane) {
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const int pr = lane & 15, pp = pr & 3;
-        const uint8_t* p = row + BB * (pr >> 2);
-        uint32_t w[8];
-#if defined(__CUDA_ARCH__)
+        const SP p = row + BB * (pr >> 2);
+        uint32_t w[8], hd[4];
         {
-            const uint4 v0 = *(const uint4*)(p + QS + 32 * pp), v1 = *(const uint4*)(p + QS + 32 * pp + 16);
-            w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
+            uint32_t v[4];
+            sp_ld128(p, QS + 32 * pp, v);
+            w[0] = v[0]; w[1] = v[1]; w[2] = v[2]; w[3] = v[3];
+            sp_ld128(p, QS + 32 * pp + 16, v);
+            w[4] = v[0]; w[5] = v[1]; w[6] = v[2]; w[7] = v[3];
         }
-#else
-        memcpy(w, p + QS + 32 * pp, 32);
-#endif
-        const uint32_t dd = ld_u32(p), u0 = ld_u32(p + 4), u1 = ld_u32(p + 8), u2 = ld_u32(p + 12);
+        sp_ld128(p, 0, hd);                        // d | dmin, scales[12]
+        const uint32_t dd = hd[0], u0 = hd[1], u1 = hd[2], u2 = hd[3];
         // 6-bit scales / mins of sub-blocks 2pp, 2pp+1 (get_scale_min_k4, src/quant/quant_ref.cpp:24-32)
         const bool hi_half = pp >= 2;
         const uint32_t sc4 = hi_half ? ((u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3F3F3F3Fu);
@@ -211,14 +264,13 @@ template <int NBITS> struct GranQ45K {
             hi >>= 4;
         } else {
             uint32_t h[8];
-#if defined(__CUDA_ARCH__)
             {
-                const uint4 v0 = *(const uint4*)(p + 16), v1 = *(const uint4*)(p + 32);
-                h[0] = v0.x; h[1] = v0.y; h[2] = v0.z; h[3] = v0.w; h[4] = v1.x; h[5] = v1.y; h[6] = v1.z; h[7] = v1.w;
+                uint32_t v[4];
+                sp_ld128(p, 16, v);
+                h[0] = v[0]; h[1] = v[1]; h[2] = v[2]; h[3] = v[3];
+                sp_ld128(p, 32, v);
+                h[4] = v[0]; h[5] = v[1]; h[6] = v[2]; h[7] = v[3];
             }
-#else
-            memcpy(h, p + 16, 32);
-#endif
             const uint32_t b0 = 2u * (uint32_t)pp;   // bit of qh for the low-nibble sub-block; b0 + 1 for the other
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -243,22 +295,20 @@ template <> struct Gran<T_Q5_K> : GranQ45K<5> {};
 template <> struct Gran<T_Q6_K> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         const int sb = lane >> 3, n = (lane >> 2) & 1, i = lane & 3;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            a.q[2 * j] = ld_u32(aq + 256 * sb + 128 * n + 32 * j + 8 * i);
-            a.q[2 * j + 1] = ld_u32(aq + 256 * sb + 128 * n + 32 * j + 8 * i + 4);
-        }
-        a.dx = ad[sb * 8];
+        for (int j = 0; j < 4; j++) sp_ld64(aq, 256 * sb + 128 * n + 32 * j + 8 * i, a.q[2 * j], a.q[2 * j + 1]);
+        a.dx = sp_ldf(ad, sb * 32);
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook&, int lane) {
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const int n = (lane >> 2) & 1, i = lane & 3;
-        const uint8_t* p = row + 210 * (lane >> 3);
+        const SP p = row + 210 * (lane >> 3);
+        const uint32_t mis = sp_low2(p);
         uint32_t qa[2], qb[2], qh[2];
-        ld_8_a2(p + 64 * n + 8 * i, qa[0], qa[1]);
-        ld_8_a2(p + 64 * n + 32 + 8 * i, qb[0], qb[1]);
-        ld_8_a2(p + 128 + 32 * n + 8 * i, qh[0], qh[1]);
+        sp_ld8b_a2(p + (64 * n + 8 * i), mis, qa[0], qa[1]);
+        sp_ld8b_a2(p + (64 * n + 32 + 8 * i), mis, qb[0], qb[1]);
+        sp_ld8b_a2(p + (128 + 32 * n + 8 * i), mis, qh[0], qh[1]);
         int d4[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int k = 0; k < 2; k++) {
@@ -267,12 +317,11 @@ template <> struct Gran<T_Q6_K> {
             d4[2] = dp4a_ss(Unit<T_Q6_K>::q6(qa[k] >> 4, qh[k]), a.q[4 + k], d4[2]);
             d4[3] = dp4a_ss(Unit<T_Q6_K>::q6(qb[k] >> 4, qh[k] >> 2), a.q[6 + k], d4[3]);
         }
-        // scale of group 8n + 2j + (i >> 1)
-        const uint8_t* sc = p + 192 + 8 * n + (i >> 1);
+        const SP sc = p + (192 + 8 * n + (i >> 1));          // scale of group 8n + 2j + (i >> 1)
         int sumi = 0;
 #pragma unroll
-        for (int j = 0; j < 4; j++) sumi += (int)(int8_t)ld_u8(sc + 2 * j) * d4[j];
-        return fp16_bits_to_float(ld_u16(p + 208)) * a.dx * (float)sumi;
+        for (int j = 0; j < 4; j++) sumi += sp_ld8s(sc, 2 * j) * d4[j];
+        return fp16_bits_to_float(sp_ld16(p, 208)) * a.dx * (float)sumi;
     }
 };
 
@@ -282,22 +331,29 @@ template <> struct Gran<T_Q6_K> {
 template <> struct Gran<T_Q8_0> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
-    static Q38B_HD void load_acts(Acts& a, const uint8_t* aq, const float* ad, int lane) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) a.q[i] = ld_u32(aq + 32 * lane + 4 * i);
-        a.dx = ad[(lane >> 3) * 8];
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, (lane >> 3) * 32);
     }
-    static Q38B_HD float dot(const uint8_t* row, const Acts& a, const Codebook&, int lane) {
-        const uint8_t* p = row + 34 * lane;
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
+        const SP p = row + 34 * lane;
+        const uint32_t mis = sp_low2(p) ^ 2u;                // the int8 values start 2 bytes into the block
         int dot = 0;
+        // 32 bytes from a 2-byte aligned address: nine aligned words, eight funnel shifts
+        const SP wbase = p + 2 - (int)mis;
+        const uint32_t sh = mis * 8;
+        uint32_t prev = sp_ld32(wbase, 0);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint32_t lo, hi;
-            ld_8_a2(p + 2 + 8 * i, lo, hi);
-            dot = dp4a_ss(lo, a.q[2 * i], dot);
-            dot = dp4a_ss(hi, a.q[2 * i + 1], dot);
+        for (int i = 0; i < 8; i++) {
+            const uint32_t next = sp_ld32(wbase, 4 * i + 4);
+            dot = dp4a_ss(funnel_r(prev, next, sh), a.q[i], dot);
+            prev = next;
         }
-        return fp16_bits_to_float(ld_u16(p)) * a.dx * (float)dot;
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * (float)dot;
     }
 };
 

@@ -34,6 +34,7 @@ struct GemvArgs {
     long long y_ld;
     float* y_peer[7];        // the same output position in the other GPUs' buffers (peer stores), n_peers used
     int n_peers;
+    int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;             // device status word (OR of ST_* bits)
     const uint32_t* codebook;   // device copy of the format's codebook (or nullptr)
     int K, M, nb, accumulate;
@@ -73,7 +74,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
     const int chunk_bytes_full = a.chunk_sb * Unit<FMT>::BLOCK_BYTES;
 
     if (warp == 0) {
-        // ---------------- producer: weights do not depend on earlier kernels, start at once ----------------
+        // ---------------- producer: resident weights do not depend on earlier kernels, start at once ----------------
+        if (!a.static_weights) pdl_wait_prior();   // otherwise W may be the output of the kernel before this one
         if (lane < TILE_ROWS) {
             const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
             const uintptr_t safe_end = w_end & ~(uintptr_t)15;

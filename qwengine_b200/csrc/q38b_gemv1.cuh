@@ -23,6 +23,7 @@ struct Gemv1Args {
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     int n_peers;
+    int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;
     const uint32_t* codebook;
     int K, M, accumulate;
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), a.chunk_slices); }
+        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), NWARPS); }
         for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&tbar[t]), a.n_slices);
         mbar_fence_init();
     }
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 
     if (warp == 0) {
         // ---------------- producer ----------------
+        if (!a.static_weights) pdl_wait_prior();   // W may be the output of the kernel before this one
         if (lane < G1_ROWS) {
             const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
             const uintptr_t safe_end = w_end & ~(uintptr_t)15;
@@ -150,10 +152,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     }
     named_bar_sync(15, NWARPS * 32);
 
-    Codebook cb;
-    cb.words = cbw;
-    cb.rep_log2 = a.cb_rep_log2;
-    cb.lane_word = (uint32_t)lane & ((1u << a.cb_rep_log2) - 1u);
+    Codebook1 cb;                                    // 32 replicas: lane l reads bank l
+    cb.lane_base = sp_from(cbw) + 4 * lane;
+    const SP actq_sp = sp_from(actq), actd_sp = sp_from(actd);
+    const SP stage0_sp = sp_from(smem + a.off_stage);
     float* red = (float*)(smem + a.off_red);         // [n_tilebuf][n_slices][8]
 
     constexpr int LPR = Gran<FMT>::LANES_PER_ROW;    // 32, or 16 when two rows share a warp pass
@@ -161,20 +163,29 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     const int sub = LPR == 32 ? 0 : (lane >> 4);     // which of the two rows of a pass this lane works on
 
     const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
+    int seen_item = -1;                              // last stage fill this warp has waited for
     for (int unit = cw; unit < n_units; unit += NWARPS) {
         const int ti = unit / a.n_slices, slice = unit - ti * a.n_slices;
         const int chunk = slice / a.chunk_slices, cslice = slice - chunk * a.chunk_slices;
         const int item = ti * a.n_chunks + chunk;
         const int stage = item % a.n_stages;
-        const uint32_t use = (uint32_t)(item / a.n_stages);
         typename Gran<FMT>::Acts acts;
-        Gran<FMT>::load_acts(acts, actq + slice * 1024, actd + slice * 32, lane);
+        Gran<FMT>::load_acts(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
         // granules past the end of the row (K not a multiple of 1024) contribute nothing
         const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
         const bool live = gran_sb < a.nsb;
-        mbar_wait_bounded(smem_u32(&full[stage]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+        // Every warp passes every stage in order -- waits for its fill and releases it -- also the stages it does not
+        // read.  A parity wait is only meaningful on a barrier the waiter is at most one phase behind or ahead of, and bulk
+        // copies may complete out of order: a warp that skipped stages could otherwise take an old phase for the new one.
+        for (int k = seen_item + 1; k < item; k++) {
+            mbar_wait_bounded(smem_u32(&full[k % a.n_stages]), (uint32_t)(k / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            if (lane == 0) mbar_arrive(smem_u32(&empty[k % a.n_stages]));
+        }
+        if (item > seen_item)
+            mbar_wait_bounded(smem_u32(&full[stage]), (uint32_t)(item / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+        seen_item = item;
         const int tile = (int)blockIdx.x + (int)gridDim.x * ti;
-        const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes + (size_t)cslice * SLICE_BYTES;
+        const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
         // address of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
         const uintptr_t src0 = (uintptr_t)a.W + (uintptr_t)(tile * G1_ROWS) * a.row_bytes +
                                (uintptr_t)(a.contiguous ? 0 : chunk * a.chunk_slices * SLICE_BYTES);
@@ -182,16 +193,17 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
             const int r = LPR == 32 ? ps : 2 * ps + sub;
-            const uint8_t* rowp = st + (size_t)r * a.slot_stride + ((src0 + (a.contiguous ? 0 : (uintptr_t)r * a.row_bytes)) & 15);
+            const SP rowp = st + (r * a.slot_stride + (int)((src0 + (a.contiguous ? 0 : (uintptr_t)r * a.row_bytes)) & 15));
             const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
             acc[ps] = live ? v : 0.0f;
         }
         __syncwarp();
-        if (lane == 0) {
-            // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
-            const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
-            const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
-            mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
+        {
+            // a warp may own several slices of one stage: it releases the stage after the last of them
+            const int nu = unit + NWARPS;
+            const int nti = nu / a.n_slices;
+            const int nitem = nti * a.n_chunks + (nu - nti * a.n_slices) / a.chunk_slices;
+            if (lane == 0 && (nu >= n_units || nitem != item)) mbar_arrive(smem_u32(&empty[stage]));
         }
 
         // sum over the lanes of each row: halving butterflies (each step halves the values a lane holds), then plain ones
@@ -246,6 +258,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             }
             __syncwarp();
         }
+    }
+    // pass the stages after this warp's last unit, so that the producer can refill them for the other warps
+    for (int k = seen_item + 1; k < n_items - a.n_stages; k++) {
+        mbar_wait_bounded(smem_u32(&full[k % a.n_stages]), (uint32_t)(k / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+        if (lane == 0) mbar_arrive(smem_u32(&empty[k % a.n_stages]));
     }
 }
 

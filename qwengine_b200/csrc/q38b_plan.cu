@@ -105,7 +105,20 @@ namespace {
 bool is_f32(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && !p->bufs[id].q8k; }
 bool is_q8k(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && p->bufs[id].q8k; }
 
+int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st);
+
+// matrices of a pass are resident: their producers may run ahead of the previous kernel
 int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
+    const int saved = p->ctx->static_weights, saved_pdl = p->ctx->pdl;
+    p->ctx->static_weights = 1;
+    p->ctx->pdl = p->ctx->pass_pdl;   // inside a pass every matvec follows one of this library's kernels
+    const int rc = enqueue_ops(p, nb, st);
+    p->ctx->static_weights = saved;
+    p->ctx->pdl = saved_pdl;
+    return rc;
+}
+
+int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     q38b_ctx* ctx = p->ctx;
     for (const Op& o : p->ops) {
         int rc = Q38B_OK;

@@ -151,7 +151,7 @@ extern "C" int emul_tile(int fmt, int K, const uint8_t* W, const uint8_t* xq, in
 
 namespace {
 template <int FMT>
-void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* actq, const float* actd, const Codebook* cbs, float* y) {
+void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* actq, const float* actd, const Codebook1* cbs, float* y) {
     constexpr int LPR = Gran<FMT>::LANES_PER_ROW;
     const int nsb = K / 256, n_slices = (nsb + 3) / 4;
     for (int r = 0; r < n_rows; r++) {
@@ -163,8 +163,8 @@ void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* ac
                 const int gran_sb = s * 4 + (LPR == 32 ? (lane >> 3) : (lane >> 2));
                 if (gran_sb >= nsb) continue;
                 typename Gran<FMT>::Acts acts;
-                Gran<FMT>::load_acts(acts, actq + s * 1024, actd + s * 32, lane);
-                ssum += Gran<FMT>::dot(rowp[r] + (size_t)s * 4 * Unit<FMT>::BLOCK_BYTES, acts, cbs[lane], lane);
+                Gran<FMT>::load_acts(acts, sp_from(actq + s * 1024), sp_from(actd + s * 32), lane);
+                ssum += Gran<FMT>::dot(sp_from(rowp[r] + (size_t)s * 4 * Unit<FMT>::BLOCK_BYTES), acts, cbs[lane], lane);
             }
             sum += ssum;
         }
@@ -195,11 +195,11 @@ extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const ui
         for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
     }
     const int entries = fmt == T_IQ3_XXS ? 256 : fmt == T_IQ3_S ? 512 : 0;
-    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) << rep_log2);
-    for (size_t i = 0; i < ((size_t)entries << rep_log2); i++)
-        cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> rep_log2] : q38b_iq3s_grid[i >> rep_log2];
-    Codebook cbs[32];
-    for (int l = 0; l < 32; l++) cbs[l] = Codebook{cb.data(), rep_log2, (uint32_t)l & ((1u << rep_log2) - 1u)};
+    (void)rep_log2;                                        // the single-column kernel always uses 32 replicas
+    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) * 32);
+    for (size_t i = 0; i < (size_t)entries * 32; i++) cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> 5] : q38b_iq3s_grid[i >> 5];
+    Codebook1 cbs[32];
+    for (int l = 0; l < 32; l++) cbs[l] = Codebook1{sp_from(cb.data()) + 4 * l};
     switch (fmt) {
         case T_Q8_0: run_slices<T_Q8_0>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         case T_Q4_K: run_slices<T_Q4_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
