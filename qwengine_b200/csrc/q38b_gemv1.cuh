@@ -52,13 +52,15 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     uint64_t* empty = full + G1_MAX_STAGES;                  // [G1_MAX_STAGES]
     uint64_t* tbar = empty + G1_MAX_STAGES;                  // [G1_MAX_TILEBUF]
     volatile int* abort_flag = (volatile int*)(tbar + G1_MAX_TILEBUF);
+    int* issued = (int*)abort_flag + 1;                      // stage fills the producer has issued so far
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int BB = Unit<FMT>::BLOCK_BYTES;
     constexpr int SLICE_BYTES = 4 * BB;
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), NWARPS); }
+        *issued = 0;
+        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), a.chunk_slices); }
         for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&tbar[t]), a.n_slices);
         mbar_fence_init();
     }
@@ -117,6 +119,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                     }
                 }
                 if (++chunk == a.n_chunks) { chunk = 0; ti++; }
+                __syncwarp((1u << G1_ROWS) - 1u);
+                if (lane == 0) st_release_shared(smem_u32(issued), item + 1);
             }
         }
         return;
@@ -174,15 +178,14 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         // granules past the end of the row (K not a multiple of 1024) contribute nothing
         const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
         const bool live = gran_sb < a.nsb;
-        // Every warp passes every stage in order -- waits for its fill and releases it -- also the stages it does not
-        // read.  A parity wait is only meaningful on a barrier the waiter is at most one phase behind or ahead of, and bulk
-        // copies may complete out of order: a warp that skipped stages could otherwise take an old phase for the new one.
-        for (int k = seen_item + 1; k < item; k++) {
-            mbar_wait_bounded(smem_u32(&full[k % a.n_stages]), (uint32_t)(k / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-            if (lane == 0) mbar_arrive(smem_u32(&empty[k % a.n_stages]));
-        }
-        if (item > seen_item)
+        // A warp reads only some of the stages, so it can reach stage fill `item` while the fill before it of the same
+        // barrier is still in flight (bulk copies complete in any order); a parity wait alone would take that older
+        // phase for this one.  The producer issues a fill only after the readers of the previous use of the barrier have
+        // released it, i.e. after that phase completed: once `issued` has passed `item` the parity is unambiguous.
+        if (item > seen_item) {
+            wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             mbar_wait_bounded(smem_u32(&full[stage]), (uint32_t)(item / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+        }
         seen_item = item;
         const int tile = (int)blockIdx.x + (int)gridDim.x * ti;
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
@@ -198,12 +201,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             acc[ps] = live ? v : 0.0f;
         }
         __syncwarp();
-        {
-            // a warp may own several slices of one stage: it releases the stage after the last of them
-            const int nu = unit + NWARPS;
-            const int nti = nu / a.n_slices;
-            const int nitem = nti * a.n_chunks + (nu - nti * a.n_slices) / a.chunk_slices;
-            if (lane == 0 && (nu >= n_units || nitem != item)) mbar_arrive(smem_u32(&empty[stage]));
+        if (lane == 0) {
+            // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
+            const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
+            const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
+            mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
         }
 
         // sum over the lanes of each row: halving butterflies (each step halves the values a lane holds), then plain ones
@@ -258,11 +260,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             }
             __syncwarp();
         }
-    }
-    // pass the stages after this warp's last unit, so that the producer can refill them for the other warps
-    for (int k = seen_item + 1; k < n_items - a.n_stages; k++) {
-        mbar_wait_bounded(smem_u32(&full[k % a.n_stages]), (uint32_t)(k / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-        if (lane == 0) mbar_arrive(smem_u32(&empty[k % a.n_stages]));
     }
 }
 

@@ -58,6 +58,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// A counter in shared memory that one thread advances (release) and others poll (acquire) until it exceeds `than`.
+__device__ __forceinline__ void st_release_shared(uint32_t addr, int v) {
+    asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_shared(uint32_t addr) {
+    int v;
+    asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_counter_bounded(uint32_t addr, int than, volatile int* abort_flag, int* status, int code,
+                                                     long long budget = WAIT_BUDGET_CYCLES) {
+    if (ld_acquire_shared(addr) > than) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (ld_acquire_shared(addr) > than) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > budget) break;
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned), completion counted on `bar`.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
