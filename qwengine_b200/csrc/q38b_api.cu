@@ -171,7 +171,8 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
     const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 1;
     for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= (cb_entries ? 5 : 0); rep_log2--) {   // this kernel needs all 32 replicas
         a.cb_rep_log2 = rep_log2;
-        a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
+        a.off_sgn = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
+        a.off_red = a.off_sgn + (type == T_IQ3_XXS ? KSIGN_TABLE_BYTES : 0);
         for (int stages = G1_MAX_STAGES; stages >= min_stages; stages--) {
             // tile buffers: a warp can run at most (stages + warps) units ahead of a tile that is still being finished
             const int tb = (G1_WARPS + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;

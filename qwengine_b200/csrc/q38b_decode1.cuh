@@ -84,8 +84,22 @@ Q38B_HD void sp_ld8b_a2(SP p, uint32_t mis, uint32_t& lo, uint32_t& hi) {
 }
 
 // Codebook replicated 32 x in shared memory: entry e for lane l is the word at base + e * 128 + l * 4.
-struct Codebook1 { SP lane_base; };
+// IQ3_XXS also keeps its 128 sign codes there as pairs of byte masks (0xFF where the weight is negative), replicated
+// 16 x: code c for lane l is the 8 bytes at sign_base + c * 128 + (l & 15) * 8 (a 64-bit load is served per half warp).
+struct Codebook1 { SP lane_base; SP sign_base; };
 Q38B_HD uint32_t cb1(const Codebook1& cb, uint32_t e_times_128) { return sp_ld32(cb.lane_base + (int)e_times_128); }
+constexpr int KSIGN_TABLE_BYTES = 128 * 128;
+// masks of sign code c (7 bits + the parity bit that makes the number of negative weights even, ksigns_iq2xs of ggml)
+Q38B_HD void ksign_entry(uint32_t c, uint32_t& lo, uint32_t& hi) {
+    uint32_t sg = c, par = c;
+    par ^= par >> 4; par ^= par >> 2; par ^= par >> 1;
+    sg |= (par & 1u) << 7;
+    lo = 0; hi = 0;
+    for (int j = 0; j < 4; j++) {
+        if ((sg >> j) & 1u) lo |= 0xFFu << (8 * j);
+        if ((sg >> (4 + j)) & 1u) hi |= 0xFFu << (8 * j);
+    }
+}
 
 // byte k of w, times 128 (the stride of a replicated codebook entry)
 Q38B_HD uint32_t byte_x128(uint32_t w, int k) { return (k == 0 ? (w << 7) : (w >> (8 * k - 7))) & 0x7F80u; }
@@ -116,17 +130,17 @@ template <> struct Gran<T_IQ3_XXS> {
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
         const SP p = row + 98 * (lane >> 3);
         const int s = lane & 7;
-        uint32_t iw[2];
-        sp_ld8b_a2(p + (2 + 8 * s), sp_low2(p) ^ 2u, iw[0], iw[1]);   // the indices start 2 bytes into the 2-byte aligned block
+        const SP ip = p + (2 + 8 * s);
         const uint32_t aux = sp_ld16(p, 66 + 4 * s) | (sp_ld16(p, 68 + 4 * s) << 16);
         int P = 0, N = 0;
 #pragma unroll
         for (int l = 0; l < 4; l++) {
-            const uint32_t s7 = (aux >> (7 * l)) & 127u;
-            const uint32_t m_lo = sign_mask4(s7);
-            const uint32_t m_hi = prmt((uint32_t)popc(s7) * 0x80000000u + s7 * 0x00020408u, 0u, 0xBA98u);
-            const uint32_t w = iw[l >> 1];
-            const uint32_t g0 = cb1(cb, byte_x128(w, 2 * (l & 1))), g1 = cb1(cb, byte_x128(w, 2 * (l & 1) + 1));
+            // the index bytes come as single-byte loads (no alignment fix-up, no extraction); 128 * index + base is one
+            // multiply-add; the sign masks come from the table
+            const uint32_t c128 = (l == 0 ? (aux << 7) : (aux >> (7 * l - 7))) & 0x3F80u;
+            uint32_t m_lo, m_hi;
+            sp_ld64(cb.sign_base + (int)c128, 0, m_lo, m_hi);
+            const uint32_t g0 = cb1(cb, sp_ld8(ip, 2 * l) * 128u), g1 = cb1(cb, sp_ld8(ip, 2 * l + 1) * 128u);
             P = dp4a_us(g0, a.q[2 * l], P);
             P = dp4a_us(g1, a.q[2 * l + 1], P);
             N = dp4a_us(g0 & m_lo, a.q[2 * l], N);

@@ -38,7 +38,7 @@ struct Gemv1Args {
     int stage_bytes;
     int n_tilebuf;
     int cb_rep_log2;
-    int off_actd, off_actq, off_cb, off_red, off_stage;
+    int off_actd, off_actq, off_cb, off_sgn, off_red, off_stage;   // off_sgn: IQ3_XXS sign-mask table (KSIGN_TABLE_BYTES)
 };
 
 // ROWS = rows per tile and stage (8 for the thin formats, 4 for the fat ones); two CTAs share an SM so that the
@@ -77,12 +77,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         if (lane < G1_ROWS) {
             const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
             const uintptr_t safe_end = w_end & ~(uintptr_t)15;
-            int ti = 0, chunk = 0;
+            int ti = 0, chunk = 0, stage = 0;
+            uint32_t use = 0;                      // parity of the number of earlier fills of this stage
             for (int item = 0; item < n_items; item++) {
-                const int stage = item % a.n_stages;
-                const uint32_t use = (uint32_t)(item / a.n_stages);
                 const uint32_t fb = smem_u32(&full[stage]);
-                mbar_wait_bounded(smem_u32(&empty[stage]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+                mbar_wait_bounded(smem_u32(&empty[stage]), use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
                 const int row0 = ((int)blockIdx.x + (int)gridDim.x * ti) * G1_ROWS;
                 uint8_t* sbase = smem + a.off_stage + (size_t)stage * a.stage_bytes;
                 // what this lane copies: the whole tile (lane 0, contiguous rows) or its own row's chunk
@@ -119,6 +118,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                     }
                 }
                 if (++chunk == a.n_chunks) { chunk = 0; ti++; }
+                if (++stage == a.n_stages) { stage = 0; use ^= 1u; }
                 __syncwarp((1u << G1_ROWS) - 1u);
                 if (lane == 0) st_release_shared(smem_u32(issued), item + 1);
             }
@@ -136,6 +136,15 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     if (CBN > 0) {
         const int rep = 1 << a.cb_rep_log2;
         for (int i = ctid; i < CBN * rep; i += NWARPS * 32) cbw[i] = a.codebook[i >> a.cb_rep_log2];
+    }
+    if (FMT == T_IQ3_XXS) {
+        uint32_t* sg = (uint32_t*)(smem + a.off_sgn);
+        for (int i = ctid; i < 128 * 16; i += NWARPS * 32) {   // code i / 16, replica i % 16
+            uint32_t lo, hi;
+            ksign_entry((uint32_t)i >> 4, lo, hi);
+            sg[2 * i] = lo;
+            sg[2 * i + 1] = hi;
+        }
     }
     pdl_wait_prior();
     for (int i = ctid; i < a.n_slices * 4; i += NWARPS * 32)
@@ -158,6 +167,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
     cb.lane_base = sp_from(cbw) + 4 * lane;
+    cb.sign_base = sp_from(smem + a.off_sgn) + 8 * (lane & 15);
     const SP actq_sp = sp_from(actq), actd_sp = sp_from(actd);
     const SP stage0_sp = sp_from(smem + a.off_stage);
     float* red = (float*)(smem + a.off_red);         // [n_tilebuf][n_slices][8]
@@ -167,12 +177,20 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     const int sub = LPR == 32 ? 0 : (lane >> 4);     // which of the two rows of a pass this lane works on
 
     const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
+    // The unit's (tile, slice, chunk) and the ring positions of its stage and tile buffer are stepped, never divided.
+    int ti = 0, slice = cw;
+    while (slice >= a.n_slices) { slice -= a.n_slices; ti++; }
+    int chunk = 0, cslice = slice;
+    while (cslice >= a.chunk_slices) { cslice -= a.chunk_slices; chunk++; }
+    int cur_item = 0, stage = 0, cur_ti = 0, tslot = 0;
+    uint32_t stage_par = 0, tile_par = 0;            // parities of the earlier uses of `stage` / `tslot`
     int seen_item = -1;                              // last stage fill this warp has waited for
+    const uint32_t w_lo = (uint32_t)(uintptr_t)a.W, rb32 = (uint32_t)a.row_bytes;
+    const uint32_t rb_step = a.contiguous ? 0u : rb32;   // rows of a contiguous stage share the copy's low address bits
     for (int unit = cw; unit < n_units; unit += NWARPS) {
-        const int ti = unit / a.n_slices, slice = unit - ti * a.n_slices;
-        const int chunk = slice / a.chunk_slices, cslice = slice - chunk * a.chunk_slices;
         const int item = ti * a.n_chunks + chunk;
-        const int stage = item % a.n_stages;
+        while (cur_item < item) { cur_item++; if (++stage == a.n_stages) { stage = 0; stage_par ^= 1u; } }
+        while (cur_ti < ti) { cur_ti++; if (++tslot == a.n_tilebuf) { tslot = 0; tile_par ^= 1u; } }
         typename Gran<FMT>::Acts acts;
         Gran<FMT>::load_acts(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
         // granules past the end of the row (K not a multiple of 1024) contribute nothing
@@ -184,19 +202,18 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         // released it, i.e. after that phase completed: once `issued` has passed `item` the parity is unambiguous.
         if (item > seen_item) {
             wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-            mbar_wait_bounded(smem_u32(&full[stage]), (uint32_t)(item / a.n_stages) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            mbar_wait_bounded(smem_u32(&full[stage]), stage_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
         }
         seen_item = item;
         const int tile = (int)blockIdx.x + (int)gridDim.x * ti;
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
-        // address of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
-        const uintptr_t src0 = (uintptr_t)a.W + (uintptr_t)(tile * G1_ROWS) * a.row_bytes +
-                               (uintptr_t)(a.contiguous ? 0 : chunk * a.chunk_slices * SLICE_BYTES);
+        // low address bits of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
+        const uint32_t src_lo = w_lo + (uint32_t)(tile * G1_ROWS) * rb32 + (a.contiguous ? 0u : (uint32_t)(chunk * a.chunk_slices * SLICE_BYTES));
         float acc[PASSES];
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
             const int r = LPR == 32 ? ps : 2 * ps + sub;
-            const SP rowp = st + (r * a.slot_stride + (int)((src0 + (a.contiguous ? 0 : (uintptr_t)r * a.row_bytes)) & 15));
+            const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
             const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
             acc[ps] = live ? v : 0.0f;
         }
@@ -238,7 +255,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             for (; bit > 0; bit >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, bit);
             if (LPR == 16) myrow = 2 * myrow + sub;
         }
-        const int tslot = ti % a.n_tilebuf;
         float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
         // one lane per row writes: the lanes whose low bits (those folded by the plain butterflies) are zero
         constexpr int LOW_MASK = (LPR == 32 ? 32 : 16) / PASSES - 1;
@@ -248,7 +264,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         if (lane == 0) mbar_arrive(tb);
         if (slice == a.n_slices - 1) {
             // this warp finishes the tile: wait for the other slices, add them in slice order
-            mbar_wait_bounded(tb, (uint32_t)(ti / a.n_tilebuf) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            mbar_wait_bounded(tb, tile_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             const int row = tile * G1_ROWS + lane;
             if (lane < G1_ROWS && row < a.M) {
                 const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
@@ -260,6 +276,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             }
             __syncwarp();
         }
+        slice += NWARPS;
+        while (slice >= a.n_slices) { slice -= a.n_slices; ti++; }
+        chunk = 0;
+        cslice = slice;
+        while (cslice >= a.chunk_slices) { cslice -= a.chunk_slices; chunk++; }
     }
 }
 
