@@ -187,6 +187,14 @@ int q38b_pass_run_host(q38b_pass* pass, int nb, int in_f32, const float* x_host,
 /* Weight bytes one run streams from HBM on this rank (sum over the matvec steps). */
 long long q38b_pass_weight_bytes(const q38b_pass* pass);
 int q38b_pass_kernel_count(const q38b_pass* pass);
+/* Single-column runs (nb = 1) of a pass on one GPU execute as ONE persistent cooperative kernel that streams the
+ * weights of consecutive matvecs without draining between them (bit-identical to the kernel-by-kernel replay, which
+ * remains the path for nb > 1, for several ranks, and for passes whose rows are not packed).  enabled = 0 forces the
+ * kernel-by-kernel replay.  No counterpart in the reference, whose decode loop launches one kernel per op
+ * (src/runtime/engine.cpp:1770-1849). */
+int q38b_pass_set_fused(q38b_pass* pass, int enabled);
+/* 1 when q38b_pass_run(pass, 1, ...) uses the persistent kernel for the steps recorded so far. */
+int q38b_pass_fused_active(q38b_pass* pass);
 
 #ifdef __cplusplus
 }

@@ -86,6 +86,8 @@ def load_library():
     lib.q38b_pass_weight_bytes.argtypes = [vp]
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
+    lib.q38b_pass_set_fused.argtypes = [vp, i32]
+    lib.q38b_pass_fused_active.argtypes = [vp]
     _LIB = lib
     return lib
 
@@ -298,6 +300,14 @@ class Pass:
 
     def set_peer_store(self, enabled):
         self.ctx._rc(self.lib.q38b_pass_set_peer_store(self.h, int(bool(enabled))), "q38b_pass_set_peer_store")
+
+    def set_fused(self, enabled):
+        """enabled=False: single-column runs replay kernel by kernel instead of running as one persistent kernel."""
+        self.ctx._rc(self.lib.q38b_pass_set_fused(self.h, int(bool(enabled))), "q38b_pass_set_fused")
+
+    @property
+    def fused_active(self):
+        return bool(self.lib.q38b_pass_fused_active(self.h))
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -64,40 +64,54 @@ __device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t
 
 constexpr int ACT_WARPS = 8;
 
+// One warp quantizes 256 floats at `src` (lane l holds elements 8l..8l+7) into the Q8_K block at `blk`.
+// COHERENT: read through L2 only (the floats were written by another SM during this kernel).
+template <bool COHERENT>
+__device__ __forceinline__ void quantize_block(const float* src, uint8_t* blk) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = COHERENT ? __ldcg(src + 8 * lane + e) : src[8 * lane + e];
+    q8k_block_from_regs(v, blk);
+}
+
+// h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u; one warp, 256 values.
+template <bool COHERENT>
+__device__ __forceinline__ void swiglu_block(const float* g, const float* u, float* h, uint8_t* blk) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float gv = COHERENT ? __ldcg(g + 8 * lane + e) : g[8 * lane + e];
+        const float uv = COHERENT ? __ldcg(u + 8 * lane + e) : u[8 * lane + e];
+        v[e] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
+    }
+    if (h) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) h[8 * lane + e] = v[e];
+    }
+    if (blk) q8k_block_from_regs(v, blk);
+}
+
 static __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(const float* __restrict__ x, long long x_ld, int K,
                                                                        int n_rows, uint8_t* __restrict__ out,
                                                                        long long out_stride) {
     const int nsb = K >> 8;
     const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
     if (blk >= (long long)n_rows * nsb) return;
-    const int r = (int)(blk / nsb), sb = (int)(blk % nsb), lane = threadIdx.x & 31;
-    const float* src = x + (size_t)r * x_ld + (size_t)sb * 256 + 8 * lane;
-    float v[8];
-#pragma unroll
-    for (int e = 0; e < 8; e++) v[e] = src[e];
-    q8k_block_from_regs(v, out + ((size_t)r * out_stride + sb) * 292);
+    const int r = (int)(blk / nsb), sb = (int)(blk % nsb);
+    quantize_block<false>(x + (size_t)r * x_ld + (size_t)sb * 256, out + ((size_t)r * out_stride + sb) * 292);
 }
 
-// h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u.
 static __global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                                                      long long ld, int n, int n_rows, float* __restrict__ h,
                                                                      uint8_t* __restrict__ out, long long out_stride) {
     const int nsb = n >> 8;
     const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
     if (blk >= (long long)n_rows * nsb) return;
-    const int r = (int)(blk / nsb), sb = (int)(blk % nsb), lane = threadIdx.x & 31;
-    const size_t off = (size_t)r * ld + (size_t)sb * 256 + 8 * lane;
-    float v[8];
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        const float gv = g[off + e];
-        v[e] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), u[off + e]);
-    }
-    if (h) {
-#pragma unroll
-        for (int e = 0; e < 8; e++) h[off + e] = v[e];
-    }
-    if (out) q8k_block_from_regs(v, out + ((size_t)r * out_stride + sb) * 292);
+    const int r = (int)(blk / nsb), sb = (int)(blk % nsb);
+    const size_t off = (size_t)r * ld + (size_t)sb * 256;
+    swiglu_block<false>(g + off, u + off, h ? h + off : nullptr, out ? out + ((size_t)r * out_stride + sb) * 292 : nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -178,10 +178,10 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
             const int tb = (G1_WARPS + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;
             if (tb > G1_MAX_TILEBUF) continue;
             a.off_stage = align_up(a.off_red + tb * a.n_slices * G1_ROWS * 4, 128);
-            if (a.off_stage + stages * a.stage_bytes > budget) continue;
+            if (a.off_stage + stages * a.stage_bytes + align_up(3 * bb, 128) > budget) continue;
             a.n_stages = stages;
             a.n_tilebuf = tb;
-            p->smem = a.off_stage + stages * a.stage_bytes + 128;
+            p->smem = a.off_stage + stages * a.stage_bytes + 128 + align_up(3 * bb, 128);   // granules past a ragged row end are read (and discarded)
             p->grid = std::max(1, std::min(2 * ctx->sm_count, a.n_tiles));
             return Q38B_OK;
         }

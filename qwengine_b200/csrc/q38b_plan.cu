@@ -3,12 +3,16 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <vector>
 
 #include "../../include/q38b200.h"
+#include "q38b_fused.cuh"
 #include "q38b_internal.h"
+
+using namespace q38b;
 
 namespace {
 
@@ -90,6 +94,14 @@ struct q38b_pass {
     float* pin_in = nullptr;
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
+    // single-column passes on one GPU run as one persistent kernel when the ops allow it
+    int fused_mode = 1;          // 0: always replay kernel by kernel
+    int fused_state = 0;         // 0: not planned yet, 1: ready, -1: this pass cannot run fused
+    size_t fused_n_ops = 0;      // ops recorded when the fused plan was made
+    FusedOp* d_fops = nullptr;
+    unsigned* d_done = nullptr;
+    int fused_groups = 0, fused_smem = 0, fused_grid = 0;
+    FusedArgs fargs = {};
 };
 
 #define PASS_CUDA(p, call)                                \
@@ -171,6 +183,198 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     }
     return Q38B_OK;
 }
+}  // namespace
+
+namespace {
+
+struct Access { int buf; long long lo, hi; bool write; };
+
+void op_accesses(const q38b_pass* p, const Op& o, std::vector<Access>& acc) {
+    acc.clear();
+    const long long ALL = 1LL << 40;
+    switch (o.kind) {
+        case OP_QUANT:
+            acc.push_back({o.a, o.off, (long long)o.off + o.n, false});
+            acc.push_back({o.b, 0, ALL, true});
+            break;
+        case OP_GEMV:
+            acc.push_back({o.b, 0, ALL, false});
+            acc.push_back({o.c, o.off, (long long)o.off + p->mats[o.a].M, true});
+            break;
+        case OP_SWIGLU:
+            acc.push_back({o.a, o.off, (long long)o.off + o.n, false});
+            acc.push_back({o.b, o.d, (long long)o.d + o.n, false});
+            acc.push_back({o.c, 0, ALL, true});
+            break;
+        default: break;
+    }
+}
+
+bool conflicts(const std::vector<Access>& x, const std::vector<Access>& y) {
+    for (const Access& a : x)
+        for (const Access& b : y)
+            if (a.buf == b.buf && (a.write || b.write) && a.lo < b.hi && b.lo < a.hi) return true;
+    return false;
+}
+
+// Plans the pass as one persistent kernel: shared-memory carve-up, rows per tile of every matvec, groups and the group
+// each one waits for.  Returns false when the pass has to be replayed kernel by kernel.
+bool plan_fused(q38b_pass* p) {
+    q38b_ctx* ctx = p->ctx;
+    if (ctx->n_ranks > 1 || p->ops.empty()) return false;
+    const int G = ctx->sm_count;
+    bool use_xxs = false, use_s = false;
+    int max_slices = 1;
+    for (const Op& o : p->ops) {
+        if (o.kind != OP_GEMV) continue;
+        const Mat& m = p->mats[o.a];
+        if (m.row_bytes != q38b_row_bytes(m.type, m.K) || m.row_bytes > 0xFFFFFFFFull) return false;   // rows must be packed
+        const int n_slices = (m.K / 256 + 3) / 4;
+        if (n_slices > FU_BAR_COUNT) return false;
+        max_slices = std::max(max_slices, n_slices);
+        use_xxs |= m.type == T_IQ3_XXS;
+        use_s |= m.type == T_IQ3_S;
+    }
+    FusedArgs& a = p->fargs;
+    a = FusedArgs{};
+    auto up = [](int v) { return (v + 127) & ~127; };
+    a.max_slices = max_slices;
+    a.off_actd = FU_HEADER_BYTES;
+    a.off_actq = a.off_actd + max_slices * 128;
+    int off = a.off_actq + max_slices * 1024;
+    a.off_cb_xxs = a.off_sgn = a.off_cb_s = 0;
+    if (use_xxs) { a.off_cb_xxs = off; off += 256 * 128; a.off_sgn = off; off += KSIGN_TABLE_BYTES; }
+    if (use_s) { a.off_cb_s = off; off += 512 * 128; }
+    a.off_red = off;
+    off = up(off + FU_MAX_TILEBUF * max_slices * 8 * 4);
+    a.off_stage = off;
+    const int ring = ctx->smem_optin - off;
+    if (ring / 24576 >= 4) a.slot_bytes = 24576;
+    else if (ring / 16384 >= 3) a.slot_bytes = 16384;
+    else return false;
+    a.n_stages = std::min(FU_MAX_STAGES, ring / a.slot_bytes);
+    a.n_tilebuf = std::min(FU_MAX_TILEBUF, a.n_stages + 18);
+    p->fused_smem = a.off_stage + a.n_stages * a.slot_bytes;
+
+    std::vector<FusedOp> fops;
+    std::vector<std::vector<Access>> accs;     // per fused op
+    std::vector<int> group_first;              // index of the first op of each group
+    std::vector<Access> acc;
+    long long tiles_so_far = 0;
+    int cur_src = -1, cur_permute = -1;        // input of the current matvec group, -1: the current group is not one
+    for (const Op& o : p->ops) {
+        if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;   // single GPU: nothing to exchange
+        FusedOp f = {};
+        op_accesses(p, o, acc);
+        bool new_group = true;
+        if (o.kind == OP_GEMV) {
+            const Mat& m = p->mats[o.a];
+            int n_rl = 0;
+            const int* rls = fused_rows_log2((int)m.type, &n_rl);
+            int rl = -1;
+            for (int i = 0; i < n_rl && rl < 0; i++)
+                if (((size_t)m.row_bytes << rls[i]) + 3 * q38b_row_bytes(m.type, 256) + 48 <= (size_t)a.slot_bytes) rl = rls[i];   // granules past a ragged row end are read (and discarded)
+            if (rl < 0) return false;
+            f.kind = FOP_GEMV;
+            f.fmt = (int)m.type;
+            f.rows_log2 = rl;
+            f.M = m.M;
+            f.nsb = m.K / 256;
+            f.n_tiles = (m.M + (1 << rl) - 1) >> rl;
+            f.tile_rot = (int)(tiles_so_far % G);
+            tiles_so_far += f.n_tiles;
+            f.row_bytes = (unsigned)m.row_bytes;
+            f.a = m.W;
+            f.b = p->bufs[o.b].ptr;
+            f.out = (float*)p->bufs[o.c].ptr + o.off;
+            const int permute = m.type == T_IQ4_XS;
+            if (cur_src == o.b && cur_permute == permute) {
+                new_group = false;
+                for (size_t k = group_first.back(); k < fops.size(); k++)
+                    if (conflicts(acc, accs[k])) new_group = true;
+            }
+            cur_src = o.b;
+            cur_permute = permute;
+        } else if (o.kind == OP_QUANT) {
+            f.kind = FOP_QUANT;
+            f.nsb = o.n / 256;
+            f.a = (const float*)p->bufs[o.a].ptr + o.off;
+            f.out = p->bufs[o.b].ptr;
+            cur_src = -1;
+        } else {
+            f.kind = FOP_SWIGLU;
+            f.nsb = o.n / 256;
+            f.a = (const float*)p->bufs[o.a].ptr + o.off;
+            f.b = (const float*)p->bufs[o.b].ptr + o.d;
+            f.out = p->bufs[o.c].ptr;
+            cur_src = -1;
+        }
+        if (new_group) group_first.push_back((int)fops.size());
+        f.group = (int)group_first.size() - 1;
+        f.wait_group = -1;
+        fops.push_back(f);
+        accs.push_back(acc);
+    }
+    if (fops.empty()) return false;
+    // a group waits for the latest earlier group any of its ops conflicts with (groups complete in order on every CTA)
+    for (size_t j = 0; j < fops.size(); j++) {
+        int wait = -1;
+        for (size_t k = 0; k < (size_t)group_first[fops[j].group]; k++)
+            if (fops[k].group > wait && conflicts(accs[j], accs[k])) wait = fops[k].group;
+        FusedOp& head = fops[group_first[fops[j].group]];
+        head.wait_group = std::max(head.wait_group, wait);
+    }
+    p->fused_groups = (int)group_first.size();
+
+    auto kern = fused_pass_kernel;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->fused_smem) != cudaSuccess) { cudaGetLastError(); return false; }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FU_THREADS, p->fused_smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); return false; }
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device);
+    if (!coop) return false;
+    p->fused_grid = G;
+    if (p->d_fops) cudaFree(p->d_fops);
+    if (p->d_done) cudaFree(p->d_done);
+    p->d_fops = nullptr;
+    p->d_done = nullptr;
+    if (cudaMalloc(&p->d_fops, fops.size() * sizeof(FusedOp)) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMalloc(&p->d_done, (size_t)p->fused_groups * sizeof(unsigned)) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMemcpy(p->d_fops, fops.data(), fops.size() * sizeof(FusedOp), cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); return false; }
+    a.ops = p->d_fops;
+    a.n_ops = (int)fops.size();
+    a.done = p->d_done;
+    a.status = ctx->d_status;
+    a.cb_xxs = use_xxs ? ctx->d_cb_iq3xxs : nullptr;
+    a.cb_s = use_s ? ctx->d_cb_iq3s : nullptr;
+    return true;
+}
+
+bool fused_ready(q38b_pass* p) {
+    if (!p->fused_mode) return false;
+    if (p->fused_state == 0 || p->fused_n_ops != p->ops.size()) {
+        p->fused_state = plan_fused(p) ? 1 : -1;
+        p->fused_n_ops = p->ops.size();
+    }
+    return p->fused_state == 1;
+}
+
+int launch_fused(q38b_pass* p, cudaStream_t st) {
+    PASS_CUDA(p, cudaMemsetAsync(p->d_done, 0, (size_t)p->fused_groups * sizeof(unsigned), st));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p->fused_grid);
+    cfg.blockDim = dim3(FU_THREADS);
+    cfg.dynamicSmemBytes = (size_t)p->fused_smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs resident: the group waits cannot starve
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PASS_CUDA(p, cudaLaunchKernelEx(&cfg, fused_pass_kernel, p->fargs));
+    return Q38B_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -291,6 +495,8 @@ void q38b_pass_destroy(q38b_pass* p) {
     if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
     if (p->pin_in) cudaFreeHost(p->pin_in);
     if (p->pin_out) cudaFreeHost(p->pin_out);
+    if (p->d_fops) cudaFree(p->d_fops);
+    if (p->d_done) cudaFree(p->d_done);
     delete p;
 }
 
@@ -384,6 +590,7 @@ int q38b_pass_op_allgather(q38b_pass* p, int buf, int off, int count) {
 int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    if (nb == 1 && fused_ready(p)) return launch_fused(p, st);
     if (!p->graphs[nb]) {
         cudaGraph_t g = nullptr;
         if (!p->cap_stream) PASS_CUDA(p, cudaStreamCreateWithFlags(&p->cap_stream, cudaStreamNonBlocking));
@@ -436,6 +643,14 @@ long long q38b_pass_weight_bytes(const q38b_pass* p) {
         if (o.kind == OP_GEMV) b += (long long)p->mats[o.a].M * (long long)q38b_row_bytes(p->mats[o.a].type, p->mats[o.a].K);
     return b;
 }
+
+int q38b_pass_set_fused(q38b_pass* p, int enabled) {
+    if (!p) return Q38B_ERR_ARG;
+    p->fused_mode = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+
+int q38b_pass_fused_active(q38b_pass* p) { return p && fused_ready(p) ? 1 : 0; }
 
 int q38b_pass_kernel_count(const q38b_pass* p) {
     if (!p) return 0;

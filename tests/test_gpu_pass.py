@@ -76,3 +76,71 @@ def test_upload_shards_cover_all_rows(ctx):
             out[0, rows] = y[0, rows]
             ps.close()
         assert np.array_equal(out.view(np.uint32), full.view(np.uint32))
+
+
+def test_fused_pass_equals_kernel_by_kernel_replay(ctx):
+    """The persistent single-kernel pass gives the bits of the kernel-by-kernel replay of the same steps."""
+    n_layers = 4
+    ws = small_weights(n_layers, 0)
+    x = synth.make_activations(1, dp.HIDDEN, seed=11)
+    outs = []
+    for fused in (True, False):
+        ps = q.Pass(ctx, max_nb=1)
+        ps.set_fused(fused)
+        io = dp.build(ps, lambda spec, rows: ps.matrix_upload(spec.fmt, ws[spec.name], spec.K), n_layers=n_layers, head=False)
+        assert ps.fused_active == fused
+        y = np.empty((1, dp.HIDDEN), np.float32)
+        for _ in range(3):   # replays reuse the group counters
+            ps.run_host(1, io["in_buf"], x, io["out_buf"], 0, y)
+        ctx.check()
+        outs.append(y.copy())
+        ps.close()
+    assert np.isfinite(outs[0]).all()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+def _fused_cases(ctx, cases):
+    ps = q.Pass(ctx, max_nb=1)
+    xin, xq = ps.buffer_f32(5120), ps.buffer_q8k(5120)
+    xin2, xq2 = ps.buffer_f32(17408), ps.buffer_q8k(17408)
+    ps.quantize(xin, 0, 5120, xq)
+    ps.quantize(xin2, 0, 17408, xq2)
+    ybufs, wts = [], []
+    for i, (fmt, M, K) in enumerate(cases):
+        w = synth.make_weights(fmt, M, K, seed=900 + i)
+        wts.append(w)
+        yb = ps.buffer_f32(M)
+        ybufs.append(yb)
+        ps.gemv(ps.matrix_upload(fmt, w, K), xq if K == 5120 else xq2, yb, 0)
+    assert ps.fused_active
+    x1 = torch.from_numpy(synth.make_activations(1, 5120, seed=3)).cuda()
+    x2 = torch.from_numpy(synth.make_activations(1, 17408, seed=4)).cuda()
+    ps.buffer_tensor(xin).copy_(x1)
+    ps.buffer_tensor(xin2).copy_(x2)
+    ps.run(1)
+    torch.cuda.synchronize()
+    ctx.check()
+    q1, q2 = ctx.quantize_q8k(x1), ctx.quantize_q8k(x2)
+    for (fmt, M, K), w, yb in zip(cases, wts, ybufs):
+        want = ctx.gemv(fmt, torch.from_numpy(w).cuda(), q1 if K == 5120 else q2, K)
+        got = ps.buffer_tensor(yb)
+        if fmt == "IQ3_S" or (fmt == "IQ3_XXS" and K > 8192):
+            # called alone, these single-column matvecs run on the tensor-core kernel (replicated codebook + activations
+            # do not fit two CTAs per SM): another summation order, the same exact integer sums
+            assert float((got - want).abs().max()) <= 2e-5 * float(want.abs().max()), (fmt, M, K)
+        else:
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (fmt, M, K)
+    ps.close()
+
+
+def test_fused_pass_all_formats(ctx):
+    """One quantize step feeding matvecs of every format (ragged row counts) through the persistent kernel, against the
+    same matvecs called one by one."""
+    _fused_cases(ctx, [("IQ3_XXS", 1000, 5120), ("IQ3_S", 333, 5120), ("IQ4_XS", 1024, 5120), ("Q4_K", 2051, 5120),
+                       ("Q5_K", 515, 5120), ("Q6_K", 777, 5120), ("Q8_0", 130, 5120), ("Q4_K", 7, 5120)])
+
+
+def test_fused_pass_long_rows(ctx):
+    """Rows too long for eight- or four-row tiles take two-row tiles; mixed with short rows and a second input vector."""
+    _fused_cases(ctx, [("IQ3_XXS", 1000, 5120), ("IQ4_XS", 517, 17408), ("Q4_K", 2051, 5120), ("IQ3_XXS", 64, 17408),
+                       ("Q4_K", 100, 17408), ("Q5_K", 33, 17408), ("Q6_K", 777, 5120), ("Q8_0", 130, 5120)])
