@@ -195,6 +195,12 @@ int q38b_pass_kernel_count(const q38b_pass* pass);
 int q38b_pass_set_fused(q38b_pass* pass, int enabled);
 /* 1 when q38b_pass_run(pass, 1, ...) uses the persistent kernel for the steps recorded so far. */
 int q38b_pass_fused_active(q38b_pass* pass);
+/* Tracing of the persistent kernel.  enable = 1 switches cycle counters on for later runs; counters10 (may be NULL)
+ * receives and clears them after synchronising the device: [0] cycles consumer warps waited for weight tiles,
+ * [1] for the other slices of a tile, [2] at group boundaries, [3] consumer-warp cycles in total, [4] cycles the
+ * producers waited for ring space, [5] tiles copied, [6] (tile, slice) units, [7] producer cycles in total, [8] the part of [2] spent waiting for the
+ * CTA's own warps, [9] the part of [2] spent waiting for the other CTAs. */
+int q38b_pass_fused_trace(q38b_pass* pass, int enable, unsigned long long* counters10);
 
 #ifdef __cplusplus
 }

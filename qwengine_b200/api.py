@@ -88,6 +88,7 @@ def load_library():
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_fused.argtypes = [vp, i32]
     lib.q38b_pass_fused_active.argtypes = [vp]
+    lib.q38b_pass_fused_trace.argtypes = [vp, i32, vp]
     _LIB = lib
     return lib
 
@@ -308,6 +309,17 @@ class Pass:
     @property
     def fused_active(self):
         return bool(self.lib.q38b_pass_fused_active(self.h))
+
+    def fused_trace(self, enable=True, read=False):
+        """Switches the persistent kernel's cycle counters on or off; read=True returns and clears them (dict)."""
+        import ctypes
+        buf = (ctypes.c_ulonglong * 10)() if read else None
+        self.ctx._rc(self.lib.q38b_pass_fused_trace(self.h, int(bool(enable)), buf), "q38b_pass_fused_trace")
+        if not read:
+            return None
+        names = ["wait_tile_cycles", "wait_slices_cycles", "group_cycles", "consumer_cycles", "producer_space_cycles", "tiles", "units",
+                 "producer_cycles", "group_barrier_cycles", "group_dependency_cycles"]
+        return dict(zip(names, [int(v) for v in buf]))
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -22,8 +22,10 @@ namespace q38b {
 
 constexpr int FU_WARPS = 16;                      // consumer warps
 constexpr int FU_THREADS = 32 * (1 + FU_WARPS);
-constexpr int FU_MAX_STAGES = 16;
+constexpr int FU_MAX_STAGES = 16;                 // stage barriers; stage fill i uses barrier i % 16
+constexpr int FU_MAX_INFLIGHT = 12;               // stage fills not yet released by their readers
 constexpr int FU_MAX_TILEBUF = 32;
+constexpr int FU_RING_SLACK = 1024;               // granules past a ragged row end are read (and discarded)
 constexpr int FU_BAR_COUNT = 32;                  // arrivals a stage / tile barrier expects = most slices a row may have
 constexpr int FU_HEADER_BYTES = 1024;
 
@@ -53,10 +55,15 @@ struct FusedArgs {
     const uint32_t* cb_xxs;   // IQ3_XXS grid (256) or nullptr when the pass has no such matrix
     const uint32_t* cb_s;     // IQ3_S grid (512) or nullptr
     int off_actd, off_actq, off_cb_xxs, off_sgn, off_cb_s, off_red, off_stage;
-    int slot_bytes, n_stages, n_tilebuf, max_slices;
+    unsigned long long* prof;   // optional [FU_PROF_N] cycle counters summed over all warps (tracing), or nullptr
+    int ring_bytes, n_tilebuf, max_slices;   // the ring holds tiles of any size back to back (128-byte granularity)
 };
 
+// tracing counters: cycles consumer warps spent waiting for a stage fill, for the other slices of a tile, at group
+// boundaries, and in total; cycles the producer waited for ring space; stage fills; units
+enum { FU_PROF_FULL = 0, FU_PROF_TILE, FU_PROF_GROUP, FU_PROF_TOTAL, FU_PROF_SPACE, FU_PROF_FILLS, FU_PROF_UNITS, FU_PROF_PRODUCER, FU_PROF_GROUP_BAR, FU_PROF_GROUP_DEP, FU_PROF_N };
 constexpr int ST_FUSED_DEP_TIMEOUT = 32;
+constexpr int ST_FUSED_BOUNDS = 64;
 
 template <class T>
 __device__ __forceinline__ T* ldg_ptr(T* const* pp) { return (T*)__ldg((const unsigned long long*)pp); }
@@ -76,7 +83,7 @@ __device__ __forceinline__ bool wait_done(const unsigned* ctr, unsigned target, 
         if (ld_acquire_gpu(ctr) >= target) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
-        __nanosleep(64);
+        __nanosleep(32);
     }
     *abort_flag = 1;
     if (status) atomicOr(status, ST_FUSED_DEP_TIMEOUT);
@@ -91,12 +98,15 @@ struct FuWarp {
     int cur_tile, tslot;                   // tile buffer of tile cur_tile
     uint32_t tile_par;
     int seen_item;                         // last stage fill this warp has waited for
+    long long t_full, t_tile;              // tracing
+    int n_units;
 };
 
 struct FuShared {
     uint8_t* smem;
     uint64_t *full, *empty, *tbar;
     int* issued;
+    int* item_off;      // [FU_MAX_STAGES] ring offset of the stage fill that uses each barrier
     volatile int* abort_flag;
 };
 
@@ -130,7 +140,7 @@ __device__ __forceinline__ void fu_gemv(const FusedArgs& a, const FusedOp* op, F
     while (slice >= n_slices) { slice -= n_slices; ti++; }
     for (; u < n_units; u += FU_WARPS) {
         const int item = w.item_base + ti;
-        while (w.cur_item < item) { w.cur_item++; if (++w.stage == a.n_stages) { w.stage = 0; w.stage_par ^= 1u; } }
+        while (w.cur_item < item) { w.cur_item++; if (++w.stage == FU_MAX_STAGES) { w.stage = 0; w.stage_par ^= 1u; } }
         const int gtile = w.tile_base + ti;
         while (w.cur_tile < gtile) { w.cur_tile++; if (++w.tslot == a.n_tilebuf) { w.tslot = 0; w.tile_par ^= 1u; } }
         typename Gran<FMT>::Acts acts;
@@ -139,13 +149,20 @@ __device__ __forceinline__ void fu_gemv(const FusedArgs& a, const FusedOp* op, F
         const bool live = gran_sb < nsb;
         // the counter of issued fills makes the parity wait unambiguous for a warp that skipped uses of this barrier
         if (item > w.seen_item) {
+            const long long t0 = a.prof ? clock64() : 0;
             wait_counter_bounded(smem_u32(sh.issued), item, sh.abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             mbar_wait_bounded(smem_u32(&sh.full[w.stage]), w.stage_par, sh.abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            if (a.prof) w.t_full += clock64() - t0;
         }
+        w.n_units++;
         w.seen_item = item;
         const int tile = first + G * ti;
-        const SP st = stage0_sp + (w.stage * a.slot_bytes + slice * SLICE_BYTES);
         const int mis = (int)((w_lo + (uint32_t)(tile * ROWS) * rb32) & 15u);   // the copy kept the low 4 address bits
+        // a tile that would not lie inside the ring is skipped and reported (a planner or ring bookkeeping error)
+        const int tile_off = (int)sp_ld32(sp_from(sh.item_off), 4 * w.stage);
+        const bool in_ring = tile_off >= 0 && (tile_off & 127) == 0 && tile_off + ROWS * (int)rb32 + mis <= a.ring_bytes;
+        if (!in_ring && lane == 0) atomicOr(a.status, ST_FUSED_BOUNDS);
+        const SP st = stage0_sp + ((in_ring ? tile_off : 0) + slice * SLICE_BYTES);
         float acc[PASSES];
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
@@ -194,7 +211,9 @@ __device__ __forceinline__ void fu_gemv(const FusedArgs& a, const FusedOp* op, F
         const uint32_t tb = smem_u32(&sh.tbar[w.tslot]);
         if (lane == 0) mbar_arrive_n(tb, n_arr);
         if (slice == n_slices - 1) {
+            const long long t0 = a.prof ? clock64() : 0;
             mbar_wait_bounded(tb, w.tile_par, sh.abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            if (a.prof) w.t_tile += clock64() - t0;
             const int row = tile * ROWS + lane;
             if (lane < ROWS && row < M) {
                 const float* rs = red + (size_t)w.tslot * a.max_slices * 8 + lane;
@@ -221,13 +240,14 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
     sh.tbar = sh.empty + FU_MAX_STAGES;                     // [FU_MAX_TILEBUF]
     sh.abort_flag = (volatile int*)(sh.tbar + FU_MAX_TILEBUF);
     sh.issued = (int*)sh.abort_flag + 1;
+    sh.item_off = sh.issued + 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = (int)gridDim.x;
 
     if (tid == 0) {
         *sh.abort_flag = 0;
         *sh.issued = 0;
-        for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&sh.full[s]), 1); mbar_init(smem_u32(&sh.empty[s]), FU_BAR_COUNT); }
+        for (int s = 0; s < FU_MAX_STAGES; s++) { mbar_init(smem_u32(&sh.full[s]), 1); mbar_init(smem_u32(&sh.empty[s]), FU_BAR_COUNT); }
         for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&sh.tbar[t]), FU_BAR_COUNT);
         mbar_fence_init();
     }
@@ -236,8 +256,10 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
     if (warp == 0) {
         // ---------------- producer: one lane, one bulk copy per tile ----------------
         if (lane == 0) {
-            int item = 0, stage = 0;
-            uint32_t use = 0;
+            // The ring is a byte FIFO: tiles of any size lie back to back, space is reclaimed in issue order.
+            int item = 0, head = 0, tail_item = 0, n_in = 0;
+            long long t_space = 0;
+            const long long t_begin = a.prof ? clock64() : 0;
             for (int oi = 0; oi < a.n_ops; oi++) {
                 const FusedOp* op = a.ops + oi;
                 if (__ldg(&op->kind) != FOP_GEMV) continue;
@@ -249,14 +271,47 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
                 int first = (int)blockIdx.x - __ldg(&op->tile_rot);
                 if (first < 0) first += G;
                 for (int t = first; t < n_tiles; t += G) {
-                    const uint32_t fb = smem_u32(&sh.full[stage]);
-                    mbar_wait_bounded(smem_u32(&sh.empty[stage]), use ^ 1u, sh.abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
                     const int row0 = t << rl;
                     const uintptr_t src = W + (uintptr_t)row0 * rb;
                     const long long len = (long long)min(1 << rl, M - row0) * rb;
-                    uint8_t* slot = sh.smem + a.off_stage + (size_t)stage * a.slot_bytes;
                     const uintptr_t lo = src & ~(uintptr_t)15;
                     uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
+                    // room for a whole tile even when the matrix ends inside it: the consumers read all its rows
+                    const int sz = (int)(((src & 15) + ((uintptr_t)rb << rl) + 15 + 127) & ~(uintptr_t)127);
+                    int pos = 0;
+                    for (;;) {
+                        bool ok = false;
+                        if (n_in == 0) { pos = 0; ok = true; }
+                        else {
+                            const int tail = sh.item_off[tail_item & (FU_MAX_STAGES - 1)];
+                            if (head > tail) {                       // in use: [tail, head)
+                                if (a.ring_bytes - head >= sz) { pos = head; ok = true; }
+                                else if (tail >= sz) { pos = 0; ok = true; }
+                            } else if (tail - head >= sz) {          // in use: [tail, end) and [0, head)
+                                pos = head;
+                                ok = true;
+                            }
+                        }
+                        if (ok && n_in < FU_MAX_INFLIGHT) break;
+                        // reclaim the oldest fill once all its readers have released it
+                        const long long t0 = a.prof ? clock64() : 0;
+                        mbar_wait_bounded(smem_u32(&sh.empty[tail_item & (FU_MAX_STAGES - 1)]), (uint32_t)(tail_item >> 4) & 1u, sh.abort_flag,
+                                          a.status, ST_WAIT_EMPTY_TIMEOUT);
+                        if (a.prof) t_space += clock64() - t0;
+                        tail_item++;
+                        n_in--;
+                    }
+                    if (pos < 0 || pos + sz > a.ring_bytes) {   // cannot happen: reported, the copy is skipped
+                        atomicOr(a.status, ST_FUSED_BOUNDS);
+                        *sh.abort_flag = 1;
+                        return;
+                    }
+                    const int bi = item & (FU_MAX_STAGES - 1);
+                    sh.item_off[bi] = pos;
+                    head = pos + sz;
+                    n_in++;
+                    const uint32_t fb = smem_u32(&sh.full[bi]);
+                    uint8_t* slot = sh.smem + a.off_stage + pos;
                     if (hi > safe_end) {   // the tensor's last bytes do not fill a 16-byte unit: plain loads
                         hi = safe_end > lo ? safe_end : lo;
                         for (uintptr_t p = hi; p < src + len; p += 2)
@@ -270,8 +325,12 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
                         mbar_arrive(fb);
                     }
                     st_release_shared(smem_u32(sh.issued), ++item);
-                    if (++stage == a.n_stages) { stage = 0; use ^= 1u; }
                 }
+            }
+            if (a.prof) {
+                atomicAdd(a.prof + FU_PROF_SPACE, (unsigned long long)t_space);
+                atomicAdd(a.prof + FU_PROF_FILLS, (unsigned long long)item);
+                atomicAdd(a.prof + FU_PROF_PRODUCER, (unsigned long long)(clock64() - t_begin));
             }
         }
         return;
@@ -308,6 +367,10 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
     w.cur_tile = w.tslot = 0;
     w.tile_par = 0;
     w.seen_item = -1;
+    w.t_full = w.t_tile = 0;
+    w.n_units = 0;
+    long long t_group = 0, t_gbar = 0, t_gdep = 0;
+    const long long t_begin = a.prof ? clock64() : 0;
     float* actd = (float*)(sh.smem + a.off_actd);
     uint8_t* actq = sh.smem + a.off_actq;
 
@@ -317,13 +380,22 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
         const int kind = __ldg(&op->kind), group = __ldg(&op->group);
         if (group != prev_group) {
             // everything this CTA did for the previous group is written; the activation area is free
+            const long long tg0 = a.prof ? clock64() : 0;
             named_bar_sync(1, NCT);
+            const long long tg1 = a.prof ? clock64() : 0;
             if (prev_group >= 0 && ctid == 0) {
                 __threadfence();
                 atomicAdd(a.done + prev_group, 1u);
             }
+            // one thread per CTA polls the counter (thousands of pollers on one address would queue up in L2 in front of
+            // the arrivals they wait for); the others wait for it at a second barrier
             const int wg = __ldg(&op->wait_group);
-            if (wg >= 0) wait_done(a.done + wg, (unsigned)G, sh.abort_flag, a.status);
+            if (wg >= 0) {
+                if (ctid == 0) wait_done(a.done + wg, (unsigned)G, sh.abort_flag, a.status);
+                named_bar_sync(3, NCT);
+            }
+            const long long tg2 = a.prof ? clock64() : 0;
+            if (a.prof) { t_gbar += tg1 - tg0; t_gdep += tg2 - tg1; }
             prev_group = group;
             if (kind == FOP_GEMV) {
                 // stage the activation vector (written by other SMs during this kernel: read it through L2)
@@ -348,6 +420,7 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
                 }
                 named_bar_sync(2, NCT);
             }
+            if (a.prof) t_group += clock64() - tg0;
         }
         if (kind == FOP_QUANT) {
             const float* src = (const float*)ldg_ptr(&op->a);
@@ -367,18 +440,24 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
 #define FU_CASE(F, RL, CB) case (F) * 8 + (RL): fu_gemv<F, (1 << (RL))>(a, op, w, sh, CB, cw, lane); break;
             switch (key) {
                 FU_CASE(T_IQ3_XXS, 3, cb_xxs)
+                FU_CASE(T_IQ3_XXS, 2, cb_xxs)
                 FU_CASE(T_IQ3_XXS, 1, cb_xxs)
                 FU_CASE(T_IQ3_S, 3, cb_s)
+                FU_CASE(T_IQ3_S, 2, cb_s)
                 FU_CASE(T_IQ3_S, 1, cb_s)
                 FU_CASE(T_IQ4_XS, 3, cb_xxs)
+                FU_CASE(T_IQ4_XS, 2, cb_xxs)
                 FU_CASE(T_IQ4_XS, 1, cb_xxs)
                 FU_CASE(T_Q4_K, 3, cb_xxs)
                 FU_CASE(T_Q4_K, 2, cb_xxs)
                 FU_CASE(T_Q4_K, 1, cb_xxs)
+                FU_CASE(T_Q5_K, 3, cb_xxs)
                 FU_CASE(T_Q5_K, 2, cb_xxs)
                 FU_CASE(T_Q5_K, 1, cb_xxs)
+                FU_CASE(T_Q6_K, 3, cb_xxs)
                 FU_CASE(T_Q6_K, 2, cb_xxs)
                 FU_CASE(T_Q6_K, 1, cb_xxs)
+                FU_CASE(T_Q8_0, 3, cb_xxs)
                 FU_CASE(T_Q8_0, 2, cb_xxs)
                 FU_CASE(T_Q8_0, 1, cb_xxs)
                 default: break;   // the planner never emits another combination
@@ -386,15 +465,18 @@ __global__ void __launch_bounds__(FU_THREADS, 1) fused_pass_kernel(const FusedAr
 #undef FU_CASE
         }
     }
+    if (a.prof && lane == 0) {
+        atomicAdd(a.prof + FU_PROF_FULL, (unsigned long long)w.t_full);
+        atomicAdd(a.prof + FU_PROF_TILE, (unsigned long long)w.t_tile);
+        atomicAdd(a.prof + FU_PROF_GROUP, (unsigned long long)t_group);
+        atomicAdd(a.prof + FU_PROF_GROUP_BAR, (unsigned long long)t_gbar);
+        atomicAdd(a.prof + FU_PROF_GROUP_DEP, (unsigned long long)t_gdep);
+        atomicAdd(a.prof + FU_PROF_TOTAL, (unsigned long long)(clock64() - t_begin));
+        atomicAdd(a.prof + FU_PROF_UNITS, (unsigned long long)w.n_units);
+    }
 }
 
-// rows-per-tile exponents the kernel is instantiated for, largest first
-inline const int* fused_rows_log2(int fmt, int* n) {
-    static const int thin[] = {3, 1}, q4k[] = {3, 2, 1}, fat[] = {2, 1};
-    if (fmt == T_IQ3_XXS || fmt == T_IQ3_S || fmt == T_IQ4_XS) { *n = 2; return thin; }
-    if (fmt == T_Q4_K) { *n = 3; return q4k; }
-    *n = 2;
-    return fat;
-}
+// rows-per-tile exponents the kernel is instantiated for (every format), largest first
+constexpr int FU_ROWS_LOG2[3] = {3, 2, 1};
 
 }  // namespace q38b

@@ -100,6 +100,7 @@ struct q38b_pass {
     size_t fused_n_ops = 0;      // ops recorded when the fused plan was made
     FusedOp* d_fops = nullptr;
     unsigned* d_done = nullptr;
+    unsigned long long* d_prof = nullptr;   // tracing counters of the persistent kernel (q38b_pass_fused_trace)
     int fused_groups = 0, fused_smem = 0, fused_grid = 0;
     FusedArgs fargs = {};
 };
@@ -248,13 +249,11 @@ bool plan_fused(q38b_pass* p) {
     a.off_red = off;
     off = up(off + FU_MAX_TILEBUF * max_slices * 8 * 4);
     a.off_stage = off;
-    const int ring = ctx->smem_optin - off;
-    if (ring / 24576 >= 4) a.slot_bytes = 24576;
-    else if (ring / 16384 >= 3) a.slot_bytes = 16384;
-    else return false;
-    a.n_stages = std::min(FU_MAX_STAGES, ring / a.slot_bytes);
-    a.n_tilebuf = std::min(FU_MAX_TILEBUF, a.n_stages + 18);
-    p->fused_smem = a.off_stage + a.n_stages * a.slot_bytes;
+    a.ring_bytes = ((ctx->smem_optin - off - FU_RING_SLACK) / 128) * 128;
+    if (a.ring_bytes < 64 * 1024) return false;
+    a.n_tilebuf = FU_MAX_TILEBUF;
+    p->fused_smem = a.off_stage + a.ring_bytes + FU_RING_SLACK;
+    const size_t tile_cap = std::min<size_t>(24 * 1024, (size_t)a.ring_bytes / 4);
 
     std::vector<FusedOp> fops;
     std::vector<std::vector<Access>> accs;     // per fused op
@@ -269,11 +268,17 @@ bool plan_fused(q38b_pass* p) {
         bool new_group = true;
         if (o.kind == OP_GEMV) {
             const Mat& m = p->mats[o.a];
-            int n_rl = 0;
-            const int* rls = fused_rows_log2((int)m.type, &n_rl);
+            // Throughput is (bytes in flight) / latency: the tiles the 16 warps are working on pin their ring space, so
+            // they should take well under half of it.  A (tile, slice) unit goes to one warp: ceil(16 / slices) + 1
+            // tiles are being read at any time.  Largest tile within that limit, else the smallest one.
+            const int n_sl = (m.K / 256 + 3) / 4;
+            const size_t pinned_tiles = (FU_WARPS + n_sl - 1) / n_sl + 1;
             int rl = -1;
-            for (int i = 0; i < n_rl && rl < 0; i++)
-                if (((size_t)m.row_bytes << rls[i]) + 3 * q38b_row_bytes(m.type, 256) + 48 <= (size_t)a.slot_bytes) rl = rls[i];   // granules past a ragged row end are read (and discarded)
+            for (int i = 0; i < 3 && rl < 0; i++) {
+                const size_t tile = ((size_t)m.row_bytes << FU_ROWS_LOG2[i]) + 160;
+                if (tile * pinned_tiles <= (size_t)a.ring_bytes * 45 / 100) rl = FU_ROWS_LOG2[i];
+            }
+            if (rl < 0 && ((size_t)m.row_bytes << 1) + 160 <= tile_cap) rl = 1;
             if (rl < 0) return false;
             f.kind = FOP_GEMV;
             f.fmt = (int)m.type;
@@ -347,6 +352,7 @@ bool plan_fused(q38b_pass* p) {
     a.status = ctx->d_status;
     a.cb_xxs = use_xxs ? ctx->d_cb_iq3xxs : nullptr;
     a.cb_s = use_s ? ctx->d_cb_iq3s : nullptr;
+    a.prof = p->d_prof;
     return true;
 }
 
@@ -497,6 +503,7 @@ void q38b_pass_destroy(q38b_pass* p) {
     if (p->pin_out) cudaFreeHost(p->pin_out);
     if (p->d_fops) cudaFree(p->d_fops);
     if (p->d_done) cudaFree(p->d_done);
+    if (p->d_prof) cudaFree(p->d_prof);
     delete p;
 }
 
@@ -651,6 +658,22 @@ int q38b_pass_set_fused(q38b_pass* p, int enabled) {
 }
 
 int q38b_pass_fused_active(q38b_pass* p) { return p && fused_ready(p) ? 1 : 0; }
+
+int q38b_pass_fused_trace(q38b_pass* p, int enable, unsigned long long* counters8) {   // FU_PROF_N counters
+    if (!p) return Q38B_ERR_ARG;
+    if (enable && !p->d_prof) {
+        PASS_CUDA(p, cudaMalloc(&p->d_prof, FU_PROF_N * sizeof(unsigned long long)));
+        PASS_CUDA(p, cudaMemset(p->d_prof, 0, FU_PROF_N * sizeof(unsigned long long)));
+    }
+    if (counters8) {
+        if (!p->d_prof) return Q38B_ERR_ARG;
+        PASS_CUDA(p, cudaMemcpy(counters8, p->d_prof, FU_PROF_N * sizeof(unsigned long long), cudaMemcpyDeviceToHost));   // synchronises
+        PASS_CUDA(p, cudaMemset(p->d_prof, 0, FU_PROF_N * sizeof(unsigned long long)));
+    }
+    if (!enable && p->d_prof) { cudaFree(p->d_prof); p->d_prof = nullptr; }
+    p->fargs.prof = p->d_prof;
+    return Q38B_OK;
+}
 
 int q38b_pass_kernel_count(const q38b_pass* p) {
     if (!p) return 0;

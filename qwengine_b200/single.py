@@ -1,6 +1,6 @@
 """Times one matvec (or prefill GEMM) shape on cuda:0 and prints one JSON line; also the command ncu profiles.
 
-    python -m qwengine_b200.single --fmt IQ3_XXS --M 17408 --K 5120 --nb 1 [--copies 8] [--reps 5] [--no-pdl]
+    python -m qwengine_b200.single --fmt IQ3_XXS --M 17408 --K 5120 --nb 1 [--copies 8] [--reps 5] [--no-pdl] [--no-fused]
     python -m qwengine_b200.single --op prefill --fmt Q4_K --M 17408 --K 5120 --tokens 1024
 
 Matvec: `copies` distinct resident matrices (random valid blocks; by default enough to exceed 1.5 GB, far beyond L2)
@@ -25,6 +25,9 @@ def main():
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--distinct-outputs", action="store_true", help="every matvec writes its own buffer: one group, no synchronisation between matvecs")
+    ap.add_argument("--trace", action="store_true", help="print the persistent kernel's wait counters")
+    ap.add_argument("--no-fused", action="store_true", help="replay the matvecs kernel by kernel instead of one persistent kernel")
     a = ap.parse_args()
     ctx = Context(0)
     ctx.set_pdl(not a.no_pdl)
@@ -34,10 +37,13 @@ def main():
     if a.op == "gemv":
         copies = a.copies or max(4, int(1.5e9 // (a.M * rb)) + 1)
         ps = Pass(ctx, max_nb=a.nb)
+        ps.set_fused(not a.no_fused)
         xin, xq, yb = ps.buffer_f32(a.K), ps.buffer_q8k(a.K), ps.buffer_f32(a.M)
         ps.quantize(xin, 0, a.K, xq)
         for _ in range(copies):
             w = torch.randint(0, 256, (a.M, rb), dtype=torch.uint8, device="cuda")
+            if a.distinct_outputs:
+                yb = ps.buffer_f32(a.M)
             ps.gemv(ps.matrix_device(f, w, a.K), xq, yb, 0)
         ps.buffer_tensor(xin).normal_()
         for _ in range(2):
@@ -49,6 +55,17 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         ctx.check()
+        if a.trace and ps.fused_active:
+            ps.fused_trace(True)
+            ps.run(a.nb)
+            t = ps.fused_trace(True, read=True)
+            print(json.dumps({"trace": t, "consumer_wait_tile_frac": round(t["wait_tile_cycles"] / max(1, t["consumer_cycles"]), 3),
+                              "consumer_wait_slices_frac": round(t["wait_slices_cycles"] / max(1, t["consumer_cycles"]), 3),
+                              "consumer_group_frac": round(t["group_cycles"] / max(1, t["consumer_cycles"]), 3),
+                              "group_barrier_frac": round(t["group_barrier_cycles"] / max(1, t["consumer_cycles"]), 3),
+                              "group_dependency_frac": round(t["group_dependency_cycles"] / max(1, t["consumer_cycles"]), 3),
+                              "producer_space_frac": round(t["producer_space_cycles"] / max(1, t["producer_cycles"]), 3)}))
+            ps.fused_trace(False)
         us = e0.elapsed_time(e1) * 1e3 / (a.reps * copies)
         print(json.dumps({"op": "gemv", "fmt": f.name, "M": a.M, "K": a.K, "nb": a.nb, "copies": copies, "us_per_launch": round(us, 2),
                           "weight_GBps": round(a.M * rb / us / 1e3, 1)}))
