@@ -317,8 +317,8 @@ class Pass:
         self.ctx._rc(self.lib.q38b_pass_fused_trace(self.h, int(bool(enable)), buf), "q38b_pass_fused_trace")
         if not read:
             return None
-        names = ["wait_tile_cycles", "wait_slices_cycles", "group_cycles", "consumer_cycles", "producer_space_cycles", "tiles", "units",
-                 "producer_cycles", "group_barrier_cycles", "group_dependency_cycles"]
+        names = ["wait_tile_cycles", "wait_units_cycles", "group_cycles", "warp_cycles", "group_barrier_cycles", "group_dependency_cycles",
+                 "tiles", "units", "waited_copy_latency_cycles_sum", "waited_copies"]
         return dict(zip(names, [int(v) for v in buf]))
 
     def barrier(self):

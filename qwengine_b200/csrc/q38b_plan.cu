@@ -95,7 +95,7 @@ struct q38b_pass {
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
     // single-column passes on one GPU run as one persistent kernel when the ops allow it
-    int fused_mode = 1;          // 0: always replay kernel by kernel
+    int fused_mode = 0;          // 1: single-column runs use the persistent kernel (opt-in: not faster than the replay yet)
     int fused_state = 0;         // 0: not planned yet, 1: ready, -1: this pass cannot run fused
     size_t fused_n_ops = 0;      // ops recorded when the fused plan was made
     FusedOp* d_fops = nullptr;
@@ -223,7 +223,8 @@ bool conflicts(const std::vector<Access>& x, const std::vector<Access>& y) {
 bool plan_fused(q38b_pass* p) {
     q38b_ctx* ctx = p->ctx;
     if (ctx->n_ranks > 1 || p->ops.empty()) return false;
-    const int G = ctx->sm_count;
+    const int G = ctx->sm_count * FU_CTAS_PER_SM;
+    const int smem_budget = FU_CTAS_PER_SM == 1 ? ctx->smem_optin : std::min(ctx->smem_optin, (228 * 1024) / FU_CTAS_PER_SM - 1024);
     bool use_xxs = false, use_s = false;
     int max_slices = 1;
     for (const Op& o : p->ops) {
@@ -231,7 +232,7 @@ bool plan_fused(q38b_pass* p) {
         const Mat& m = p->mats[o.a];
         if (m.row_bytes != q38b_row_bytes(m.type, m.K) || m.row_bytes > 0xFFFFFFFFull) return false;   // rows must be packed
         const int n_slices = (m.K / 256 + 3) / 4;
-        if (n_slices > FU_BAR_COUNT) return false;
+        if (n_slices > FU_BAR_COUNT || m.K / 256 > 255) return false;
         max_slices = std::max(max_slices, n_slices);
         use_xxs |= m.type == T_IQ3_XXS;
         use_s |= m.type == T_IQ3_S;
@@ -246,20 +247,47 @@ bool plan_fused(q38b_pass* p) {
     a.off_cb_xxs = a.off_sgn = a.off_cb_s = 0;
     if (use_xxs) { a.off_cb_xxs = off; off += 256 * 128; a.off_sgn = off; off += KSIGN_TABLE_BYTES; }
     if (use_s) { a.off_cb_s = off; off += 512 * 128; }
-    a.off_red = off;
-    off = up(off + FU_MAX_TILEBUF * max_slices * 8 * 4);
-    a.off_stage = off;
-    a.ring_bytes = ((ctx->smem_optin - off - FU_RING_SLACK) / 128) * 128;
-    if (a.ring_bytes < 64 * 1024) return false;
-    a.n_tilebuf = FU_MAX_TILEBUF;
-    p->fused_smem = a.off_stage + a.ring_bytes + FU_RING_SLACK;
-    const size_t tile_cap = std::min<size_t>(24 * 1024, (size_t)a.ring_bytes / 4);
+    int n_fops = 0, n_gemv = 0;
+    for (const Op& o : p->ops) {
+        if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;
+        n_fops++;
+        n_gemv += o.kind == OP_GEMV;
+    }
+    if (n_gemv > 32000 || (long long)n_fops * 8 + (long long)n_gemv * 48 > 48 * 1024) return false;
+    a.n_gemv = n_gemv;
+    a.off_optab = up(off);
+    a.off_gemvtab = up(a.off_optab + n_fops * 8);
+    a.off_filltab = a.off_gemvtab + n_gemv * 32;
+    off = a.off_filltab + n_gemv * 16;
+    // rows per tile of every matvec (largest of 8, 4, 2 whose tile stays under 24 KB), then equal ring slots that hold
+    // the largest tile
+    const size_t tile_cap = 24 * 1024;
+    size_t max_tile = 0;
+    for (const Op& o : p->ops) {
+        if (o.kind != OP_GEMV) continue;
+        const Mat& m = p->mats[o.a];
+        size_t tile = 0;
+        for (int rl = 3; rl >= 1 && !tile; rl--)
+            if (((size_t)m.row_bytes << rl) + 160 <= tile_cap) tile = ((size_t)m.row_bytes << rl) + 160;
+        if (!tile) return false;
+        max_tile = std::max(max_tile, tile);
+    }
+    if (!max_tile) return false;
+    a.slot_bytes = up((int)max_tile);
+    a.off_red = up(off);
+    for (a.n_slots = FU_MAX_SLOTS; a.n_slots >= 3; a.n_slots--) {
+        a.off_stage = up(a.off_red + a.n_slots * max_slices * 8 * 4);
+        if (a.off_stage + a.n_slots * a.slot_bytes + FU_RING_SLACK <= smem_budget) break;
+    }
+    if (a.n_slots < 3) return false;
+    p->fused_smem = a.off_stage + a.n_slots * a.slot_bytes + FU_RING_SLACK;
 
     std::vector<FusedOp> fops;
     std::vector<std::vector<Access>> accs;     // per fused op
     std::vector<int> group_first;              // index of the first op of each group
     std::vector<Access> acc;
     long long tiles_so_far = 0;
+    int gemv_seen = 0;
     int cur_src = -1, cur_permute = -1;        // input of the current matvec group, -1: the current group is not one
     for (const Op& o : p->ops) {
         if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;   // single GPU: nothing to exchange
@@ -268,21 +296,19 @@ bool plan_fused(q38b_pass* p) {
         bool new_group = true;
         if (o.kind == OP_GEMV) {
             const Mat& m = p->mats[o.a];
-            // Throughput is (bytes in flight) / latency: the tiles the 16 warps are working on pin their ring space, so
-            // they should take well under half of it.  A (tile, slice) unit goes to one warp: ceil(16 / slices) + 1
-            // tiles are being read at any time.  Largest tile within that limit, else the smallest one.
-            const int n_sl = (m.K / 256 + 3) / 4;
-            const size_t pinned_tiles = (FU_WARPS + n_sl - 1) / n_sl + 1;
             int rl = -1;
-            for (int i = 0; i < 3 && rl < 0; i++) {
-                const size_t tile = ((size_t)m.row_bytes << FU_ROWS_LOG2[i]) + 160;
-                if (tile * pinned_tiles <= (size_t)a.ring_bytes * 45 / 100) rl = FU_ROWS_LOG2[i];
-            }
-            if (rl < 0 && ((size_t)m.row_bytes << 1) + 160 <= tile_cap) rl = 1;
+            for (int r = 3; r >= 1 && rl < 0; r--)
+                if (((size_t)m.row_bytes << r) + 160 <= (size_t)a.slot_bytes) rl = r;
             if (rl < 0) return false;
             f.kind = FOP_GEMV;
+            f.gemv_index = gemv_seen++;
             f.fmt = (int)m.type;
             f.rows_log2 = rl;
+            // units of (slice, 4 rows) when that gives ten or more per tile -- then the 16 warps work on one or two tiles
+            // and the other slots hold copies in flight -- else units of (slice, 2 rows)
+            const int n_sl = (m.K / 256 + 3) / 4;
+            f.unit_rows = (rl >= 2 && n_sl * ((1 << rl) / 4) >= 10) ? 4 : 2;
+            if (n_sl * ((1 << rl) / f.unit_rows) > FU_BAR_COUNT) return false;
             f.M = m.M;
             f.nsb = m.K / 256;
             f.n_tiles = (m.M + (1 << rl) - 1) >> rl;
@@ -302,12 +328,14 @@ bool plan_fused(q38b_pass* p) {
             cur_permute = permute;
         } else if (o.kind == OP_QUANT) {
             f.kind = FOP_QUANT;
+            f.gemv_index = -1;
             f.nsb = o.n / 256;
             f.a = (const float*)p->bufs[o.a].ptr + o.off;
             f.out = p->bufs[o.b].ptr;
             cur_src = -1;
         } else {
             f.kind = FOP_SWIGLU;
+            f.gemv_index = -1;
             f.nsb = o.n / 256;
             f.a = (const float*)p->bufs[o.a].ptr + o.off;
             f.b = (const float*)p->bufs[o.b].ptr + o.d;
@@ -334,7 +362,7 @@ bool plan_fused(q38b_pass* p) {
     auto kern = fused_pass_kernel;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->fused_smem) != cudaSuccess) { cudaGetLastError(); return false; }
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FU_THREADS, p->fused_smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); return false; }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FU_THREADS, p->fused_smem) != cudaSuccess || per_sm < FU_CTAS_PER_SM) { cudaGetLastError(); return false; }
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device);
     if (!coop) return false;

@@ -101,6 +101,7 @@ def test_fused_pass_equals_kernel_by_kernel_replay(ctx):
 
 def _fused_cases(ctx, cases):
     ps = q.Pass(ctx, max_nb=1)
+    ps.set_fused(True)
     xin, xq = ps.buffer_f32(5120), ps.buffer_q8k(5120)
     xin2, xq2 = ps.buffer_f32(17408), ps.buffer_q8k(17408)
     ps.quantize(xin, 0, 5120, xq)
