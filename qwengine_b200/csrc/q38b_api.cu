@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -125,24 +126,23 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
 constexpr int G1_WARPS = 8;
 constexpr int G1_SMEM_BUDGET = 113 * 1024;   // two CTAs per SM (228 KB of shared memory per SM, 1 KB reserved per CTA)
 
-// rows per tile: 8 for the thin formats, 4 for the fat ones (keeps a stage near 16-24 KB)
-constexpr int g1_rows(int fmt) { return (fmt == T_Q5_K || fmt == T_Q6_K || fmt == T_Q8_0) ? 4 : 8; }
 
 struct Plan1 {
     Gemv1Args a;
     int grid;
     int smem;
+    int rows;   // rows per tile: 8, 4 or 2
 };
 
 // Shared-memory carve-up of the single-column kernel: barriers | activation scales | activations | codebook |
 // per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
-int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, Plan1* p) {
+int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, int G1_ROWS, Plan1* p) {
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
     const int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
     const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128;
-    const int G1_ROWS = g1_rows((int)type);
     Gemv1Args& a = p->a;
+    p->rows = G1_ROWS;
     a.nsb = nsb;
     a.n_slices = (nsb + 3) / 4;
     a.n_tiles = (M + G1_ROWS - 1) / G1_ROWS;
@@ -190,9 +190,21 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_byte
     return Q38B_ERR_NOMEM;
 }
 
-template <int FMT>
-int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    auto kern = gemv1_kernel<FMT, G1_WARPS, g1_rows(FMT)>;
+// Rows per tile: the largest of 8, 4, 2 that can be planned.  Measured on B200 for every shape of the benchmark pass,
+// eight rows win even where fewer rows would balance the CTAs better or let a tile be fetched by one copy: the cost per
+// (tile, slice) unit (activation loads, waits, lane reduction) outweighs both.
+int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, Plan1* best) {
+    const int cands[3] = {8, 4, 2};
+    for (int rows : cands) {
+        memset(best, 0, sizeof(*best));
+        if (plan_gemv1_rows(ctx, type, K, M, row_bytes, rows, best) == Q38B_OK) return Q38B_OK;
+    }
+    return Q38B_ERR_NOMEM;
+}
+
+template <int FMT, int ROWS>
+int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
+    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS>;
     static int configured_device = -1;
     if (configured_device != ctx->device) {
         Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G1_SMEM_BUDGET));
@@ -212,6 +224,16 @@ int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p.a));
     return Q38B_OK;
+}
+
+template <int FMT>
+int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
+    switch (p.rows) {
+        case 8: return launch_gemv1_rows<FMT, 8>(ctx, p, st);
+        case 4: return launch_gemv1_rows<FMT, 4>(ctx, p, st);
+        case 2: return launch_gemv1_rows<FMT, 2>(ctx, p, st);
+        default: return Q38B_ERR_ARG;
+    }
 }
 
 template <int KIND>

@@ -240,8 +240,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                     const int h = n >> 1;
                     const bool up = (lane & bit) != 0;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        if (i < h) {
+                    for (int i = 0; i < (PASSES > 1 ? PASSES / 2 : 1); i++) {
+                        if (i < h && i + h < PASSES) {
                             const float keep = up ? v[i + h] : v[i], give = up ? v[i] : v[i + h];
                             v[i] = keep + __shfl_xor_sync(0xffffffffu, give, bit);
                         }
