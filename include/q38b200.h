@@ -85,6 +85,15 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x_dev, long long x_ld, int K, 
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* q8k_dev,
                   long long q8k_stride, int nb, float* y_dev, long long y_ld, int accumulate, void* stream);
 
+/* Single-column matvec of up to three matrices of one format, K and row stride that read the SAME column, in one
+ * launch: y[i][0..M[i]) = W[i] x.  The column comes either as Q8_K blocks (q8k, x_f32 = NULL) or as K floats
+ * (x_f32, 16-byte aligned, q8k = NULL), which every CTA quantizes itself with the arithmetic of q38b_quantize_q8k:
+ * results equal the separate quantize + q38b_gemv_q8k calls bit for bit.  Replaces runs of gemv_q8 calls on one
+ * activation vector (q / k / v, gate / up: src/runtime/engine.cpp:1646, 1770-1849) and the quantize kernel before them
+ * (src/cuda/gemv.cu:31-47).  Q38B_ERR_UNSUPPORTED when the shape runs only on the multi-column kernel (call
+ * q38b_gemv_q8k per matrix then). */
+int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                    const void* q8k, const float* x_f32, float* const* y, void* stream);
 /* Matvec straight from fp32 activations x_dev[c * x_ld .. + K), the form in which the reference's engine holds them
  * before quantize_act_q8 + gemv_q8n (src/cuda/gemv.cu:200-204, 215-228): quantizes the nb columns to Q8_K into
  * `q8k_scratch_dev` (caller-owned device scratch of at least nb * q38b_q8k_bytes(K) bytes) and runs q38b_gemv_q8k. */
@@ -186,7 +195,12 @@ int q38b_pass_run_host(q38b_pass* pass, int nb, int in_f32, const float* x_host,
                        float* y_host, int y_len, void* stream);
 /* Weight bytes one run streams from HBM on this rank (sum over the matvec steps). */
 long long q38b_pass_weight_bytes(const q38b_pass* pass);
+/* Kernels one single-column run launches on this rank (after merging, see q38b_pass_set_merge). */
 int q38b_pass_kernel_count(const q38b_pass* pass);
+/* Single-column runs on one GPU merge steps by default: matvecs of one format and shape class that read the same
+ * column share a launch (q38b_gemv_group), and a quantize step whose output only feeds the matvecs right after it is
+ * folded into them.  Results are bit-identical either way; enabled = 0 replays one kernel per recorded step. */
+int q38b_pass_set_merge(q38b_pass* pass, int enabled);
 /* Experimental, off by default: with enabled = 1, single-column runs (nb = 1) of a pass on one GPU execute as ONE
  * persistent cooperative kernel that streams the weights of consecutive matvecs without draining between them
  * (bit-identical to the kernel-by-kernel replay, which remains the path for nb > 1, for several ranks, and for passes

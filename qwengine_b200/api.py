@@ -87,6 +87,8 @@ def load_library():
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_fused.argtypes = [vp, i32]
+    lib.q38b_pass_set_merge.argtypes = [vp, i32]
+    lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     lib.q38b_pass_fused_active.argtypes = [vp]
     lib.q38b_pass_fused_trace.argtypes = [vp, i32, vp]
     _LIB = lib
@@ -193,6 +195,20 @@ class Context:
                                         xq.stride(0) // F.Q8K_BLOCK_BYTES, nb, out.data_ptr(), out.stride(0),
                                         int(bool(accumulate)), _stream()), "q38b_gemv_q8k")
         return out
+
+    def gemv_group(self, fmt, Ws, K, xq=None, x_f32=None):
+        """q38b_gemv_group: up to three matrices [M_i, row_bytes] of one format on one column, given as Q8_K blocks
+        (xq uint8 [1, K/256*292]) or as floats (x_f32 [K] or [1, K]); returns the list of y_i float32 [M_i]."""
+        import ctypes
+        f = F.get(fmt)
+        n = len(Ws)
+        outs = [torch.empty(w.shape[0], dtype=torch.float32, device=w.device) for w in Ws]
+        Wp = (ctypes.c_void_p * n)(*[w.data_ptr() for w in Ws])
+        yp = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+        Ms = (ctypes.c_int * n)(*[w.shape[0] for w in Ws])
+        self._rc(self.lib.q38b_gemv_group(self.h, f.type_id, n, Wp, Ws[0].stride(0), K, Ms, xq.data_ptr() if xq is not None else None,
+                                          x_f32.data_ptr() if x_f32 is not None else None, yp, _stream()), "q38b_gemv_group")
+        return outs
 
     def gemv_f32(self, fmt, W, x, K, scratch=None, out=None, accumulate=False):
         """Matvec from fp32 activations x [nb, K]; `scratch` is a uint8 device tensor for the Q8_K blocks."""
@@ -301,6 +317,10 @@ class Pass:
 
     def set_peer_store(self, enabled):
         self.ctx._rc(self.lib.q38b_pass_set_peer_store(self.h, int(bool(enabled))), "q38b_pass_set_peer_store")
+
+    def set_merge(self, enabled):
+        """enabled=False: single-column runs launch one kernel per recorded step (no shared launches, no folded quantize)."""
+        self.ctx._rc(self.lib.q38b_pass_set_merge(self.h, int(bool(enabled))), "q38b_pass_set_merge")
 
     def set_fused(self, enabled):
         """enabled=False: single-column runs replay kernel by kernel instead of running as one persistent kernel."""

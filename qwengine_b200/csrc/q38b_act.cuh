@@ -27,15 +27,14 @@ __device__ __forceinline__ int warp_min_i(int v) {
 // Same arithmetic as quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381): the first element of largest
 // magnitude, signed, maps to -127 (iscale = -127 / max); q = min(127, round-half-even(iscale * x));
 // bsums per 16 elements; d = 1 / iscale; an all-zero block is all zero bytes.
-__device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t* blk) {
+// Core: the 8 int8 values of this lane packed in w0 | w1, their sum s8, and the block's d (the same in every lane).
+__device__ __forceinline__ void q8k_block_core(const float (&v)[8], uint32_t& w0, uint32_t& w1, int& s8, float& d) {
     const int lane = threadIdx.x & 31;
     float am = 0.0f;
 #pragma unroll
     for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(v[e]));
     am = warp_max_f(am);
-    uint32_t w0 = 0, w1 = 0;
-    int s8 = 0;
-    float d = 0.0f;
+    w0 = 0; w1 = 0; s8 = 0; d = 0.0f;
     if (am != 0.0f) {
         int idx = 256;
         float mine = 0.0f;
@@ -54,6 +53,14 @@ __device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t
         }
         d = __fdiv_rn(1.0f, iscale);
     }
+}
+
+__device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t* blk) {
+    const int lane = threadIdx.x & 31;
+    uint32_t w0, w1;
+    int s8;
+    float d;
+    q8k_block_core(v, w0, w1, s8, d);
     uint32_t* qs = (uint32_t*)(blk + 4);   // blocks are 4-byte aligned (292 = 4 * 73)
     qs[2 * lane] = w0;
     qs[2 * lane + 1] = w1;

@@ -136,7 +136,7 @@ struct Plan1 {
 
 // Shared-memory carve-up of the single-column kernel: barriers | activation scales | activations | codebook |
 // per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
-int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, int G1_ROWS, Plan1* p) {
+int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, Plan1* p) {
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
     const int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
@@ -145,7 +145,12 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row
     p->rows = G1_ROWS;
     a.nsb = nsb;
     a.n_slices = (nsb + 3) / 4;
-    a.n_tiles = (M + G1_ROWS - 1) / G1_ROWS;
+    a.n_tiles = 0;
+    for (int i = 0; i < G1_MAX_MATS; i++) {
+        a.tile_start[i] = a.n_tiles;
+        if (i < n_mats) a.n_tiles += (Ms[i] + G1_ROWS - 1) / G1_ROWS;
+    }
+    for (int i = n_mats; i < G1_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
     a.off_actd = 2048;
     a.off_actq = a.off_actd + a.n_slices * 4 * 32;
     a.off_cb = a.off_actq + a.n_slices * 1024;
@@ -193,11 +198,11 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row
 // Rows per tile: the largest of 8, 4, 2 that can be planned.  Measured on B200 for every shape of the benchmark pass,
 // eight rows win even where fewer rows would balance the CTAs better or let a tile be fetched by one copy: the cost per
 // (tile, slice) unit (activation loads, waits, lane reduction) outweighs both.
-int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, int M, size_t row_bytes, Plan1* best) {
+int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, Plan1* best) {
     const int cands[3] = {8, 4, 2};
     for (int rows : cands) {
         memset(best, 0, sizeof(*best));
-        if (plan_gemv1_rows(ctx, type, K, M, row_bytes, rows, best) == Q38B_OK) return Q38B_OK;
+        if (plan_gemv1_rows(ctx, type, K, Ms, n_mats, row_bytes, rows, best) == Q38B_OK) return Q38B_OK;
     }
     return Q38B_ERR_NOMEM;
 }
@@ -395,12 +400,13 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
         // single column: the dp4a kernel (one lane per 32- or 64-weight granule)
         Plan1 p1;
         memset(&p1, 0, sizeof(p1));
-        const int rc1 = plan_gemv1(ctx, type, K, M, row_bytes, &p1);
+        const int rc1 = plan_gemv1(ctx, type, K, &M, 1, row_bytes, &p1);
         if (rc1 == Q38B_OK) {
             Gemv1Args& g = p1.a;
             g.W = (const uint8_t*)W;
             g.row_bytes = (long long)row_bytes;
             g.xq = (const uint8_t*)q8k;
+            g.x_f32 = nullptr;
             g.y = y;
             g.n_peers = n_peers;
             g.static_weights = ctx->static_weights;
@@ -450,6 +456,58 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
         case T_IQ3_XXS: return launch_gemv<T_IQ3_XXS>(ctx, p, st);
         case T_IQ3_S: return launch_gemv<T_IQ3_S>(ctx, p, st);
         case T_IQ4_XS: return launch_gemv<T_IQ4_XS>(ctx, p, st);
+        default: return Q38B_ERR_UNSUPPORTED;
+    }
+}
+
+int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M) {
+    if (!ctx || ctx->uniform_columns || n_mats < 1 || n_mats > G1_MAX_MATS || !known_format(type) || K <= 0 || K % 256) return 0;
+    Plan1 p1;
+    return plan_gemv1(ctx, type, K, M, n_mats, row_bytes, &p1) == Q38B_OK;
+}
+
+int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                    const void* q8k, const float* x_f32, float* const* y, void* stream) {
+    if (!ctx || !W || !M || !y || n_mats < 1 || n_mats > G1_MAX_MATS || (!q8k == !x_f32)) return Q38B_ERR_ARG;
+    if (!known_format(type)) return Q38B_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 256 || row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
+    const int al = format_alignment(type);
+    if ((row_bytes % al) || (q8k && ((uintptr_t)q8k & 3)) || (x_f32 && ((uintptr_t)x_f32 & 15))) return Q38B_ERR_ALIGN;
+    for (int i = 0; i < n_mats; i++) {
+        if (!W[i] || !y[i] || M[i] < 1) return Q38B_ERR_ARG;
+        if (((uintptr_t)W[i] & 15) || ((uintptr_t)y[i] & 3)) return Q38B_ERR_ALIGN;
+    }
+    if (ctx->uniform_columns) return Q38B_ERR_UNSUPPORTED;
+    Plan1 p1;
+    memset(&p1, 0, sizeof(p1));
+    if (plan_gemv1(ctx, type, K, M, n_mats, row_bytes, &p1) != Q38B_OK) return Q38B_ERR_UNSUPPORTED;   // shapes only the tensor-core kernel takes
+    Gemv1Args& g = p1.a;
+    g.W = (const uint8_t*)W[0];
+    g.y = y[0];
+    g.M = M[0];
+    for (int i = 1; i < n_mats; i++) {
+        g.W_more[i - 1] = (const uint8_t*)W[i];
+        g.y_more[i - 1] = y[i];
+        g.M_more[i - 1] = M[i];
+    }
+    g.row_bytes = (long long)row_bytes;
+    g.xq = (const uint8_t*)q8k;
+    g.x_f32 = x_f32;
+    g.n_peers = 0;
+    g.static_weights = ctx->static_weights;
+    g.status = ctx->d_status;
+    g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+    g.K = K;
+    g.accumulate = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (type) {
+        case T_Q8_0: return launch_gemv1<T_Q8_0>(ctx, p1, st);
+        case T_Q4_K: return launch_gemv1<T_Q4_K>(ctx, p1, st);
+        case T_Q5_K: return launch_gemv1<T_Q5_K>(ctx, p1, st);
+        case T_Q6_K: return launch_gemv1<T_Q6_K>(ctx, p1, st);
+        case T_IQ3_XXS: return launch_gemv1<T_IQ3_XXS>(ctx, p1, st);
+        case T_IQ3_S: return launch_gemv1<T_IQ3_S>(ctx, p1, st);
+        case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
         default: return Q38B_ERR_UNSUPPORTED;
     }
 }

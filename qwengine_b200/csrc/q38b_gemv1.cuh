@@ -8,6 +8,7 @@
 // each (tile, slice) writes its 8 row sums to its own slot and arrives on the tile's mbarrier; the warp that took
 // the tile's last slice waits for the others, adds the slices in order (deterministic) and stores y.
 #pragma once
+#include "q38b_act.cuh"
 #include "q38b_decode1.cuh"
 #include "q38b_pipe.cuh"
 
@@ -16,10 +17,19 @@ namespace q38b {
 constexpr int G1_MAX_STAGES = 64;
 constexpr int G1_MAX_TILEBUF = 64;
 
+constexpr int G1_MAX_MATS = 3;
+
 struct Gemv1Args {
+    // up to three matrices of one format, K and row stride that read the same column: their tiles form one sequence
+    // (matrix 0's tiles, then matrix 1's, ...), so one launch replaces three and the CTAs' leftovers even out
     const uint8_t* W;
+    const uint8_t* W_more[G1_MAX_MATS - 1];
+    float* y_more[G1_MAX_MATS - 1];
+    int M_more[G1_MAX_MATS - 1];
+    int tile_start[G1_MAX_MATS];   // first tile of each matrix in the sequence (tile_start[0] = 0; unused ones = n_tiles)
     long long row_bytes;
-    const uint8_t* xq;      // Q8_K blocks of the single column
+    const uint8_t* xq;      // Q8_K blocks of the single column, or nullptr:
+    const float* x_f32;     // then the K floats of the column, quantized to Q8_K blocks by every CTA in its prologue
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     int n_peers;
@@ -29,7 +39,7 @@ struct Gemv1Args {
     int K, M, accumulate;
     int nsb;                // super-blocks per row
     int n_slices;           // ceil(nsb / 4)
-    int n_tiles;            // ceil(M / 8)
+    int n_tiles;            // tiles of all matrices
     int n_stages;
     int chunk_slices;       // slices per stage (K-chunk); n_chunks = ceil(n_slices / chunk_slices)
     int n_chunks;
@@ -75,14 +85,17 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         // ---------------- producer ----------------
         if (!a.static_weights) pdl_wait_prior();   // W may be the output of the kernel before this one
         if (lane < G1_ROWS) {
-            const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
-            const uintptr_t safe_end = w_end & ~(uintptr_t)15;
             int ti = 0, chunk = 0, stage = 0;
             uint32_t use = 0;                      // parity of the number of earlier fills of this stage
             for (int item = 0; item < n_items; item++) {
                 const uint32_t fb = smem_u32(&full[stage]);
                 mbar_wait_bounded(smem_u32(&empty[stage]), use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
-                const int row0 = ((int)blockIdx.x + (int)gridDim.x * ti) * G1_ROWS;
+                const int gtile = (int)blockIdx.x + (int)gridDim.x * ti;
+                const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+                const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
+                const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
+                const int row0 = (gtile - a.tile_start[mi]) * G1_ROWS;
+                const uintptr_t safe_end = ((uintptr_t)Wm + (uintptr_t)(Mm - 1) * a.row_bytes + packed_row) & ~(uintptr_t)15;
                 uint8_t* sbase = smem + a.off_stage + (size_t)stage * a.stage_bytes;
                 // what this lane copies: the whole tile (lane 0, contiguous rows) or its own row's chunk
                 uintptr_t src = 0;
@@ -90,12 +103,12 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                 uint8_t* slot = sbase;
                 if (a.contiguous) {
                     if (lane == 0) {
-                        src = (uintptr_t)a.W + (uintptr_t)row0 * a.row_bytes;
-                        len = (long long)min(G1_ROWS, a.M - row0) * a.row_bytes;
+                        src = (uintptr_t)Wm + (uintptr_t)row0 * a.row_bytes;
+                        len = (long long)min(G1_ROWS, Mm - row0) * a.row_bytes;
                     }
-                } else if (row0 + lane < a.M) {
+                } else if (row0 + lane < Mm) {
                     const int off = chunk * a.chunk_slices * SLICE_BYTES;
-                    src = (uintptr_t)a.W + (uintptr_t)(row0 + lane) * a.row_bytes + (uintptr_t)off;
+                    src = (uintptr_t)Wm + (uintptr_t)(row0 + lane) * a.row_bytes + (uintptr_t)off;
                     len = min(a.chunk_slices * SLICE_BYTES, packed_row - off);
                     slot = sbase + (size_t)lane * a.slot_stride;
                 }
@@ -147,6 +160,33 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         }
     }
     pdl_wait_prior();
+    if (a.x_f32) {
+        // quantize the column here (every CTA, the same arithmetic as quantize_q8k_kernel): one warp per 256 values
+        for (int sb = cw; sb < a.n_slices * 4; sb += NWARPS) {
+            uint32_t w0 = 0, w1 = 0;
+            float d = 0.0f;
+            if (sb < a.nsb) {
+                float v[8];
+                const float4 lo4 = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane);
+                const float4 hi4 = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane + 4);
+                v[0] = lo4.x; v[1] = lo4.y; v[2] = lo4.z; v[3] = lo4.w;
+                v[4] = hi4.x; v[5] = hi4.y; v[6] = hi4.z; v[7] = hi4.w;
+                int s8;
+                q8k_block_core(v, w0, w1, s8, d);
+            }
+            if (lane == 0) actd[sb * 8] = d;
+            uint8_t* dst = actq + sb * 256;
+            if (FMT == T_IQ4_XS) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const int k = 8 * lane + e;
+                    dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
+                }
+            } else {
+                *(uint2*)(dst + 8 * lane) = make_uint2(w0, w1);
+            }
+        }
+    } else {
     for (int i = ctid; i < a.n_slices * 4; i += NWARPS * 32)
         actd[i * 8] = i < a.nsb ? *(const float*)(a.xq + (size_t)i * Q8K_BYTES) : 0.0f;
     for (int i = ctid; i < a.n_slices * 256; i += NWARPS * 32) {   // word i of the (zero padded) activation vector
@@ -162,6 +202,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         } else {
             *(uint32_t*)(dst + 4 * wi) = v;
         }
+    }
     }
     named_bar_sync(15, NWARPS * 32);
 
@@ -185,7 +226,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     int cur_item = 0, stage = 0, cur_ti = 0, tslot = 0;
     uint32_t stage_par = 0, tile_par = 0;            // parities of the earlier uses of `stage` / `tslot`
     int seen_item = -1;                              // last stage fill this warp has waited for
-    const uint32_t w_lo = (uint32_t)(uintptr_t)a.W, rb32 = (uint32_t)a.row_bytes;
+    const uint32_t rb32 = (uint32_t)a.row_bytes;
     const uint32_t rb_step = a.contiguous ? 0u : rb32;   // rows of a contiguous stage share the copy's low address bits
     for (int unit = cw; unit < n_units; unit += NWARPS) {
         const int item = ti * a.n_chunks + chunk;
@@ -205,7 +246,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             mbar_wait_bounded(smem_u32(&full[stage]), stage_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
         }
         seen_item = item;
-        const int tile = (int)blockIdx.x + (int)gridDim.x * ti;
+        const int gtile = (int)blockIdx.x + (int)gridDim.x * ti;
+        const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+        const int tile = gtile - a.tile_start[mi];                 // tile of matrix mi
+        const uint32_t w_lo = (uint32_t)(uintptr_t)(mi == 0 ? a.W : a.W_more[mi - 1]);
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
         // low address bits of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
         const uint32_t src_lo = w_lo + (uint32_t)(tile * G1_ROWS) * rb32 + (a.contiguous ? 0u : (uint32_t)(chunk * a.chunk_slices * SLICE_BYTES));
@@ -266,12 +310,14 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             // this warp finishes the tile: wait for the other slices, add them in slice order
             mbar_wait_bounded(tb, tile_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             const int row = tile * G1_ROWS + lane;
-            if (lane < G1_ROWS && row < a.M) {
+            float* ym = mi == 0 ? a.y : a.y_more[mi - 1];
+            const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
+            if (lane < G1_ROWS && row < Mm) {
                 const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
                 float v = 0.0f;
                 for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];
-                const float out = a.accumulate ? a.y[row] + v : v;
-                a.y[row] = out;
+                const float out = a.accumulate ? ym[row] + v : v;
+                ym[row] = out;
                 for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][row] = out;   // fused all-gather: push to every peer
             }
             __syncwarp();

@@ -1,5 +1,6 @@
 // q38b_internal.h -- host-side state shared by the translation units of libq38b200.so.
 #pragma once
+#include <cstddef>
 #include <cstdint>
 
 struct q38b_ctx {
@@ -24,3 +25,6 @@ struct q38b_ctx {
     size_t arena_bytes = 0, arena_used = 0;
     int peers_connected = 0;
 };
+
+// 1 when q38b_gemv_group would run these matrices (single column) on the one-column kernel
+extern "C" int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M);

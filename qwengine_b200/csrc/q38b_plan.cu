@@ -95,6 +95,7 @@ struct q38b_pass {
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
     // single-column passes on one GPU run as one persistent kernel when the ops allow it
+    int merge_steps = 1;         // single-column replays: one launch for matvecs that share a column, quantize steps folded into them
     int fused_mode = 0;          // 1: single-column runs use the persistent kernel (opt-in: not faster than the replay yet)
     int fused_state = 0;         // 0: not planned yet, 1: ready, -1: this pass cannot run fused
     size_t fused_n_ops = 0;      // ops recorded when the fused plan was made
@@ -131,9 +132,106 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
     return rc;
 }
 
+// One launch of the merged single-column replay: `n` matvec ops (indices into p->ops) that read one column, which comes
+// as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source of that quantize op (folded into the launch).
+struct Merged { int first_op; int n; int ops[3]; int quant; };
+
+// Which steps of a single-column replay on one GPU can share launches.  A quantize step is folded into the matvecs that
+// read its output when they follow it directly, nothing else reads that output before it is rewritten, and all of them
+// run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
+void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>& skip) {
+    const q38b_ctx* ctx = p->ctx;
+    const std::vector<Op>& ops = p->ops;
+    const size_t n = ops.size();
+    out.clear();
+    skip.assign(n, 0);
+    auto next_real = [&](size_t i) { while (i < n && (ops[i].kind == OP_GATHER || ops[i].kind == OP_BARRIER)) i++; return i; };
+    auto on_column = [&](size_t k, int col) { return k < n && ops[k].kind == OP_GEMV && ops[k].b == col; };
+    size_t i = next_real(0);
+    while (i < n) {
+        int quant = -1;
+        size_t g0 = i;
+        if (ops[i].kind == OP_QUANT) {
+            const int col = ops[i].b;
+            const size_t j = next_real(i + 1);
+            size_t run_end = j;
+            while (on_column(run_end, col)) run_end = next_real(run_end + 1);
+            bool ok = run_end > j && ops[i].off % 4 == 0;
+            for (size_t k = run_end; ok && k < n; k++) {   // nobody else reads the Q8_K buffer before it is written again
+                const Op& o = ops[k];
+                if ((o.kind == OP_QUANT && o.b == col) || (o.kind == OP_SWIGLU && o.c == col)) break;
+                if (o.kind == OP_GEMV && o.b == col) ok = false;
+            }
+            for (size_t k = j; ok && k < run_end; k = next_real(k + 1)) {
+                const Mat& m = p->mats[ops[k].a];
+                if (m.K != ops[i].n || !q38b_gemv_group_plannable(ctx, m.type, 1, m.row_bytes, m.K, &m.M)) ok = false;
+            }
+            if (!ok) { i = next_real(i + 1); continue; }   // the quantize step runs as a kernel of its own
+            quant = (int)i;
+            skip[i] = 1;
+            g0 = j;
+        } else if (ops[i].kind != OP_GEMV) {
+            i = next_real(i + 1);
+            continue;
+        }
+        // cut the run of matvecs on this column into launches of up to three
+        const int col = ops[g0].b;
+        size_t k = g0;
+        while (on_column(k, col)) {
+            Merged mg = {(int)k, 0, {0, 0, 0}, quant};
+            const Mat& m0 = p->mats[ops[k].a];
+            int Ms[3];
+            while (on_column(k, col) && mg.n < 3) {
+                const Mat& m = p->mats[ops[k].a];
+                if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
+                Ms[mg.n] = m.M;
+                if (!q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)) break;
+                mg.ops[mg.n++] = (int)k;
+                k = next_real(k + 1);
+            }
+            if (mg.n == 0) {   // runs on the multi-column kernel only (never after a folded quantize): left alone
+                k = next_real(k + 1);
+                continue;
+            }
+            if (mg.n > 1 || quant >= 0) {
+                for (int t = 0; t < mg.n; t++) skip[mg.ops[t]] = 1;
+                out.push_back(mg);
+            }
+        }
+        i = k;
+    }
+}
+
+bool merging(const q38b_pass* p, int nb) { return nb == 1 && p->merge_steps && p->ctx->n_ranks <= 1 && !p->ctx->uniform_columns; }
+
 int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     q38b_ctx* ctx = p->ctx;
-    for (const Op& o : p->ops) {
+    std::vector<Merged> merged;
+    std::vector<char> skip(p->ops.size(), 0);
+    if (merging(p, nb)) merge_plan(p, merged, skip);
+    size_t next_merged = 0;
+    for (size_t oi = 0; oi < p->ops.size(); oi++) {
+        while (next_merged < merged.size() && merged[next_merged].first_op == (int)oi) {
+            const Merged& mg = merged[next_merged++];
+            const void* W[3];
+            float* y[3];
+            int M[3];
+            for (int t = 0; t < mg.n; t++) {
+                const Op& g = p->ops[mg.ops[t]];
+                const Mat& m = p->mats[g.a];
+                W[t] = m.W;
+                M[t] = m.M;
+                y[t] = (float*)p->bufs[g.c].ptr + g.off;
+            }
+            const Op& g0 = p->ops[mg.ops[0]];
+            const Mat& m0 = p->mats[g0.a];
+            const void* q8k = mg.quant >= 0 ? nullptr : p->bufs[g0.b].ptr;
+            const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
+            const int rc = q38b_gemv_group(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, st);
+            if (rc != Q38B_OK) return rc;
+        }
+        if (skip[oi]) continue;
+        const Op& o = p->ops[oi];
         int rc = Q38B_OK;
         switch (o.kind) {
             case OP_QUANT: {
@@ -679,6 +777,13 @@ long long q38b_pass_weight_bytes(const q38b_pass* p) {
     return b;
 }
 
+int q38b_pass_set_merge(q38b_pass* p, int enabled) {
+    if (!p) return Q38B_ERR_ARG;
+    p->merge_steps = enabled ? 1 : 0;
+    for (auto& g : p->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }   // recorded again at the next run
+    return Q38B_OK;
+}
+
 int q38b_pass_set_fused(q38b_pass* p, int enabled) {
     if (!p) return Q38B_ERR_ARG;
     p->fused_mode = enabled ? 1 : 0;
@@ -706,8 +811,14 @@ int q38b_pass_fused_trace(q38b_pass* p, int enable, unsigned long long* counters
 int q38b_pass_kernel_count(const q38b_pass* p) {
     if (!p) return 0;
     int n = 0;
-    for (const Op& o : p->ops) n += (o.kind != OP_GATHER) && (o.kind != OP_BARRIER || p->ctx->n_ranks > 1);
-    return n;
+    std::vector<Merged> merged;
+    std::vector<char> skip(p->ops.size(), 0);
+    if (merging(p, 1)) merge_plan(p, merged, skip);
+    for (size_t i = 0; i < p->ops.size(); i++) {
+        const Op& o = p->ops[i];
+        n += !skip[i] && (o.kind != OP_GATHER) && (o.kind != OP_BARRIER || p->ctx->n_ranks > 1);
+    }
+    return n + (int)merged.size();
 }
 
 }  // extern "C"

@@ -145,3 +145,44 @@ def test_fused_pass_long_rows(ctx):
     """Rows too long for eight- or four-row tiles take two-row tiles; mixed with short rows and a second input vector."""
     _fused_cases(ctx, [("IQ3_XXS", 1000, 5120), ("IQ4_XS", 517, 17408), ("Q4_K", 2051, 5120), ("IQ3_XXS", 64, 17408),
                        ("Q4_K", 100, 17408), ("Q5_K", 33, 17408), ("Q6_K", 777, 5120), ("Q8_0", 130, 5120)])
+
+
+@pytest.mark.parametrize("fmt", ["IQ3_XXS", "IQ4_XS", "Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+def test_gemv_group_equals_separate_calls(ctx, fmt):
+    """Three matrices on one column in one launch, from Q8_K blocks and from floats (quantized inside the kernel), give
+    the bits of quantize + one matvec call per matrix."""
+    K = 5120
+    Ms = [1000, 7, 2051]
+    ws = [torch.from_numpy(synth.make_weights(fmt, M, K, seed=40 + i)).cuda() for i, M in enumerate(Ms)]
+    x = torch.from_numpy(synth.make_activations(1, K, seed=8)).cuda()
+    xq = ctx.quantize_q8k(x)
+    want = [ctx.gemv(fmt, w, xq, K)[0] for w in ws]
+    for kwargs in (dict(xq=xq), dict(x_f32=x)):
+        got = ctx.gemv_group(fmt, ws, K, **kwargs)
+        torch.cuda.synchronize()
+        ctx.check()
+        for g, w_ in zip(got, want):
+            assert torch.equal(g.view(torch.int32), w_.view(torch.int32)), (fmt, list(kwargs))
+    # a zero column quantizes to all-zero blocks
+    got = ctx.gemv_group(fmt, ws[:2], K, x_f32=torch.zeros(K, device="cuda"))
+    assert all(float(g.abs().max()) == 0.0 for g in got)
+
+
+def test_merged_replay_equals_one_kernel_per_step(ctx):
+    """Shared launches and folded quantize steps change nothing in the results, and fewer kernels run."""
+    n_layers = 4
+    ws = small_weights(n_layers, 0)
+    x = synth.make_activations(1, dp.HIDDEN, seed=12)
+    outs, counts = [], []
+    for merge in (True, False):
+        ps = q.Pass(ctx, max_nb=1)
+        ps.set_merge(merge)
+        io = dp.build(ps, lambda spec, rows: ps.matrix_upload(spec.fmt, ws[spec.name], spec.K), n_layers=n_layers, head=False)
+        y = np.empty((1, dp.HIDDEN), np.float32)
+        ps.run_host(1, io["in_buf"], x, io["out_buf"], 0, y)
+        ctx.check()
+        outs.append(y.copy())
+        counts.append(ps.kernel_count)
+        ps.close()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    assert counts[0] < counts[1]
