@@ -468,7 +468,14 @@ int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, si
 
 int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                     const void* q8k, const float* x_f32, float* const* y, void* stream) {
+    return q38b_gemv_group_peers(ctx, type, n_mats, W, row_bytes, K, M, q8k, x_f32, y, nullptr, 0, stream);
+}
+
+int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                          const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream) {
     if (!ctx || !W || !M || !y || n_mats < 1 || n_mats > G1_MAX_MATS || (!q8k == !x_f32)) return Q38B_ERR_ARG;
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return Q38B_ERR_ARG;
+    for (int i = 0; i < n_mats * n_peers; i++) if (!y_peers[i] || ((uintptr_t)y_peers[i] & 3)) return Q38B_ERR_ARG;
     if (!known_format(type)) return Q38B_ERR_UNSUPPORTED;
     if (K <= 0 || K % 256 || row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
     const int al = format_alignment(type);
@@ -493,7 +500,9 @@ int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const*
     g.row_bytes = (long long)row_bytes;
     g.xq = (const uint8_t*)q8k;
     g.x_f32 = x_f32;
-    g.n_peers = 0;
+    g.n_peers = n_peers;
+    for (int i = 0; i < n_mats; i++)
+        for (int pr = 0; pr < n_peers; pr++) (i == 0 ? g.y_peer[pr] : g.y_peer_more[i - 1][pr]) = y_peers[i * n_peers + pr];
     g.static_weights = ctx->static_weights;
     g.status = ctx->d_status;
     g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;

@@ -32,6 +32,7 @@ struct Gemv1Args {
     const float* x_f32;     // then the K floats of the column, quantized to Q8_K blocks by every CTA in its prologue
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
+    float* y_peer_more[G1_MAX_MATS - 1][7];   // the same for matrices 1 and 2
     int n_peers;
     int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;
@@ -318,7 +319,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                 for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];
                 const float out = a.accumulate ? ym[row] + v : v;
                 ym[row] = out;
-                for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][row] = out;   // fused all-gather: push to every peer
+                for (int pr = 0; pr < a.n_peers; pr++) (mi == 0 ? a.y_peer[pr] : a.y_peer_more[mi - 1][pr])[row] = out;   // fused all-gather: push to every peer
             }
             __syncwarp();
         }

@@ -28,3 +28,6 @@ struct q38b_ctx {
 
 // 1 when q38b_gemv_group would run these matrices (single column) on the one-column kernel
 extern "C" int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M);
+// q38b_gemv_group with peer stores: y_peers[i * n_peers + r] is where peer r keeps the output of matrix i
+extern "C" int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                                     const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream);

@@ -184,6 +184,7 @@ void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>&
             while (on_column(k, col) && mg.n < 3) {
                 const Mat& m = p->mats[ops[k].a];
                 if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
+                if (p->bufs[ops[k].c].n_peer_ranks != p->bufs[ops[mg.first_op].c].n_peer_ranks) break;   // peer-visible outputs or not: one kind per launch
                 Ms[mg.n] = m.M;
                 if (!q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)) break;
                 mg.ops[mg.n++] = (int)k;
@@ -202,7 +203,7 @@ void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>&
     }
 }
 
-bool merging(const q38b_pass* p, int nb) { return nb == 1 && p->merge_steps && p->ctx->n_ranks <= 1 && !p->ctx->uniform_columns; }
+bool merging(const q38b_pass* p, int nb) { return nb == 1 && p->merge_steps && !p->ctx->uniform_columns; }
 
 int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     q38b_ctx* ctx = p->ctx;
@@ -227,7 +228,21 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
             const Mat& m0 = p->mats[g0.a];
             const void* q8k = mg.quant >= 0 ? nullptr : p->bufs[g0.b].ptr;
             const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
-            const int rc = q38b_gemv_group(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, st);
+            float* peers[3 * 7];
+            int np = 0;
+            if (p->peer_store && ctx->n_ranks > 1) {
+                const Buf& d0 = p->bufs[g0.c];
+                for (int r = 0; r < d0.n_peer_ranks; r++) np += r != ctx->rank && d0.peer[r];
+                for (int t = 0; t < mg.n; t++) {
+                    const Op& g = p->ops[mg.ops[t]];
+                    const Buf& d = p->bufs[g.c];
+                    int k = 0;
+                    for (int r = 0; r < d.n_peer_ranks; r++)
+                        if (r != ctx->rank && d.peer[r]) peers[t * np + k++] = (float*)d.peer[r] + g.off;
+                    if (k != np) return Q38B_ERR_ARG;   // all outputs of one launch live in peer-visible buffers, or none
+                }
+            }
+            const int rc = q38b_gemv_group_peers(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, st);
             if (rc != Q38B_OK) return rc;
         }
         if (skip[oi]) continue;
