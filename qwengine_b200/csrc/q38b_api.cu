@@ -174,7 +174,7 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
     }
     a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
     const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 1;
-    for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= (cb_entries ? 5 : 0); rep_log2--) {   // this kernel needs all 32 replicas
+    for (int rep_log2 = cb_entries ? cb1_rep_log2((int)type) : 0; rep_log2 >= (cb_entries ? cb1_rep_log2((int)type) : 0); rep_log2--) {   // the replica count is part of the format's decoder
         a.cb_rep_log2 = rep_log2;
         a.off_sgn = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
         a.off_red = a.off_sgn + (type == T_IQ3_XXS ? KSIGN_TABLE_BYTES : 0);

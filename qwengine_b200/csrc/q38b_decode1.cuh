@@ -104,6 +104,12 @@ Q38B_HD void ksign_entry(uint32_t c, uint32_t& lo, uint32_t& hi) {
 // byte k of w, times 128 (the stride of a replicated codebook entry)
 Q38B_HD uint32_t byte_x128(uint32_t w, int k) { return (k == 0 ? (w << 7) : (w >> (8 * k - 7))) & 0x7F80u; }
 
+// byte k of w, times 64 (the stride of an entry of a codebook replicated 16 x)
+Q38B_HD uint32_t byte_x64(uint32_t w, int k) { return (k == 0 ? (w << 6) : (w >> (8 * k - 6))) & 0x3FC0u; }
+// replicas of the single-column kernels' shared-memory codebooks: IQ3_XXS (256 entries) 32, every lane its own bank;
+// IQ3_S (512 entries) 16, lanes l and l + 16 share a replica (32 KB instead of 64)
+Q38B_HD constexpr int cb1_rep_log2(int fmt) { return fmt == T_IQ3_S ? 4 : 5; }
+
 // what a lane needs from the activations for one slice
 template <int NWORDS> struct ActRegs {
     uint32_t q[NWORDS];   // int8 activations of the granule, in the format's staged order
@@ -170,7 +176,7 @@ template <> struct Gran<T_IQ3_S> {
         const int s = lane & 7;
         uint32_t iw[2];
         sp_ld8b_a2(p + (2 + 8 * s), sp_low2(p) ^ 2u, iw[0], iw[1]);
-        const uint32_t qh = sp_ld8(p, 66 + s) << 15;               // bit j of qh now sits at bit 15 + j: entry 256 * 128
+        const uint32_t qh = sp_ld8(p, 66 + s) << 14;               // bit j of qh now sits at bit 14 + j: entry 256 * 64
         const uint32_t sg = sp_ld16(p, 74 + 4 * s) | (sp_ld16(p, 76 + 4 * s) << 16);
         const uint32_t ls = (sp_ld8(p, 106 + (s >> 1)) >> (4 * (s & 1))) & 0xFu;
         int P = 0, N = 0;
@@ -179,8 +185,8 @@ template <> struct Gran<T_IQ3_S> {
             const uint32_t sb = sg >> (8 * l);
             const uint32_t m_lo = sign_mask4(sb & 0xFu), m_hi = sign_mask4((sb >> 4) & 0xFu);
             const uint32_t w = iw[l >> 1];
-            const uint32_t g0 = cb1(cb, byte_x128(w, 2 * (l & 1)) | ((qh >> (2 * l)) & 0x8000u));
-            const uint32_t g1 = cb1(cb, byte_x128(w, 2 * (l & 1) + 1) | ((qh >> (2 * l + 1)) & 0x8000u));
+            const uint32_t g0 = cb1(cb, byte_x64(w, 2 * (l & 1)) | ((qh >> (2 * l)) & 0x4000u));
+            const uint32_t g1 = cb1(cb, byte_x64(w, 2 * (l & 1) + 1) | ((qh >> (2 * l + 1)) & 0x4000u));
             P = dp4a_us(g0, a.q[2 * l], P);
             P = dp4a_us(g1, a.q[2 * l + 1], P);
             N = dp4a_us(g0 & m_lo, a.q[2 * l], N);

@@ -423,12 +423,12 @@ __global__ void __launch_bounds__(FU_THREADS, FU_CTAS_PER_SM) fused_pass_kernel(
     }
     if (a.cb_s) {
         uint32_t* cbw = (uint32_t*)(sh.smem + a.off_cb_s);
-        for (int i = tid; i < 512 * 32; i += NCT) cbw[i] = __ldg(a.cb_s + (i >> 5));
+        for (int i = tid; i < 512 * 16; i += NCT) cbw[i] = __ldg(a.cb_s + (i >> 4));
     }
     Codebook1 cb_xxs, cb_s;
     cb_xxs.lane_base = sp_from(sh.smem + a.off_cb_xxs) + 4 * lane;
     cb_xxs.sign_base = sp_from(sh.smem + a.off_sgn) + 8 * (lane & 15);
-    cb_s.lane_base = sp_from(sh.smem + a.off_cb_s) + 4 * lane;
+    cb_s.lane_base = sp_from(sh.smem + a.off_cb_s) + 4 * (lane & 15);
     cb_s.sign_base = cb_xxs.sign_base;
 
     float* actd = (float*)(sh.smem + a.off_actd);

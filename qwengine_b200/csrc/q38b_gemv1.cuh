@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     named_bar_sync(15, NWARPS * 32);
 
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
-    cb.lane_base = sp_from(cbw) + 4 * lane;
+    cb.lane_base = sp_from(cbw) + 4 * (lane & ((1 << cb1_rep_log2(FMT)) - 1));
     cb.sign_base = sp_from(smem + a.off_sgn) + 8 * (lane & 15);
     const SP actq_sp = sp_from(actq), actd_sp = sp_from(actd);
     const SP stage0_sp = sp_from(smem + a.off_stage);

@@ -359,7 +359,7 @@ bool plan_fused(q38b_pass* p) {
     int off = a.off_actq + max_slices * 1024;
     a.off_cb_xxs = a.off_sgn = a.off_cb_s = 0;
     if (use_xxs) { a.off_cb_xxs = off; off += 256 * 128; a.off_sgn = off; off += KSIGN_TABLE_BYTES; }
-    if (use_s) { a.off_cb_s = off; off += 512 * 128; }
+    if (use_s) { a.off_cb_s = off; off += 512 * 64; }
     int n_fops = 0, n_gemv = 0;
     for (const Op& o : p->ops) {
         if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;

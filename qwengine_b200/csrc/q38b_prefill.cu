@@ -62,6 +62,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  : "memory");
 }
 
+constexpr int PF_PREFETCH_BLOCKS = 3;   // super-blocks (256 weights) of look-ahead of the L2 prefetch
+
 template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -107,6 +109,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             const uint32_t use = (uint32_t)(slab / PF_STAGES);
             mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
             const int sub = slab * 2 + half;                     // 32-weight sub-block index within the row
+            // the weights come straight from HBM: ask L2 for this row's super-blocks a few slabs ahead (one line each)
+            if ((slab & 3) == 0 && half == 0) {
+                const size_t ahead = (size_t)((slab >> 2) + PF_PREFETCH_BLOCKS) * Unit<FMT>::BLOCK_BYTES * (FMT == T_Q8_0 ? 8 : 1);
+                if (ahead < (size_t)a.row_bytes) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + ahead));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + min(ahead + 128, (size_t)a.row_bytes - 2)));
+                }
+            }
             float y[32];
             dequant_sub<FMT>(wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES, sub & 7, y);
             // row r of the tile: 128 bytes; 16-byte chunk c goes to chunk c ^ (r & 7) (128-byte swizzle)

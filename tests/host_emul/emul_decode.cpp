@@ -195,13 +195,14 @@ extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const ui
         for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
     }
     const int entries = fmt == T_IQ3_XXS ? 256 : fmt == T_IQ3_S ? 512 : 0;
-    (void)rep_log2;                                        // the single-column kernel always uses 32 replicas
-    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) * 32);
-    for (size_t i = 0; i < (size_t)entries * 32; i++) cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> 5] : q38b_iq3s_grid[i >> 5];
+    (void)rep_log2;                                        // the single-column decoders fix their replica counts
+    const int rl = cb1_rep_log2(fmt), reps = 1 << rl;
+    std::vector<uint32_t> cb((size_t)(entries ? entries : 1) * reps);
+    for (size_t i = 0; i < (size_t)entries * reps; i++) cb[i] = fmt == T_IQ3_XXS ? q38b_iq3xxs_grid[i >> rl] : q38b_iq3s_grid[i >> rl];
     std::vector<uint32_t> sgn(KSIGN_TABLE_BYTES / 4);
     for (int i = 0; i < 128 * 16; i++) ksign_entry((uint32_t)i >> 4, sgn[2 * i], sgn[2 * i + 1]);
     Codebook1 cbs[32];
-    for (int l = 0; l < 32; l++) cbs[l] = Codebook1{sp_from(cb.data()) + 4 * l, sp_from(sgn.data()) + 8 * (l & 15)};
+    for (int l = 0; l < 32; l++) cbs[l] = Codebook1{sp_from(cb.data()) + 4 * (l & (reps - 1)), sp_from(sgn.data()) + 8 * (l & 15)};
     switch (fmt) {
         case T_Q8_0: run_slices<T_Q8_0>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         case T_Q4_K: run_slices<T_Q4_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
