@@ -428,6 +428,17 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
             }
         }
     }
+    // Long rows on the multi-column kernel: the staged activations (nb x K bytes) would leave almost no shared memory
+    // for the weight stages, so the matvec runs as two launches over the two halves of K, the second accumulating onto
+    // the first.  The rule depends on K and the format alone: columns stay bit-identical for every nb this kernel serves.
+    if (K > 8192 && (K / 256) % 2 == 0 && type != T_Q8_0 && ((size_t)(K / 512) * block_bytes((int)type)) % 16 == 0) {   // the second half must start 16-byte aligned like any matrix
+        const int Kh = K / 2;
+        const size_t w_off = (size_t)(Kh / 256) * block_bytes((int)type);
+        int rc = q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, Kh, M, q8k, q8k_stride, nb, y, y_ld, accumulate, y_peers, n_peers, stream);
+        if (rc != Q38B_OK) return rc;
+        return q38b_gemv_q8k_scatter(ctx, type, (const uint8_t*)W + w_off, row_bytes, Kh, M, (const uint8_t*)q8k + (size_t)(Kh / 256) * Q8K_BYTES,
+                                     q8k_stride, nb, y, y_ld, 1, y_peers, n_peers, stream);
+    }
     Plan p;
     memset(&p, 0, sizeof(p));
     int rc = plan_gemv(ctx, type, K, M, nb, &p);

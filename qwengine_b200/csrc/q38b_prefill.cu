@@ -62,6 +62,74 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Fast dequantization to bf16 pairs for the A operand (K-quants).  An integer n < 128 becomes the bf16 number 128 + n by
+// OR-ing it under the bit pattern 0x4300, the bias is subtracted exactly (bf16 holds every integer below 256), and one
+// packed bf16 fused multiply-add applies scale and minimum to two weights.  Against the exact dequantizer the scale and
+// the minimum are rounded to bf16 before instead of after the multiplication: a relative error of 2^-9 per weight, the
+// same size as the rounding of the product to bf16 that the tensor core's operand format imposes anyway.
+// p[j] = weights 2j, 2j + 1 of the 32-weight sub-block.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t bf2_u32(__nv_bfloat162 v) { return *(const uint32_t*)&v; }
+__device__ __forceinline__ __nv_bfloat162 u32_bf2(uint32_t v) { return *(const __nv_bfloat162*)&v; }
+__device__ __forceinline__ __nv_bfloat162 bf2_splat(float x) { return __float2bfloat162_rn(x); }
+// bytes b0..b3 of t (each < 128) -> bf16 pairs (b0, b1) and (b2, b3), minus `bias`
+__device__ __forceinline__ void bytes_to_bf2(uint32_t t, __nv_bfloat162 bias, __nv_bfloat162& lo, __nv_bfloat162& hi) {
+    lo = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5140)), bias);
+    hi = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5342)), bias);
+}
+
+template <int FMT>
+__device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t (&p)[16]) {
+    if (FMT == T_Q4_K || FMT == T_Q5_K) {
+        if (((uintptr_t)b & 3) != 0) return false;   // the 32-bit loads below need it (blocks are multiples of 16 bytes; GGUF tensors are 32-byte aligned)
+        const uint32_t dd = *(const uint32_t*)b;
+        const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu))), mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+        const uint8_t* sc = b + 4;
+        int scv, mv;
+        if (s < 4) { scv = sc[s] & 63; mv = sc[s + 4] & 63; }
+        else { scv = (sc[s + 4] & 0xF) | ((sc[s - 4] >> 6) << 4); mv = (sc[s + 4] >> 4) | ((sc[s] >> 6) << 4); }
+        const __nv_bfloat162 a2 = bf2_splat(d * (float)scv), c2 = bf2_splat(-(mn * (float)mv));
+        const __nv_bfloat162 bias = u32_bf2(0x43004300u);
+        const uint32_t* q = (const uint32_t*)(b + (FMT == T_Q5_K ? 48 : 16) + 32 * (s >> 1));
+        const uint32_t* qh = (const uint32_t*)(b + 16);
+        const int sh = (s & 1) ? 4 : 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            uint32_t t = (q[i] >> sh) & 0x0F0F0F0Fu;
+            if (FMT == T_Q5_K) t |= ((qh[i] >> s) & 0x01010101u) << 4;
+            __nv_bfloat162 lo, hi;
+            bytes_to_bf2(t, bias, lo, hi);
+            p[2 * i] = bf2_u32(__hfma2(lo, a2, c2));
+            p[2 * i + 1] = bf2_u32(__hfma2(hi, a2, c2));
+        }
+        return true;
+    }
+    if (FMT == T_Q6_K) {
+        // sub-block s = 4h + j of the super-block: weights 128h + 32j .. + 31; ql nibble (low for j < 2) and two bits of qh
+        const float d = __half2float(__ushort_as_half(*(const unsigned short*)(b + 208)));
+        const int h = s >> 2, j = s & 3;
+        const uint16_t* ql = (const uint16_t*)(b + 64 * h + 32 * (j & 1));   // Q6_K blocks are 210 bytes: 2-byte aligned only
+        const uint16_t* qh = (const uint16_t*)(b + 128 + 32 * h);
+        const int8_t* sc = (const int8_t*)(b + 192 + 8 * h + 2 * j);
+        const __nv_bfloat162 bias = u32_bf2(0x43204320u);                   // 128 + 32
+        const __nv_bfloat162 a0 = bf2_splat(d * (float)sc[0]), a1 = bf2_splat(d * (float)sc[1]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t lw = (uint32_t)ql[2 * i] | ((uint32_t)ql[2 * i + 1] << 16);
+            const uint32_t hw = (uint32_t)qh[2 * i] | ((uint32_t)qh[2 * i + 1] << 16);
+            const uint32_t t = ((lw >> (4 * (j >> 1))) & 0x0F0F0F0Fu) | (((hw >> (2 * j)) & 0x03030303u) << 4);
+            __nv_bfloat162 lo, hi;
+            bytes_to_bf2(t, bias, lo, hi);
+            const __nv_bfloat162 a2 = i < 4 ? a0 : a1;
+            p[2 * i] = bf2_u32(__hmul2(lo, a2));
+            p[2 * i + 1] = bf2_u32(__hmul2(hi, a2));
+        }
+        return true;
+    }
+    return false;
+}
+
 constexpr int PF_PREFETCH_BLOCKS = 3;   // super-blocks (256 weights) of look-ahead of the L2 prefetch
 
 template <int FMT>
@@ -76,7 +144,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     uint8_t* stages = smem + 1024;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = blockIdx.x * PF_ROWS;
-    const int tok0 = blockIdx.y * 2 * PF_NTILE;
+    const int tok0 = blockIdx.y * a.n_acc * PF_NTILE;
     const int n_slabs = a.K / PF_KSLAB;
 
     if (tid == 0) {
@@ -117,20 +185,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + min(ahead + 128, (size_t)a.row_bytes - 2)));
                 }
             }
-            float y[32];
-            dequant_sub<FMT>(wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES, sub & 7, y);
+            uint32_t p[16];
+            const uint8_t* blk = wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES;
+            if (!fast_sub_bf16<FMT>(blk, sub & 7, p)) {
+                float y[32];
+                dequant_sub<FMT>(blk, sub & 7, y);
+#pragma unroll
+                for (int j = 0; j < 16; j++) p[j] = bf2_u32(__floats2bfloat162_rn(y[2 * j], y[2 * j + 1]));
+            }
             // row r of the tile: 128 bytes; 16-byte chunk c goes to chunk c ^ (r & 7) (128-byte swizzle)
             uint8_t* arow = stages + (size_t)st * PF_STAGE_BYTES + (size_t)r * 128;
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                uint32_t p[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const __nv_bfloat162 v = __floats2bfloat162_rn(y[8 * c + 2 * j], y[8 * c + 2 * j + 1]);
-                    p[j] = *(const uint32_t*)&v;
-                }
                 const int chunk = (4 * half + c) ^ (r & 7);
-                *(uint4*)(arow + 16 * chunk) = make_uint4(p[0], p[1], p[2], p[3]);
+                *(uint4*)(arow + 16 * chunk) = make_uint4(p[4 * c], p[4 * c + 1], p[4 * c + 2], p[4 * c + 3]);
             }
             fence_proxy_async();                                 // generic-proxy stores -> visible to the tensor core
             mbar_arrive(smem_u32(&full_a[st]));
@@ -276,8 +344,10 @@ extern "C" int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W, si
     a.M = M;
     a.B = B;
     a.accumulate = accumulate ? 1 : 0;
-    a.n_acc = B > PF_NTILE ? 2 : 1;
-    const dim3 grid((unsigned)((M + PF_ROWS - 1) / PF_ROWS), (unsigned)((B + 2 * PF_NTILE - 1) / (2 * PF_NTILE)));
+    const int row_tiles = (M + PF_ROWS - 1) / PF_ROWS;
+    a.n_acc = B > PF_NTILE ? 2 : 1;   // 512 tokens per CTA (two accumulators) halve the dequantization work per token
+    const int tok_per_cta = a.n_acc * PF_NTILE;
+    const dim3 grid((unsigned)row_tiles, (unsigned)((B + tok_per_cta - 1) / tok_per_cta));
     cudaStream_t st = (cudaStream_t)stream;
     switch (type) {
         case T_Q8_0: return launch_prefill<T_Q8_0>(ctx, a, map, grid, st);
