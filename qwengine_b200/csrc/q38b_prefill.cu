@@ -36,13 +36,6 @@ constexpr int PF_B_BYTES = PF_NTILE * PF_KSLAB * 2;       // 32 KB per accumulat
 constexpr int PF_STAGE_BYTES = PF_A_BYTES + 2 * PF_B_BYTES;
 constexpr int PF_THREADS = 320;    // 8 decode warps + TMA warp + MMA warp
 constexpr int PF_SMEM = 1024 + PF_STAGES * PF_STAGE_BYTES + 256;
-// Raw weight blocks are staged in shared memory by bulk copies, one 256-weight chunk (four slabs) of all 128 rows at a
-// time, two chunks deep, so that the dequantizing threads never wait for global memory.  Bytes of a chunk of one row,
-// and the room its 16-byte aligned superset needs.  Q8_0 (272 bytes per chunk) does not fit and loads directly.
-template <int FMT> __host__ __device__ constexpr int pf_chunk_bytes() { return FMT == T_Q8_0 ? 8 * 34 : Unit<FMT>::BLOCK_BYTES; }
-template <int FMT> __host__ __device__ constexpr int pf_raw_stride() { return (pf_chunk_bytes<FMT>() + 30 + 15) / 16 * 16; }
-template <int FMT> __host__ __device__ constexpr bool pf_raw() { return FMT != T_Q8_0; }
-template <int FMT> __host__ __device__ constexpr int pf_smem() { return PF_SMEM + (pf_raw<FMT>() ? 2 * PF_ROWS * pf_raw_stride<FMT>() : 0); }
 
 struct PrefillArgs {
     const uint8_t* W;
@@ -146,12 +139,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     uint64_t* full_b = full_a + PF_STAGES;           // [stages] TMA bytes
     uint64_t* empty = full_b + PF_STAGES;            // [stages] tcgen05.commit
     uint64_t* acc_done = empty + PF_STAGES;          // [1]
-    uint64_t* raw_full = acc_done + 1;               // [2] bulk copies of a chunk of raw blocks (32 lanes arrive)
-    uint64_t* raw_empty = raw_full + 2;              // [2] 256 decode threads arrive
-    uint32_t* tmem_slot = (uint32_t*)(raw_empty + 2);
+    uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     uint8_t* stages = smem + 1024;
-    uint8_t* raw = stages + PF_STAGES * PF_STAGE_BYTES;    // [2][PF_ROWS][pf_raw_stride]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = blockIdx.x * PF_ROWS;
     const int tok0 = blockIdx.y * a.n_acc * PF_NTILE;
@@ -165,7 +155,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             mbar_init(smem_u32(&empty[s]), 1);
         }
         mbar_init(smem_u32(acc_done), 1);
-        for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&raw_full[b]), 32); mbar_init(smem_u32(&raw_empty[b]), 256); }
         mbar_fence_init();
     }
     if (warp == 9) {   // this warp owns the tensor memory allocation (512 columns = two 128 x 256 fp32 accumulators)
@@ -189,7 +178,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
             const int sub = slab * 2 + half;                     // 32-weight sub-block index within the row
             // the weights come straight from HBM: ask L2 for this row's super-blocks a few slabs ahead (one line each)
-            if (!pf_raw<FMT>() && (slab & 3) == 0 && half == 0) {
+            if ((slab & 3) == 0 && half == 0) {
                 const size_t ahead = (size_t)((slab >> 2) + PF_PREFETCH_BLOCKS) * Unit<FMT>::BLOCK_BYTES * (FMT == T_Q8_0 ? 8 : 1);
                 if (ahead < (size_t)a.row_bytes) {
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + ahead));
@@ -198,12 +187,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             }
             uint32_t p[16];
             const uint8_t* blk = wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES;
-            if (pf_raw<FMT>()) {
-                const int chunk = slab >> 2, buf = chunk & 1;
-                if ((slab & 3) == 0) mbar_wait_bounded(smem_u32(&raw_full[buf]), (uint32_t)(chunk >> 1) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-                const uint8_t* src = wrow + (size_t)chunk * pf_chunk_bytes<FMT>();
-                blk = raw + ((size_t)buf * PF_ROWS + r) * pf_raw_stride<FMT>() + ((uintptr_t)src & 15);
-            }
             if (!fast_sub_bf16<FMT>(blk, sub & 7, p)) {
                 float y[32];
                 dequant_sub<FMT>(blk, sub & 7, y);
@@ -219,47 +202,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             }
             fence_proxy_async();                                 // generic-proxy stores -> visible to the tensor core
             mbar_arrive(smem_u32(&full_a[st]));
-            if (pf_raw<FMT>() && (slab & 3) == 3) mbar_arrive(smem_u32(&raw_empty[(slab >> 2) & 1]));   // this chunk's raw blocks are read
         }
     } else if (warp == 8) {
         // ---------------- operand B: activation tiles by TMA ----------------
-        const int n_chunks = n_slabs >> 2;
-        const uintptr_t safe_end = ((uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + (uintptr_t)n_chunks * pf_chunk_bytes<FMT>()) & ~(uintptr_t)15;
-        // one chunk of raw blocks: lane l copies rows l, l + 32, l + 64, l + 96 (the 16-byte aligned superset of each)
-        auto issue_chunk = [&](int chunk) {
-            const int buf = chunk & 1;
-            mbar_wait_bounded(smem_u32(&raw_empty[buf]), ((uint32_t)(chunk >> 1) & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
-            const uint32_t fb = smem_u32(&raw_full[buf]);
-            uintptr_t lo[4];
-            uint32_t bytes[4], total = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int r = lane + 32 * i;
-                const int grow = min(row0 + r, a.M - 1);
-                const uintptr_t src = (uintptr_t)a.W + (uintptr_t)grow * a.row_bytes + (uintptr_t)chunk * pf_chunk_bytes<FMT>();
-                lo[i] = src & ~(uintptr_t)15;
-                uintptr_t hi = (src + pf_chunk_bytes<FMT>() + 15) & ~(uintptr_t)15;
-                uint8_t* dst = raw + ((size_t)buf * PF_ROWS + r) * pf_raw_stride<FMT>();
-                if (hi > safe_end) {   // the tensor's last bytes do not fill a 16-byte unit: plain loads
-                    hi = safe_end > lo[i] ? safe_end : lo[i];
-                    for (uintptr_t q = hi; q < src + pf_chunk_bytes<FMT>(); q += 2)
-                        if (q >= src) *(uint16_t*)(dst + (q - lo[i])) = *(const uint16_t*)q;
-                }
-                bytes[i] = (uint32_t)(hi - lo[i]);
-                total += bytes[i];
-            }
-            if (total) mbar_arrive_expect_tx(fb, total);
-            else mbar_arrive(fb);
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                if (bytes[i]) bulk_copy_g2s(smem_u32(raw + ((size_t)buf * PF_ROWS + lane + 32 * i) * pf_raw_stride<FMT>()), (const void*)lo[i], bytes[i], fb);
-        };
-        if (pf_raw<FMT>()) {
-            issue_chunk(0);
-            if (n_chunks > 1) issue_chunk(1);
-        }
-        for (int slab = 0; slab < n_slabs; slab++) {
-            if (lane == 0) {
+        if (lane == 0) {
+            for (int slab = 0; slab < n_slabs; slab++) {
                 const int st = slab % PF_STAGES;
                 const uint32_t use = (uint32_t)(slab / PF_STAGES);
                 mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
@@ -269,9 +216,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 for (int n = 0; n < a.n_acc; n++)
                     tma_load_2d(smem_u32(b0 + n * PF_B_BYTES), &xmap, slab * PF_KSLAB, tok0 + n * PF_NTILE, fb);
             }
-            __syncwarp();
-            // the chunk after the one the decode warps are starting now (its buffer is free once they have left the previous one)
-            if (pf_raw<FMT>() && (slab & 3) == 0 && slab > 0 && (slab >> 2) + 1 < n_chunks) issue_chunk((slab >> 2) + 1);
         }
     } else {
         // ---------------- MMA issue ----------------
@@ -362,11 +306,11 @@ int launch_prefill(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, 
     auto kern = prefill_kernel<FMT>;
     static int configured_device = -1;
     if (configured_device != ctx->device) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem<FMT>());
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
         if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
         configured_device = ctx->device;
     }
-    kern<<<grid, PF_THREADS, pf_smem<FMT>(), st>>>(a, map);
+    kern<<<grid, PF_THREADS, PF_SMEM, st>>>(a, map);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
     return Q38B_OK;
