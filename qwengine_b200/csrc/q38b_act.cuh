@@ -5,6 +5,7 @@
 #include <cstdint>
 
 #include "q38b_decode.cuh"
+#include "q38b_pipe.cuh"
 
 namespace q38b {
 
@@ -112,7 +113,12 @@ static __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(con
 
 static __global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                                                      long long ld, int n, int n_rows, float* __restrict__ h,
-                                                                     uint8_t* __restrict__ out, long long out_stride) {
+                                                                     uint8_t* __restrict__ out, long long out_stride,
+                                                                     const PeerSync sync, int* status) {
+    if (sync.n > 0) {   // gate and up were completed by the other GPUs: cross-GPU barrier first
+        peer_sync_wait(sync, blockIdx.x == 0, (int)threadIdx.x, status);
+        __syncthreads();
+    }
     const int nsb = n >> 8;
     const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
     if (blk >= (long long)n_rows * nsb) return;

@@ -368,13 +368,28 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x, long long x_ld, int K, int 
     return Q38B_OK;
 }
 
+// takes the cross-GPU barrier the planner left for the next launch, if any
+static PeerSync take_pending_sync(q38b_ctx* ctx) {
+    PeerSync ps;
+    memset(&ps, 0, sizeof(ps));
+    if (ctx->pending_sync_seq >= 0 && ctx->n_ranks > 1 && ctx->peers_connected) {
+        ps.local = ctx->d_flags;
+        for (int r = 0; r < 8; r++) ps.peer[r] = ctx->peer_flags[r];
+        ps.n = ctx->n_ranks;
+        ps.rank = ctx->rank;
+        ps.seq = ctx->pending_sync_seq;
+    }
+    ctx->pending_sync_seq = -1;
+    return ps;
+}
+
 int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g, const float* u, long long ld, int n, int n_rows, float* h, void* q8k,
                     long long q8k_stride, void* stream) {
     if (!ctx || !g || !u || n <= 0 || n % 256 || n_rows < 1 || ld < n || (q8k && q8k_stride < n / 256)) return Q38B_ERR_ARG;
     if (((uintptr_t)g | (uintptr_t)u | (uintptr_t)h | (uintptr_t)q8k) & 3) return Q38B_ERR_ALIGN;
     const long long blocks = (long long)n_rows * (n / 256);
     swiglu_q8k_kernel<<<(unsigned)((blocks + ACT_WARPS - 1) / ACT_WARPS), ACT_WARPS * 32, 0, (cudaStream_t)stream>>>(
-        g, u, ld, n, n_rows, h, (uint8_t*)q8k, q8k_stride);
+        g, u, ld, n, n_rows, h, (uint8_t*)q8k, q8k_stride, take_pending_sync(ctx), ctx->d_status);
     Q38B_CUDA(ctx, cudaGetLastError());
     return Q38B_OK;
 }
@@ -511,6 +526,7 @@ int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* 
     g.row_bytes = (long long)row_bytes;
     g.xq = (const uint8_t*)q8k;
     g.x_f32 = x_f32;
+    g.sync = take_pending_sync(ctx);
     g.n_peers = n_peers;
     for (int i = 0; i < n_mats; i++)
         for (int pr = 0; pr < n_peers; pr++) (i == 0 ? g.y_peer[pr] : g.y_peer_more[i - 1][pr]) = y_peers[i * n_peers + pr];

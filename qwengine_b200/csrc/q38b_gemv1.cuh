@@ -33,6 +33,7 @@ struct Gemv1Args {
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     float* y_peer_more[G1_MAX_MATS - 1][7];   // the same for matrices 1 and 2
+    PeerSync sync;          // cross-GPU barrier before the column is read (the peers pushed parts of it), n = 0: none
     int n_peers;
     int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;
@@ -161,6 +162,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         }
     }
     pdl_wait_prior();
+    if (a.sync.n > 0) {
+        peer_sync_wait(a.sync, blockIdx.x == 0, ctid, a.status);
+        named_bar_sync(14, NWARPS * 32);
+    }
     if (a.x_f32) {
         // quantize the column here (every CTA, the same arithmetic as quantize_q8k_kernel): one warp per 256 values
         for (int sb = cw; sb < a.n_slices * 4; sb += NWARPS) {

@@ -92,6 +92,34 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Cross-GPU barrier folded into the prologue of a kernel (one process per GPU, peer-mapped flag blocks).  A flag block
+// holds [r] = the latest epoch rank r has signalled, [9] = the next free epoch, [10] = the first epoch of the pass run in
+// progress (written by a one-thread kernel at the start of every run, so epochs only grow whatever passes alternate).
+// Barrier number `seq` of a run has epoch [10] + seq + 1 on every rank.  n = 0: no barrier.
+struct PeerSync {
+    uint32_t* local;
+    uint32_t* peer[8];
+    int n, rank, seq;
+};
+constexpr int ST_PEER_TIMEOUT = 16;
+// Threads t = 0 .. n - 1 of every CTA call this once the stream's earlier kernels are complete (their stores into the
+// peers' buffers are done); `signaller` is true in one CTA.  Thread t tells rank t and waits (bounded) for rank t.
+__device__ __forceinline__ void peer_sync_wait(const PeerSync& ps, bool signaller, int t, int* status) {
+    if (t >= ps.n || t == ps.rank) return;
+    const uint32_t e = *(volatile uint32_t*)(ps.local + 10) + (uint32_t)ps.seq + 1u;
+    if (signaller) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ps.peer[t] + ps.rank), "r"(e) : "memory");
+    }
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ps.local + t) : "memory");
+        if ((int)(v - e) >= 0) break;
+        if (clock64() - t0 > 4000000000LL) { if (status) atomicOr(status, ST_PEER_TIMEOUT); break; }
+    }
+}
+
 // Programmatic dependent launch: let the next kernel of the stream start its prologue now; wait until the
 // kernels this one depends on have finished and their writes are visible (no-ops without the launch attribute).
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -56,27 +56,20 @@ struct Buf { void* ptr; int n; bool q8k; void* peer[8]; int n_peer_ranks; bool i
 struct Mat { uint32_t type; const void* W; size_t row_bytes; int K, M; bool owned; };
 
 struct PeerPtrs { uint32_t* p[8]; };
-constexpr int ST_PEER_TIMEOUT = 16;
 
-// Cross-GPU barrier of the peer-store gather.  Runs after the matvecs whose outputs were pushed to the peers: the
-// kernel boundary plus the system fence make those stores visible before the flag.  Lane g signals GPU g with this
-// rank's barrier count and waits (bounded, ~2 s of SM clocks) until GPU g's count has reached it.
-__global__ void peer_barrier_kernel(uint32_t* local, PeerPtrs peers, int n, int rank, int* status) {
-    const int lane = threadIdx.x;
-    uint32_t e = 0;
-    if (lane == 0) { e = local[8] + 1u; local[8] = e; }
-    e = __shfl_sync(0xffffffffu, e, 0);
-    if (lane < n && lane != rank) {
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.p[lane] + rank), "r"(e) : "memory");
-        const long long t0 = clock64();
-        for (;;) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local + lane) : "memory");
-            if ((int)(v - e) >= 0) break;
-            if (clock64() - t0 > 4000000000LL) { atomicOr(status, ST_PEER_TIMEOUT); break; }
+// Cross-GPU barrier of the peer-store gather as a kernel of its own (barriers that no matvec or SwiGLU launch follows;
+// q38b_peer_barrier).  Runs after the matvecs whose outputs were pushed to the peers: the kernel boundary plus the system
+// fence make those stores visible before the flag.  n_new > 0: first claim n_new epochs for a new run (see PeerSync).
+__global__ void peer_barrier_kernel(PeerSync ps, int n_new, int do_barrier, int* status) {
+    if (n_new > 0) {
+        if (threadIdx.x == 0) {
+            const uint32_t base = ps.local[9];
+            ps.local[10] = base;
+            ps.local[9] = base + (uint32_t)n_new;
         }
+        __syncwarp();
     }
+    if (do_barrier) peer_sync_wait(ps, true, (int)threadIdx.x, status);
 }
 
 }  // namespace
@@ -118,6 +111,23 @@ struct q38b_pass {
 namespace {
 bool is_f32(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && !p->bufs[id].q8k; }
 bool is_q8k(const q38b_pass* p, int id) { return id >= 0 && id < (int)p->bufs.size() && p->bufs[id].q8k; }
+
+PeerSync make_sync(const q38b_ctx* ctx, int seq) {
+    PeerSync ps;
+    memset(&ps, 0, sizeof(ps));
+    ps.local = ctx->d_flags;
+    for (int r = 0; r < 8; r++) ps.peer[r] = ctx->peer_flags[r];
+    ps.n = ctx->n_ranks;
+    ps.rank = ctx->rank;
+    ps.seq = seq;
+    return ps;
+}
+int launch_barrier(q38b_ctx* ctx, int n_new, int do_barrier, int seq, cudaStream_t st) {
+    peer_barrier_kernel<<<1, 32, 0, st>>>(make_sync(ctx, seq), n_new, do_barrier, ctx->d_status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
+    return Q38B_OK;
+}
 
 int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st);
 
@@ -211,6 +221,16 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     std::vector<char> skip(p->ops.size(), 0);
     if (merging(p, nb)) merge_plan(p, merged, skip);
     size_t next_merged = 0;
+    // Cross-GPU barriers of this run: numbered in order; a barrier that a merged matvec launch or a SwiGLU kernel
+    // follows is folded into that launch's prologue, the others run as a kernel of their own.
+    int n_barriers = 0, barrier_seq = 0;
+    if (ctx->n_ranks > 1 && ctx->peers_connected)
+        for (const Op& o : p->ops) n_barriers += o.kind == OP_BARRIER;
+    if (n_barriers > 0) {
+        const int rc = launch_barrier(ctx, n_barriers, 0, 0, st);   // claims the run's epochs
+        if (rc != Q38B_OK) return rc;
+    }
+    ctx->pending_sync_seq = -1;
     for (size_t oi = 0; oi < p->ops.size(); oi++) {
         while (next_merged < merged.size() && merged[next_merged].first_op == (int)oi) {
             const Merged& mg = merged[next_merged++];
@@ -276,9 +296,23 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                                      d.n / 256, st);
                 break;
             }
-            case OP_BARRIER:
-                rc = q38b_peer_barrier(ctx, st);
+            case OP_BARRIER: {
+                if (n_barriers == 0) break;
+                if (ctx->pending_sync_seq >= 0) {   // two barriers in a row: the earlier one runs by itself
+                    rc = launch_barrier(ctx, 0, 1, ctx->pending_sync_seq, st);
+                    ctx->pending_sync_seq = -1;
+                    if (rc != Q38B_OK) return rc;
+                }
+                size_t j = oi + 1;
+                while (j < p->ops.size() && (p->ops[j].kind == OP_GATHER || p->ops[j].kind == OP_BARRIER)) j++;
+                bool next_is_merged = false;   // op j opens a merged launch: its folded quantize step or its first matvec
+                for (const Merged& mg : merged) next_is_merged |= (mg.quant >= 0 ? mg.quant : mg.first_op) == (int)j;
+                const bool next_is_swiglu = j < p->ops.size() && !skip[j] && p->ops[j].kind == OP_SWIGLU;
+                const bool adjacent = j == oi + 1;   // nothing (not even a gather) between the barrier and that launch
+                if (adjacent && (next_is_merged || next_is_swiglu)) ctx->pending_sync_seq = barrier_seq++;
+                else rc = launch_barrier(ctx, 0, 1, barrier_seq++, st);
                 break;
+            }
             case OP_GATHER: {
                 if (ctx->n_ranks <= 1) break;
                 Nccl& n = nccl();
@@ -602,12 +636,7 @@ int q38b_peer_barrier(q38b_ctx* ctx, void* stream) {
     if (!ctx) return Q38B_ERR_ARG;
     if (ctx->n_ranks <= 1) return Q38B_OK;
     if (!ctx->peers_connected) return Q38B_ERR_ARG;
-    PeerPtrs pp;
-    for (int r = 0; r < 8; r++) pp.p[r] = ctx->peer_flags[r];
-    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->d_flags, pp, ctx->n_ranks, ctx->rank, ctx->d_status);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
-    return Q38B_OK;
+    return launch_barrier(ctx, 1, 1, 0, (cudaStream_t)stream);   // a run of one barrier
 }
 
 int q38b_pass_set_peer_store(q38b_pass* p, int enabled) {
