@@ -186,3 +186,53 @@ def test_merged_replay_equals_one_kernel_per_step(ctx):
         ps.close()
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
     assert counts[0] < counts[1]
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_passes_merge_invariant(ctx, seed):
+    """Random recorded passes (mixed formats, matvecs sharing and not sharing a column, quantize steps whose output is
+    or is not read again later, SwiGLU, outputs at offsets) give the same bits with and without merged launches."""
+    rng = np.random.default_rng(seed)
+    fmts = ["IQ3_XXS", "IQ4_XS", "Q4_K", "Q6_K", "IQ3_S", "Q8_0", "Q5_K"]
+    K = 1024
+    n_mats = 10
+    mats = [(fmts[int(rng.integers(len(fmts)))], int(rng.choice([256, 264, 512, 1000]))) for _ in range(n_mats)]
+    ws = [synth.make_weights(f, M, K, seed=1000 + 17 * seed + i, scale=dp.UNIT_GAIN_SCALE.get(f, 1e-4), zero_mean=True) for i, (f, M) in enumerate(mats)]
+    # a fixed program of steps drawn once, replayed on two passes
+    steps = []
+    for _ in range(14):
+        kind = rng.choice(["quant", "gemv", "gemv", "gemv", "swiglu"])
+        if kind == "quant":
+            steps.append(("quant", int(rng.integers(2)), int(rng.integers(2))))                  # source buffer, Q8_K buffer
+        elif kind == "gemv":
+            steps.append(("gemv", int(rng.integers(n_mats)), int(rng.integers(2)), int(rng.integers(3)), int(rng.choice([0, 8, 1024]))))
+        else:
+            steps.append(("swiglu", int(rng.integers(3)), int(rng.integers(3)), int(rng.integers(2))))
+    x = synth.make_activations(1, K, seed=50 + seed)
+    results = []
+    for merge in (True, False):
+        ps = q.Pass(ctx, max_nb=1)
+        ps.set_merge(merge)
+        src = [ps.buffer_f32(K), ps.buffer_f32(K)]
+        qb = [ps.buffer_q8k(K), ps.buffer_q8k(K)]
+        outs = [ps.buffer_f32(2048 + 1024) for _ in range(3)]
+        mids = [ps.matrix_upload(f, w, K) for (f, _), w in zip(mats, ws)]
+        ps.quantize(src[0], 0, K, qb[0])
+        ps.quantize(src[1], 0, K, qb[1])
+        for st in steps:
+            if st[0] == "quant":
+                ps.quantize(src[st[1]], 0, K, qb[st[2]])
+            elif st[0] == "gemv":
+                ps.gemv(mids[st[1]], qb[st[2]], outs[st[3]], st[4])
+            else:
+                ps.swiglu(outs[st[1]], 0, outs[st[2]], 1024, K, qb[st[3]])
+        for b in src:
+            ps.buffer_tensor(b).copy_(torch.from_numpy(x).cuda())
+        for _ in range(2):
+            ps.run(1)
+        torch.cuda.synchronize()
+        ctx.check()
+        results.append([ps.buffer_tensor(o).cpu().numpy().copy() for o in outs])
+        ps.close()
+    for a, b in zip(*results):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
