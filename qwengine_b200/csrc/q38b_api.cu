@@ -82,15 +82,15 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, int M, int nb, Plan* p)
                 int slot = align_up(cs * bb + 32, 16);
                 while (slot % 128 != bank_skew) slot += 16;
                 const int stage = TILE_ROWS * slot;
-                if (stage > 56 * 1024 && cs > 1) continue;
-                const int stages = avail / (NGROUPS * stage);
-                if (stages < 2) continue;
+                // one ring for both groups: each reads one stage while at least one more is being filled
+                const int stages = avail / stage;
+                if (stages < 3 && !(stages == 2 && cs == 1)) continue;
                 a.chunk_sb = cs;
                 a.n_chunks = (nsb + cs - 1) / cs;
-                a.n_stages = std::min(stages, 4);
+                a.n_stages = std::min(stages, MAX_STAGES);
                 a.slot_stride = slot;
                 a.stage_bytes = stage;
-                p->smem = a.off_stage + NGROUPS * a.n_stages * stage + 128;
+                p->smem = a.off_stage + a.n_stages * stage + 128;
                 const int ctas_needed = (a.n_tiles + NGROUPS - 1) / NGROUPS;
                 p->grid = std::max(1, std::min(ctx->sm_count, ctas_needed));
                 return Q38B_OK;

@@ -22,7 +22,7 @@ namespace q38b {
 constexpr int TILE_ROWS = 16;
 constexpr int GROUP_WARPS = 8;
 constexpr int GROUP_THREADS = GROUP_WARPS * 32;
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_STAGES = 8;
 constexpr int Q8K_BYTES = 292;   // float d | int8 qs[256] | int16 bsums[16]  (src/quant/quant_formats.h:95)
 
 struct GemvArgs {
@@ -54,17 +54,20 @@ template <int FMT, int NGROUPS>
 __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
     uint8_t* smem = smem_raw;
-    uint64_t* bars = (uint64_t*)smem;                       // full[NGROUPS][MAX_STAGES], empty[NGROUPS][MAX_STAGES]
-    volatile int* abort_flag = (volatile int*)(smem + 8 * 2 * NGROUPS * MAX_STAGES);
+    // One ring of stages for all groups: this CTA's tiles k = 0, 1, 2, ... (tile blockIdx.x + gridDim.x * k) go to group
+    // k % NGROUPS; the n_chunks stage fills of tile k are fills k * n_chunks .. + n_chunks - 1 of the ring.
+    uint64_t* bars = (uint64_t*)smem;                       // full[MAX_STAGES], empty[MAX_STAGES]
+    volatile int* abort_flag = (volatile int*)(smem + 8 * 2 * MAX_STAGES);   // the header ends well before off_actd = 256
+    int* issued = (int*)abort_flag + 1;                     // stage fills the producer has issued so far
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int g = 0; g < NGROUPS; g++)
-            for (int s = 0; s < a.n_stages; s++) {
-                mbar_init(smem_u32(&bars[g * MAX_STAGES + s]), TILE_ROWS);                        // full: one arrival per row copy
-                mbar_init(smem_u32(&bars[(NGROUPS + g) * MAX_STAGES + s]), GROUP_WARPS);          // empty: one per consumer warp
-            }
+        *issued = 0;
+        for (int s = 0; s < a.n_stages; s++) {
+            mbar_init(smem_u32(&bars[s]), TILE_ROWS);                        // full: one arrival per row copy
+            mbar_init(smem_u32(&bars[MAX_STAGES + s]), GROUP_WARPS);         // empty: one per warp of the group that reads the stage
+        }
         mbar_fence_init();
     }
     __syncthreads();
@@ -79,43 +82,43 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         if (lane < TILE_ROWS) {
             const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
             const uintptr_t safe_end = w_end & ~(uintptr_t)15;
-            int item[NGROUPS];
-            bool more = true;
-            for (int g = 0; g < NGROUPS; g++) item[g] = 0;
-            for (int it = 0; more; it++) {
-                more = false;
-                for (int g = 0; g < NGROUPS; g++) {
-                    const int tile = blockIdx.x + gridDim.x * (g + NGROUPS * (it / a.n_chunks));
-                    if (tile >= a.n_tiles) continue;
-                    more = true;
-                    const int chunk = it % a.n_chunks;
-                    const int stage = item[g] % a.n_stages;
-                    const uint32_t use = (uint32_t)(item[g] / a.n_stages);
-                    item[g]++;
-                    const uint32_t full = smem_u32(&bars[g * MAX_STAGES + stage]);
-                    const uint32_t empty = smem_u32(&bars[(NGROUPS + g) * MAX_STAGES + stage]);
-                    mbar_wait_bounded(empty, (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+            int item = 0, stage = 0;
+            uint32_t use = 0;
+            for (int k = 0;; k++) {
+                const int tile = blockIdx.x + gridDim.x * k;
+                if (tile >= a.n_tiles) break;
+                for (int chunk = 0; chunk < a.n_chunks; chunk++) {
+                    const uint32_t full = smem_u32(&bars[stage]);
+                    const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
+                    mbar_wait_bounded(empty, use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
                     const int row = tile * TILE_ROWS + lane;
-                    if (row >= a.M) { mbar_arrive(full); continue; }
-                    const int sb0 = chunk * a.chunk_sb;
-                    const int len = (sb0 + a.chunk_sb <= a.nsb ? chunk_bytes_full : (a.nsb - sb0) * Unit<FMT>::BLOCK_BYTES);
-                    const uintptr_t src = (uintptr_t)a.W + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
-                    const uintptr_t lo = src & ~(uintptr_t)15;
-                    uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
-                    uint8_t* slot = smem + a.off_stage + (size_t)(g * a.n_stages + stage) * a.stage_bytes + (size_t)lane * a.slot_stride;
-                    if (hi > safe_end) {
-                        // the last bytes of the tensor do not fill a 16-byte unit: fetch them with plain loads
-                        hi = safe_end > lo ? safe_end : lo;
-                        for (uintptr_t p = hi; p < src + len; p += 2)
-                            if (p >= src) *(uint16_t*)(slot + (p - lo)) = *(const uint16_t*)p;
-                    }
-                    const uint32_t bytes = (uint32_t)(hi - lo);
-                    if (bytes) {
-                        mbar_arrive_expect_tx(full, bytes);
-                        bulk_copy_g2s(smem_u32(slot), (const void*)lo, bytes, full);
-                    } else {
+                    if (row >= a.M) {
                         mbar_arrive(full);
+                    } else {
+                        const int sb0 = chunk * a.chunk_sb;
+                        const int len = (sb0 + a.chunk_sb <= a.nsb ? chunk_bytes_full : (a.nsb - sb0) * Unit<FMT>::BLOCK_BYTES);
+                        const uintptr_t src = (uintptr_t)a.W + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+                        const uintptr_t lo = src & ~(uintptr_t)15;
+                        uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
+                        uint8_t* slot = smem + a.off_stage + (size_t)stage * a.stage_bytes + (size_t)lane * a.slot_stride;
+                        if (hi > safe_end) {
+                            // the last bytes of the tensor do not fill a 16-byte unit: fetch them with plain loads
+                            hi = safe_end > lo ? safe_end : lo;
+                            for (uintptr_t p = hi; p < src + len; p += 2)
+                                if (p >= src) *(uint16_t*)(slot + (p - lo)) = *(const uint16_t*)p;
+                        }
+                        const uint32_t bytes = (uint32_t)(hi - lo);
+                        if (bytes) {
+                            mbar_arrive_expect_tx(full, bytes);
+                            bulk_copy_g2s(smem_u32(slot), (const void*)lo, bytes, full);
+                        } else {
+                            mbar_arrive(full);
+                        }
                     }
+                    item++;
+                    if (++stage == a.n_stages) { stage = 0; use ^= 1u; }
+                    __syncwarp((1u << TILE_ROWS) - 1u);
+                    if (lane == 0) st_release_shared(smem_u32(issued), item);
                 }
             }
         }
@@ -169,21 +172,25 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
     const bool bvalid = g < a.nb;
     const uint8_t* bq_col = actq + (size_t)(bvalid ? g : 0) * a.K;
 
-    int item = 0;
     for (int ti = 0;; ti++) {
-        const int tile = blockIdx.x + gridDim.x * (grp + NGROUPS * ti);
+        const int k = grp + NGROUPS * ti;                // this CTA's tile number k
+        const int tile = blockIdx.x + gridDim.x * k;
         if (tile >= a.n_tiles) break;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const int rowA = tile * TILE_ROWS + g, rowB = rowA + 8;
-        for (int chunk = 0; chunk < a.n_chunks; chunk++, item++) {
+        for (int chunk = 0; chunk < a.n_chunks; chunk++) {
+            const int item = k * a.n_chunks + chunk;
             const int stage = item % a.n_stages;
             const uint32_t use = (uint32_t)(item / a.n_stages);
-            const uint32_t full = smem_u32(&bars[grp * MAX_STAGES + stage]);
-            const uint32_t empty = smem_u32(&bars[(NGROUPS + grp) * MAX_STAGES + stage]);
+            const uint32_t full = smem_u32(&bars[stage]);
+            const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
+            // a group reads only its own tiles' fills, so it skips uses of a barrier: once the fill has been issued (the
+            // producer issues it after the readers of the stage's previous fill released it) the parity is unambiguous
+            wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             mbar_wait_bounded(full, use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             const int sb0 = chunk * a.chunk_sb;
             const int nsb_c = min(a.chunk_sb, a.nsb - sb0);
-            const uint8_t* st = smem + a.off_stage + (size_t)(grp * a.n_stages + stage) * a.stage_bytes;
+            const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes;
             const uintptr_t srcA = (uintptr_t)a.W + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
             const uintptr_t srcB = srcA + 8 * (uintptr_t)a.row_bytes;
             const uint8_t* baseA = st + (size_t)g * a.slot_stride + (srcA & 15);
