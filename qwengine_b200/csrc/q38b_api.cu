@@ -55,14 +55,19 @@ struct Plan {
 
 // Carves the 227 KB of shared memory of one CTA: barriers | activation scales | activations | codebook |
 // reduction buffers | NGROUPS rings of n_stages stages of 16 row slots.
-int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, int M, int nb, Plan* p) {
+int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, int nb, Plan* p) {
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
     int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
     const int budget = ctx->smem_optin - 128;   // base is aligned up to 128 inside the kernel
     GemvArgs& a = p->a;
     a.nsb = nsb;
-    a.n_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
+    a.n_tiles = 0;
+    for (int i = 0; i < GEMV_MAX_MATS; i++) {
+        a.tile_start[i] = a.n_tiles;
+        if (i < n_mats) a.n_tiles += (Ms[i] + TILE_ROWS - 1) / TILE_ROWS;
+    }
+    for (int i = n_mats; i < GEMV_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
     a.off_actd = 256;
     a.off_actq = a.off_actd + align_up(nsb * 32, 16);
     a.off_cb = a.off_actq + align_up(nb * K, 128);
@@ -369,6 +374,11 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x, long long x_ld, int K, int 
 }
 
 // takes the cross-GPU barrier the planner left for the next launch, if any
+// rows so long that the multi-column kernel runs them as two launches over the halves of K
+static bool gemvn_splits_k(uint32_t type, int K) {
+    return K > 8192 && (K / 256) % 2 == 0 && type != T_Q8_0 && ((size_t)(K / 512) * block_bytes((int)type)) % 16 == 0;
+}
+
 static PeerSync take_pending_sync(q38b_ctx* ctx) {
     PeerSync ps;
     memset(&ps, 0, sizeof(ps));
@@ -446,7 +456,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     // Long rows on the multi-column kernel: the staged activations (nb x K bytes) would leave almost no shared memory
     // for the weight stages, so the matvec runs as two launches over the two halves of K, the second accumulating onto
     // the first.  The rule depends on K and the format alone: columns stay bit-identical for every nb this kernel serves.
-    if (K > 8192 && (K / 256) % 2 == 0 && type != T_Q8_0 && ((size_t)(K / 512) * block_bytes((int)type)) % 16 == 0) {   // the second half must start 16-byte aligned like any matrix
+    if (gemvn_splits_k(type, K)) {   // (the second half must start 16-byte aligned like any matrix)
         const int Kh = K / 2;
         const size_t w_off = (size_t)(Kh / 256) * block_bytes((int)type);
         int rc = q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, Kh, M, q8k, q8k_stride, nb, y, y_ld, accumulate, y_peers, n_peers, stream);
@@ -456,7 +466,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     }
     Plan p;
     memset(&p, 0, sizeof(p));
-    int rc = plan_gemv(ctx, type, K, M, nb, &p);
+    int rc = plan_gemv(ctx, type, K, &M, 1, nb, &p);
     if (rc != Q38B_OK) return rc;
     GemvArgs& a = p.a;
     a.W = (const uint8_t*)W;
@@ -474,6 +484,62 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     a.M = M;
     a.nb = nb;
     a.accumulate = accumulate ? 1 : 0;
+    switch (type) {
+        case T_Q8_0: return launch_gemv<T_Q8_0>(ctx, p, st);
+        case T_Q4_K: return launch_gemv<T_Q4_K>(ctx, p, st);
+        case T_Q5_K: return launch_gemv<T_Q5_K>(ctx, p, st);
+        case T_Q6_K: return launch_gemv<T_Q6_K>(ctx, p, st);
+        case T_IQ3_XXS: return launch_gemv<T_IQ3_XXS>(ctx, p, st);
+        case T_IQ3_S: return launch_gemv<T_IQ3_S>(ctx, p, st);
+        case T_IQ4_XS: return launch_gemv<T_IQ4_XS>(ctx, p, st);
+        default: return Q38B_ERR_UNSUPPORTED;
+    }
+}
+
+int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb) {
+    if (!ctx || n_mats < 1 || n_mats > GEMV_MAX_MATS || !known_format(type) || K <= 0 || K % 256 || nb < 1 || nb > 8) return 0;
+    if (gemvn_splits_k(type, K) || row_bytes < q38b_row_bytes(type, K)) return 0;
+    Plan p;
+    memset(&p, 0, sizeof(p));
+    return plan_gemv(ctx, type, K, M, n_mats, nb, &p) == Q38B_OK;
+}
+
+int q38b_gemvn_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                     const void* q8k, long long q8k_stride, int nb, float* const* y, const long long* y_ld, void* stream) {
+    if (!ctx || !W || !M || !y || !y_ld || !q8k || n_mats < 1 || n_mats > GEMV_MAX_MATS) return Q38B_ERR_ARG;
+    if (!q38b_gemvn_group_plannable(ctx, type, n_mats, row_bytes, K, M, nb)) return Q38B_ERR_UNSUPPORTED;
+    const int al = format_alignment(type);
+    if ((row_bytes % al) || ((uintptr_t)q8k & 3) || q8k_stride < K / 256) return Q38B_ERR_ALIGN;
+    for (int i = 0; i < n_mats; i++) {
+        if (!W[i] || !y[i] || M[i] < 1 || y_ld[i] < M[i]) return Q38B_ERR_ARG;
+        if (((uintptr_t)W[i] & 15) || ((uintptr_t)y[i] & 3)) return Q38B_ERR_ALIGN;
+    }
+    Plan p;
+    memset(&p, 0, sizeof(p));
+    const int rc = plan_gemv(ctx, type, K, M, n_mats, nb, &p);
+    if (rc != Q38B_OK) return rc;
+    GemvArgs& a = p.a;
+    a.W = (const uint8_t*)W[0];
+    a.y = y[0];
+    a.y_ld = y_ld[0];
+    a.M = M[0];
+    for (int i = 1; i < n_mats; i++) {
+        a.W_more[i - 1] = (const uint8_t*)W[i];
+        a.y_more[i - 1] = y[i];
+        a.y_ld_more[i - 1] = y_ld[i];
+        a.M_more[i - 1] = M[i];
+    }
+    a.row_bytes = (long long)row_bytes;
+    a.xq = (const uint8_t*)q8k;
+    a.x_stride = q8k_stride;
+    a.n_peers = 0;
+    a.static_weights = ctx->static_weights;
+    a.status = ctx->d_status;
+    a.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+    a.K = K;
+    a.nb = nb;
+    a.accumulate = 0;
+    cudaStream_t st = (cudaStream_t)stream;
     switch (type) {
         case T_Q8_0: return launch_gemv<T_Q8_0>(ctx, p, st);
         case T_Q4_K: return launch_gemv<T_Q4_K>(ctx, p, st);

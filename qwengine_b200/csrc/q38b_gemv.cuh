@@ -25,7 +25,16 @@ constexpr int GROUP_THREADS = GROUP_WARPS * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int Q8K_BYTES = 292;   // float d | int8 qs[256] | int16 bsums[16]  (src/quant/quant_formats.h:95)
 
+constexpr int GEMV_MAX_MATS = 3;
+
 struct GemvArgs {
+    // up to three matrices of one format, K and row stride on the same activation columns: their 16-row tiles form one
+    // sequence (matrix 0's, then matrix 1's, ...), one launch replaces three
+    const uint8_t* W_more[GEMV_MAX_MATS - 1];
+    float* y_more[GEMV_MAX_MATS - 1];
+    long long y_ld_more[GEMV_MAX_MATS - 1];
+    int M_more[GEMV_MAX_MATS - 1];
+    int tile_start[GEMV_MAX_MATS];   // first tile of each matrix (unused ones = n_tiles)
     const uint8_t* W;        // [M] rows, row_bytes apart, GGUF blocks
     long long row_bytes;
     const uint8_t* xq;       // Q8_K blocks; column c starts at xq + c * x_stride * 292
@@ -80,24 +89,27 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         // ---------------- producer: resident weights do not depend on earlier kernels, start at once ----------------
         if (!a.static_weights) pdl_wait_prior();   // otherwise W may be the output of the kernel before this one
         if (lane < TILE_ROWS) {
-            const uintptr_t w_end = (uintptr_t)a.W + (uintptr_t)(a.M - 1) * a.row_bytes + packed_row;
-            const uintptr_t safe_end = w_end & ~(uintptr_t)15;
             int item = 0, stage = 0;
             uint32_t use = 0;
             for (int k = 0;; k++) {
-                const int tile = blockIdx.x + gridDim.x * k;
-                if (tile >= a.n_tiles) break;
+                const int gtile = blockIdx.x + gridDim.x * k;
+                if (gtile >= a.n_tiles) break;
+                const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+                const int tile = gtile - a.tile_start[mi];
+                const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
+                const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
+                const uintptr_t safe_end = ((uintptr_t)Wm + (uintptr_t)(Mm - 1) * a.row_bytes + packed_row) & ~(uintptr_t)15;
                 for (int chunk = 0; chunk < a.n_chunks; chunk++) {
                     const uint32_t full = smem_u32(&bars[stage]);
                     const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
                     mbar_wait_bounded(empty, use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
                     const int row = tile * TILE_ROWS + lane;
-                    if (row >= a.M) {
+                    if (row >= Mm) {
                         mbar_arrive(full);
                     } else {
                         const int sb0 = chunk * a.chunk_sb;
                         const int len = (sb0 + a.chunk_sb <= a.nsb ? chunk_bytes_full : (a.nsb - sb0) * Unit<FMT>::BLOCK_BYTES);
-                        const uintptr_t src = (uintptr_t)a.W + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+                        const uintptr_t src = (uintptr_t)Wm + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
                         const uintptr_t lo = src & ~(uintptr_t)15;
                         uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
                         uint8_t* slot = smem + a.off_stage + (size_t)stage * a.stage_bytes + (size_t)lane * a.slot_stride;
@@ -174,8 +186,11 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
 
     for (int ti = 0;; ti++) {
         const int k = grp + NGROUPS * ti;                // this CTA's tile number k
-        const int tile = blockIdx.x + gridDim.x * k;
-        if (tile >= a.n_tiles) break;
+        const int gtile = blockIdx.x + gridDim.x * k;
+        if (gtile >= a.n_tiles) break;
+        const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+        const int tile = gtile - a.tile_start[mi];        // tile of matrix mi
+        const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const int rowA = tile * TILE_ROWS + g, rowB = rowA + 8;
         for (int chunk = 0; chunk < a.n_chunks; chunk++) {
@@ -191,7 +206,7 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             const int sb0 = chunk * a.chunk_sb;
             const int nsb_c = min(a.chunk_sb, a.nsb - sb0);
             const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes;
-            const uintptr_t srcA = (uintptr_t)a.W + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+            const uintptr_t srcA = (uintptr_t)Wm + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
             const uintptr_t srcB = srcA + 8 * (uintptr_t)a.row_bytes;
             const uint8_t* baseA = st + (size_t)g * a.slot_stride + (srcA & 15);
             const uint8_t* baseB = st + (size_t)(g + 8) * a.slot_stride + (srcB & 15);
@@ -220,8 +235,9 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             for (int w = 0; w < GROUP_WARPS; w++) v += rbuf[(w * 32 + ls) * 4 + i];
             const int row = tile * TILE_ROWS + (ls >> 2) + 8 * (i >> 1);
             const int col = 2 * (ls & 3) + (i & 1);
-            if (row < a.M && col < a.nb) {
-                float* yo = a.y + (size_t)col * a.y_ld + row;
+            const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
+            if (row < Mm && col < a.nb) {
+                float* yo = (mi == 0 ? a.y : a.y_more[mi - 1]) + (size_t)col * (mi == 0 ? a.y_ld : a.y_ld_more[mi - 1]) + row;
                 const float out = a.accumulate ? *yo + v : v;
                 *yo = out;
                 for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][(size_t)col * a.y_ld + row] = out;

@@ -32,3 +32,7 @@ extern "C" int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int
 // q38b_gemv_group with peer stores: y_peers[i * n_peers + r] is where peer r keeps the output of matrix i
 extern "C" int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                                      const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream);
+// the same for the multi-column kernel (nb columns of Q8_K blocks, q8k_stride blocks apart; y[i][c * y_ld[i] + r]); no peers
+extern "C" int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb);
+extern "C" int q38b_gemvn_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                                const void* q8k, long long q8k_stride, int nb, float* const* y, const long long* y_ld, void* stream);

@@ -149,7 +149,7 @@ struct Merged { int first_op; int n; int ops[3]; int quant; };
 // Which steps of a single-column replay on one GPU can share launches.  A quantize step is folded into the matvecs that
 // read its output when they follow it directly, nothing else reads that output before it is rewritten, and all of them
 // run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
-void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>& skip) {
+void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vector<char>& skip) {
     const q38b_ctx* ctx = p->ctx;
     const std::vector<Op>& ops = p->ops;
     const size_t n = ops.size();
@@ -161,6 +161,10 @@ void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>&
     while (i < n) {
         int quant = -1;
         size_t g0 = i;
+        if (ops[i].kind == OP_QUANT && nb > 1) {   // several columns: the quantize step stays a kernel (each CTA would redo nb x K values)
+            i = next_real(i + 1);
+            continue;
+        }
         if (ops[i].kind == OP_QUANT) {
             const int col = ops[i].b;
             const size_t j = next_real(i + 1);
@@ -194,9 +198,11 @@ void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>&
             while (on_column(k, col) && mg.n < 3) {
                 const Mat& m = p->mats[ops[k].a];
                 if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
-                if (p->bufs[ops[k].c].n_peer_ranks != p->bufs[ops[mg.first_op].c].n_peer_ranks) break;   // peer-visible outputs or not: one kind per launch
+                if (p->bufs[ops[k].c].n_peer_ranks != p->bufs[ops[mg.first_op].c].n_peer_ranks) break;
+                if (nb > 1 && mg.n >= 1 && ctx->n_ranks > 1) break;   // the multi-column kernel pushes to the peers for one matrix only   // peer-visible outputs or not: one kind per launch
                 Ms[mg.n] = m.M;
-                if (!q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)) break;
+                if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)
+                            : !q38b_gemvn_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms, nb)) break;
                 mg.ops[mg.n++] = (int)k;
                 k = next_real(k + 1);
             }
@@ -213,13 +219,13 @@ void merge_plan(const q38b_pass* p, std::vector<Merged>& out, std::vector<char>&
     }
 }
 
-bool merging(const q38b_pass* p, int nb) { return nb == 1 && p->merge_steps && !p->ctx->uniform_columns; }
+bool merging(const q38b_pass* p, int nb) { return p->merge_steps && (nb > 1 || !p->ctx->uniform_columns); }
 
 int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
     q38b_ctx* ctx = p->ctx;
     std::vector<Merged> merged;
     std::vector<char> skip(p->ops.size(), 0);
-    if (merging(p, nb)) merge_plan(p, merged, skip);
+    if (merging(p, nb)) merge_plan(p, nb, merged, skip);
     size_t next_merged = 0;
     // Cross-GPU barriers of this run: numbered in order; a barrier that a merged matvec launch or a SwiGLU kernel
     // follows is folded into that launch's prologue, the others run as a kernel of their own.
@@ -246,6 +252,14 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
             }
             const Op& g0 = p->ops[mg.ops[0]];
             const Mat& m0 = p->mats[g0.a];
+            if (nb > 1) {
+                long long ylds[3];
+                for (int t = 0; t < mg.n; t++) ylds[t] = p->bufs[p->ops[mg.ops[t]].c].n;
+                const Buf& sb = p->bufs[g0.b];
+                const int rc = q38b_gemvn_group(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, sb.ptr, sb.n / 256, nb, y, ylds, st);
+                if (rc != Q38B_OK) return rc;
+                continue;
+            }
             const void* q8k = mg.quant >= 0 ? nullptr : p->bufs[g0.b].ptr;
             const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
             float* peers[3 * 7];
@@ -857,7 +871,7 @@ int q38b_pass_kernel_count(const q38b_pass* p) {
     int n = 0;
     std::vector<Merged> merged;
     std::vector<char> skip(p->ops.size(), 0);
-    if (merging(p, 1)) merge_plan(p, merged, skip);
+    if (merging(p, 1)) merge_plan(p, 1, merged, skip);
     for (size_t i = 0; i < p->ops.size(); i++) {
         const Op& o = p->ops[i];
         n += !skip[i] && (o.kind != OP_GATHER) && (o.kind != OP_BARRIER || p->ctx->n_ranks > 1);
