@@ -2,7 +2,7 @@
 //
 // One CTA per SM, 16 warps.  The weight tiles of this CTA (contiguous rows, one bulk copy each), of all matvecs of the
 // pass in order, stream through a ring of equal shared-memory slots: tile i lives in slot i % S.  There is no producer
-// warp: the warp that finishes a tile (it has waited for every other reader of the slot) issues the copy of tile i + S
+// warp: the warp that finishes a tile (the last of its readers to arrive on the slot's counter) issues the copy of tile i + S
 // into the slot it just freed, walking on into the next matvecs when this one has no more tiles.  The matrices of a pass
 // are resident and never written, so the ring stays full across matvec boundaries and HBM stays busy while the warps
 // synchronise.
@@ -10,7 +10,7 @@
 // A tile is cut into units of (1024-weight slice, 2 or 4 rows); units go round-robin to the warps, so all warps work on
 // one or two tiles at a time and the other slots hold copies in flight (throughput = bytes in flight / latency).  A lane
 // owns one granule of the slice, keeps its activations in registers for the rows of the unit, and the row sums of a unit
-// go to the slot's (slice, row) table; the warp that owns the tile's last unit waits for the others (per-slot mbarrier),
+// go to the slot's (slice, row) table; whichever warp completes the tile's last unit (a counter per slot, nobody waits)
 // adds the slices in order and writes y.
 //
 // Ops are cut into groups: a run of matvecs that read the same activation vector and do not depend on one another, or
@@ -40,7 +40,7 @@ constexpr int FU_WARPS = Q38B_FU_WARPS;          // warps per CTA
 constexpr int FU_CTAS_PER_SM = Q38B_FU_CTAS_PER_SM;
 constexpr int FU_THREADS = 32 * FU_WARPS;
 constexpr int FU_MAX_SLOTS = 16;
-constexpr int FU_BAR_COUNT = 64;                  // arrivals a slot's "tile done" barrier expects = most units a tile may have
+constexpr int FU_BAR_COUNT = 64;                  // most units a tile may have
 constexpr int FU_HEADER_BYTES = 1024;
 constexpr int FU_RING_SLACK = 1024;               // granules past a ragged row end are read (and discarded)
 
