@@ -201,21 +201,6 @@ int q38b_pass_kernel_count(const q38b_pass* pass);
  * column share a launch (q38b_gemv_group), and a quantize step whose output only feeds the matvecs right after it is
  * folded into them.  Results are bit-identical either way; enabled = 0 replays one kernel per recorded step. */
 int q38b_pass_set_merge(q38b_pass* pass, int enabled);
-/* Experimental, off by default: with enabled = 1, single-column runs (nb = 1) of a pass on one GPU execute as ONE
- * persistent cooperative kernel that streams the weights of consecutive matvecs without draining between them
- * (bit-identical to the kernel-by-kernel replay, which remains the path for nb > 1, for several ranks, and for passes
- * whose rows are not packed).  No counterpart in the reference, whose decode loop launches one kernel per op
- * (src/runtime/engine.cpp:1770-1849). */
-int q38b_pass_set_fused(q38b_pass* pass, int enabled);
-/* 1 when q38b_pass_run(pass, 1, ...) uses the persistent kernel for the steps recorded so far. */
-int q38b_pass_fused_active(q38b_pass* pass);
-/* Tracing of the persistent kernel.  enable = 1 switches cycle counters on for later runs; counters10 (may be NULL)
- * receives and clears them after synchronising the device, summed over all warps: [0] cycles waited for weight tiles,
- * [1] for the other units of a tile, [2] at group boundaries, [3] warp cycles in total, [4] the part of [2] spent
- * waiting for the CTA's own warps, [5] the part of [2] spent waiting for the other CTAs, [6] tiles copied, [7] units, [8] issue-to-landing cycles summed over the
- * copies a warp had to wait for, [9] the number of such waits. */
-int q38b_pass_fused_trace(q38b_pass* pass, int enable, unsigned long long* counters10);
-
 #ifdef __cplusplus
 }
 #endif

@@ -86,11 +86,8 @@ def load_library():
     lib.q38b_pass_weight_bytes.argtypes = [vp]
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
-    lib.q38b_pass_set_fused.argtypes = [vp, i32]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
-    lib.q38b_pass_fused_active.argtypes = [vp]
-    lib.q38b_pass_fused_trace.argtypes = [vp, i32, vp]
     _LIB = lib
     return lib
 
@@ -321,25 +318,6 @@ class Pass:
     def set_merge(self, enabled):
         """enabled=False: single-column runs launch one kernel per recorded step (no shared launches, no folded quantize)."""
         self.ctx._rc(self.lib.q38b_pass_set_merge(self.h, int(bool(enabled))), "q38b_pass_set_merge")
-
-    def set_fused(self, enabled):
-        """enabled=False: single-column runs replay kernel by kernel instead of running as one persistent kernel."""
-        self.ctx._rc(self.lib.q38b_pass_set_fused(self.h, int(bool(enabled))), "q38b_pass_set_fused")
-
-    @property
-    def fused_active(self):
-        return bool(self.lib.q38b_pass_fused_active(self.h))
-
-    def fused_trace(self, enable=True, read=False):
-        """Switches the persistent kernel's cycle counters on or off; read=True returns and clears them (dict)."""
-        import ctypes
-        buf = (ctypes.c_ulonglong * 10)() if read else None
-        self.ctx._rc(self.lib.q38b_pass_fused_trace(self.h, int(bool(enable)), buf), "q38b_pass_fused_trace")
-        if not read:
-            return None
-        names = ["wait_tile_cycles", "wait_units_cycles", "group_cycles", "warp_cycles", "group_barrier_cycles", "group_dependency_cycles",
-                 "tiles", "units", "waited_copy_latency_cycles_sum", "waited_copies"]
-        return dict(zip(names, [int(v) for v in buf]))
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -31,6 +31,17 @@ constexpr int GEMV_THREADS = 32 * (1 + NGROUPS * GROUP_WARPS);
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
+// Opt-in shared-memory size of a kernel, set once per context (= per device) and kernel; the record lives in the
+// context, so two contexts on two devices never disturb each other.
+int ensure_kernel_smem(q38b_ctx* ctx, const void* kern, int dyn_smem_bytes, bool max_carveout) {
+    for (int i = 0; i < ctx->n_configured; i++)
+        if (ctx->configured[i] == kern) return Q38B_OK;
+    Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem_bytes));
+    if (max_carveout) Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    if (ctx->n_configured < (int)(sizeof(ctx->configured) / sizeof(ctx->configured[0]))) ctx->configured[ctx->n_configured++] = kern;
+    return Q38B_OK;
+}
+
 bool known_format(uint32_t t) {
     switch (t) {
         case T_Q8_0: case T_Q4_K: case T_Q5_K: case T_Q6_K: case T_IQ3_XXS: case T_IQ3_S: case T_IQ4_XS: return true;
@@ -108,11 +119,8 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
 template <int FMT>
 int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     auto kern = gemv_kernel<FMT, NGROUPS>;
-    static int configured_device = -1;   // one opt-in per process and device is enough
-    if (configured_device != ctx->device) {
-        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin));
-        configured_device = ctx->device;
-    }
+    const int rc = ensure_kernel_smem(ctx, (const void*)kern, ctx->smem_optin, false);
+    if (rc != Q38B_OK) return rc;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)p.grid);
@@ -137,17 +145,23 @@ struct Plan1 {
     int grid;
     int smem;
     int rows;   // rows per tile: 8, 4 or 2
+    int rg;     // 1: row-group mapping (tables in static shared memory, activations staged twice)
 };
+
+// The row-group decoders want every row to start 8 bytes aligned: W is 16-byte aligned, so the row stride decides.
+bool rowgroup_eligible(uint32_t type, size_t row_bytes, int rows) { return type == T_IQ3_XXS && row_bytes % 8 == 0 && rows % 4 == 0; }
 
 // Shared-memory carve-up of the single-column kernel: barriers | activation scales | activations | codebook |
 // per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
 int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, Plan1* p) {
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
-    const int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
-    const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128;
+    const int rg = rowgroup_eligible(type, row_bytes, G1_ROWS) ? 1 : 0;
+    const int cb_entries = rg ? 0 : type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;   // row groups keep their tables in static shared memory
+    const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128 - (rg ? RG_STATIC_BYTES : 0);
     Gemv1Args& a = p->a;
     p->rows = G1_ROWS;
+    p->rg = rg;
     a.nsb = nsb;
     a.n_slices = (nsb + 3) / 4;
     a.n_tiles = 0;
@@ -158,7 +172,7 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
     for (int i = n_mats; i < G1_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
     a.off_actd = 2048;
     a.off_actq = a.off_actd + a.n_slices * 4 * 32;
-    a.off_cb = a.off_actq + a.n_slices * 1024;
+    a.off_cb = a.off_actq + a.n_slices * (rg ? 4 * ACTR_BLOCK_BYTES : 1024);
     const int packed = nsb * bb;
     // stage shape: 8 whole rows in one bulk copy when the rows are packed and small enough, else 8 per-row copies of a
     // K-chunk of `chunk_slices` slices (bulk copies are issue-rate limited: keep each above ~2 KB)
@@ -182,7 +196,7 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
     for (int rep_log2 = cb_entries ? cb1_rep_log2((int)type) : 0; rep_log2 >= (cb_entries ? cb1_rep_log2((int)type) : 0); rep_log2--) {   // the replica count is part of the format's decoder
         a.cb_rep_log2 = rep_log2;
         a.off_sgn = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
-        a.off_red = a.off_sgn + (type == T_IQ3_XXS ? KSIGN_TABLE_BYTES : 0);
+        a.off_red = a.off_sgn + (type == T_IQ3_XXS && !rg ? KSIGN_TABLE_BYTES : 0);
         for (int stages = G1_MAX_STAGES; stages >= min_stages; stages--) {
             // tile buffers: a warp can run at most (stages + warps) units ahead of a tile that is still being finished
             const int tb = (G1_WARPS + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;
@@ -212,15 +226,11 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_m
     return Q38B_ERR_NOMEM;
 }
 
-template <int FMT, int ROWS>
+template <int FMT, int ROWS, bool RG>
 int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS>;
-    static int configured_device = -1;
-    if (configured_device != ctx->device) {
-        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G1_SMEM_BUDGET));
-        Q38B_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-        configured_device = ctx->device;
-    }
+    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS, RG>;
+    const int rc = ensure_kernel_smem(ctx, (const void*)kern, G1_SMEM_BUDGET - (RG ? RG_STATIC_BYTES : 0), true);
+    if (rc != Q38B_OK) return rc;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)p.grid);
@@ -238,10 +248,14 @@ int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
 
 template <int FMT>
 int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
+    if constexpr (FMT == T_IQ3_XXS) {
+        if (p.rg && p.rows == 8) return launch_gemv1_rows<FMT, 8, true>(ctx, p, st);
+        if (p.rg && p.rows == 4) return launch_gemv1_rows<FMT, 4, true>(ctx, p, st);
+    }
     switch (p.rows) {
-        case 8: return launch_gemv1_rows<FMT, 8>(ctx, p, st);
-        case 4: return launch_gemv1_rows<FMT, 4>(ctx, p, st);
-        case 2: return launch_gemv1_rows<FMT, 2>(ctx, p, st);
+        case 8: return launch_gemv1_rows<FMT, 8, false>(ctx, p, st);
+        case 4: return launch_gemv1_rows<FMT, 4, false>(ctx, p, st);
+        case 2: return launch_gemv1_rows<FMT, 2, false>(ctx, p, st);
         default: return Q38B_ERR_ARG;
     }
 }

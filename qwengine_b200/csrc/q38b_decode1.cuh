@@ -9,6 +9,10 @@
 // Compiles for the host too (the CPU unit test runs the 32 lanes one after the other).
 #pragma once
 #include "q38b_decode.cuh"
+#if !defined(__CUDA_ARCH__)
+#include <cstdio>
+#include <cstdlib>
+#endif
 
 namespace q38b {
 
@@ -65,11 +69,13 @@ inline SP sp_from(const void* p) { return SP{(const uint8_t*)p}; }
 inline uint32_t sp_low2(SP p) { return (uint32_t)((uintptr_t)p.a & 2); }
 inline uint32_t sp_ld8(SP p, int o = 0) { return p.a[o]; }
 inline int sp_ld8s(SP p, int o = 0) { return (int8_t)p.a[o]; }
-inline uint32_t sp_ld16(SP p, int o = 0) { uint16_t v; memcpy(&v, p.a + o, 2); return v; }
-inline uint32_t sp_ld32(SP p, int o = 0) { uint32_t v; memcpy(&v, p.a + o, 4); return v; }
-inline float sp_ldf(SP p, int o = 0) { float v; memcpy(&v, p.a + o, 4); return v; }
-inline void sp_ld64(SP p, int o, uint32_t& x, uint32_t& y) { memcpy(&x, p.a + o, 4); memcpy(&y, p.a + o + 4, 4); }
-inline void sp_ld128(SP p, int o, uint32_t (&v)[4]) { memcpy(v, p.a + o, 16); }
+// the host versions refuse what the device would fault on: an address that is not a multiple of the access size
+inline void sp_check_aligned(const uint8_t* p, int n) { if ((uintptr_t)p % (uintptr_t)n) { fprintf(stderr, "misaligned %d-byte shared load\n", n); abort(); } }
+inline uint32_t sp_ld16(SP p, int o = 0) { uint16_t v; sp_check_aligned(p.a + o, 2); memcpy(&v, p.a + o, 2); return v; }
+inline uint32_t sp_ld32(SP p, int o = 0) { uint32_t v; sp_check_aligned(p.a + o, 4); memcpy(&v, p.a + o, 4); return v; }
+inline float sp_ldf(SP p, int o = 0) { float v; sp_check_aligned(p.a + o, 4); memcpy(&v, p.a + o, 4); return v; }
+inline void sp_ld64(SP p, int o, uint32_t& x, uint32_t& y) { sp_check_aligned(p.a + o, 8); memcpy(&x, p.a + o, 4); memcpy(&y, p.a + o + 4, 4); }
+inline void sp_ld128(SP p, int o, uint32_t (&v)[4]) { sp_check_aligned(p.a + o, 16); memcpy(v, p.a + o, 16); }
 #endif
 Q38B_HD SP operator+(SP p, int o) { return SP{p.a + o}; }
 Q38B_HD SP operator-(SP p, int o) { return SP{p.a - o}; }
@@ -374,6 +380,102 @@ template <> struct Gran<T_Q8_0> {
             prev = next;
         }
         return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * (float)dot;
+    }
+};
+
+// ===============================================================================================================
+// Eight lanes per row ("row-group" mapping), for rows that start 8 bytes aligned and are a multiple of 8 bytes apart
+// (K a multiple of 1024 with packed rows): a warp pass covers ONE super-block of FOUR rows, lane = (row lane / 8,
+// sub-block s = lane % 8).  Blocks of IQ3_XXS are 98 bytes, so block b of a 4-block slice starts at 2b (mod 8) in
+// every row: the alignment of every field is a compile-time property of b and each field is fetched with the widest
+// aligned load (64-bit for the index bytes where they sit 8-byte aligned, one 32-bit load for the sign word where it
+// sits 4-byte aligned).  The activations of a sub-block are the same for the four rows of a pass and for every pass
+// of a tile, so they are kept in registers twice -- as they are and negated -- and the signs of the weights are
+// applied to THEM: one PRMT picks q or -q per byte with a selector taken from a 128-entry table (one 32-bit load
+// per 8 weights), one dp4a multiplies with the unsigned codebook word.  Row sums accumulate in a register over the
+// blocks of the slice and are reduced over the 8 lanes of the row at the end (3 shuffles).
+// ===============================================================================================================
+
+// PRMT selectors of sign code c: low half for weights 0..3, high half for weights 4..7 of the group of eight (weight 7
+// takes the parity bit): nibble i = i (keep byte i of q) or 4 + i (byte i of -q).
+Q38B_HD uint32_t ksign_selectors(uint32_t c) {
+    uint32_t sg = c, par = c;
+    par ^= par >> 4; par ^= par >> 2; par ^= par >> 1;
+    sg |= (par & 1u) << 7;
+    uint32_t r = 0x32103210u;
+    for (int j = 0; j < 8; j++)
+        if ((sg >> j) & 1u) r |= 4u << (4 * j);
+    return r;
+}
+
+// bytewise negation of four int8 values (none of them -128)
+Q38B_HD uint32_t neg_bytes4(uint32_t w) { return (0x80808080u - (w & 0x7F7F7F7Fu)) ^ (~w & 0x80808080u); }
+
+// Staged activations of the row-group mapping: 512 bytes per super-block, chunk k (0, 1: the 32 int8 values of a
+// sub-block in two halves; 2, 3: their negations) of sub-block s at k * 128 + s * 16, so that the eight sub-blocks'
+// k-th chunks are one conflict-free 128-byte line.  Position of activation j (0..255) of a block, negated or not:
+Q38B_HD int actr_pos(int j, int negated) { return (2 * negated + ((j >> 4) & 1)) * 128 + (j >> 5) * 16 + (j & 15); }
+constexpr int ACTR_BLOCK_BYTES = 512;
+
+// tables of the row-group decoders in shared memory: codebook entry e, replica l at cb + e * 128 + l * 4; sign
+// selectors of code c, replica l at sgn + c * 128 + l * 4
+struct TablesR { SP cb_lane; SP sgn_lane; };   // bases with 4 * lane already added
+
+struct ActsR { uint32_t q[8], nq[8]; float dx; };
+
+template <int FMT> struct GranR;
+
+template <> struct GranR<T_IQ3_XXS> {
+    static constexpr int BB = 98;
+    static Q38B_HD void load_acts(ActsR& a, SP act_block, SP actd_block, int s) {
+        uint32_t v[4];
+        sp_ld128(act_block, 16 * s, v);        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(act_block, 128 + 16 * s, v);  a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        sp_ld128(act_block, 256 + 16 * s, v);  a.nq[0] = v[0]; a.nq[1] = v[1]; a.nq[2] = v[2]; a.nq[3] = v[3];
+        sp_ld128(act_block, 384 + 16 * s, v);  a.nq[4] = v[0]; a.nq[5] = v[1]; a.nq[6] = v[2]; a.nq[7] = v[3];
+        a.dx = sp_ldf(actd_block, 0) * 0.25f;
+    }
+    // `row`: first byte of this lane's row in the slice (a multiple of 8); B: block of the slice, 0..3
+    template <int B>
+    static Q38B_HD float dot(SP row, int s, const ActsR& a, const TablesR& t) {
+        const SP r8 = row + 8 * s, r4 = row + 4 * s;
+        constexpr int P = BB * B;                    // block start; P % 8 == 2 * B
+        uint32_t i0, i1, aux;
+        if (B == 0) {                                // index bytes at P + 2 (mod 8 = 2), sign word at 2 (mod 4)
+            uint32_t x0, x1;
+            sp_ld64(r8, P, x0, x1);
+            const uint32_t h = sp_ld16(r8, P + 8);
+            i0 = funnel_r(x0, x1, 16);
+            i1 = prmt(x1, h, 0x5432u);
+            aux = prmt(sp_ld16(r4, P + 66), sp_ld16(r4, P + 68), 0x5410u);
+        } else if (B == 1) {                         // index bytes at 4 (mod 8), sign word at 0 (mod 4)
+            i0 = sp_ld32(r8, P + 2);
+            i1 = sp_ld32(r8, P + 6);
+            aux = sp_ld32(r4, P + 66);
+        } else if (B == 2) {                         // index bytes at 6 (mod 8), sign word at 2 (mod 4)
+            uint32_t x0, x1;
+            const uint32_t h = sp_ld16(r8, P + 2);
+            sp_ld64(r8, P + 4, x0, x1);
+            i0 = prmt(h, x0, 0x5410u);
+            i1 = funnel_r(x0, x1, 16);
+            aux = prmt(sp_ld16(r4, P + 66), sp_ld16(r4, P + 68), 0x5410u);
+        } else {                                     // index bytes at 0 (mod 8), sign word at 0 (mod 4)
+            sp_ld64(r8, P + 2, i0, i1);
+            aux = sp_ld32(r4, P + 66);
+        }
+        int sum = 0;
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t c128 = (l == 0 ? (aux << 7) : (aux >> (7 * l - 7))) & 0x3F80u;
+            const uint32_t sel = sp_ld32(t.sgn_lane + (int)c128);
+            const uint32_t w = l < 2 ? i0 : i1;
+            const uint32_t g0 = sp_ld32(t.cb_lane + (int)byte_x128(w, 2 * (l & 1)));
+            const uint32_t g1 = sp_ld32(t.cb_lane + (int)byte_x128(w, 2 * (l & 1) + 1));
+            sum = dp4a_us(g0, prmt(a.q[2 * l], a.nq[2 * l], sel), sum);
+            sum = dp4a_us(g1, prmt(a.q[2 * l + 1], a.nq[2 * l + 1], sel >> 16), sum);
+        }
+        const int sumi = (int)(2u * (aux >> 28) + 1u) * sum;
+        return fp16_bits_to_float(sp_ld16(row, P)) * a.dx * (float)sumi;
     }
 };
 

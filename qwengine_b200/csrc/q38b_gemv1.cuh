@@ -53,11 +53,30 @@ struct Gemv1Args {
     int off_actd, off_actq, off_cb, off_sgn, off_red, off_stage;   // off_sgn: IQ3_XXS sign-mask table (KSIGN_TABLE_BYTES)
 };
 
-// ROWS = rows per tile and stage (8 for the thin formats, 4 for the fat ones); two CTAs share an SM so that the
+// One block of the slice for every row pass of a row-group tile (B is a template argument: the alignment of the block's
+// fields follows from it).
+template <int FMT, int B, int NPASS>
+__device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int s, SP act_block, SP actd_block, const TablesR& tabs, float (&acc)[NPASS]) {
+    ActsR ar;
+    GranR<FMT>::load_acts(ar, act_block, actd_block, s);
+#pragma unroll
+    for (int ps = 0; ps < NPASS; ps++) acc[ps] += GranR<FMT>::template dot<B>(rowp[ps], s, ar, tabs);
+}
+
+// shared-memory tables of the row-group decoders (static, so that their addresses are immediates of the loads)
+constexpr int RG_CB_WORDS = 256 * 32, RG_SGN_WORDS = 128 * 32;
+constexpr int RG_STATIC_BYTES = 4 * (RG_CB_WORDS + RG_SGN_WORDS);
+
+// ROWS = rows per tile and stage (8 unless no 8-row plan fits shared memory); two CTAs share an SM so that the
 // prologue of one (or of the next kernel of the stream) overlaps the streaming of the other.
-template <int FMT, int NWARPS, int ROWS>
+// RG: the row-group mapping of q38b_decode1.cuh (IQ3_XXS, rows 8 bytes aligned): lane = (row of a group of four,
+// sub-block), tables in static shared memory, activations staged in the layout of actr_pos.
+template <int FMT, int NWARPS, int ROWS, bool RG>
 __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1Args a) {
     constexpr int G1_ROWS = ROWS;
+    static_assert(!RG || (FMT == T_IQ3_XXS && ROWS % 4 == 0), "row-group mapping: IQ3_XXS, tiles of 4 or 8 rows");
+    __shared__ __align__(128) uint32_t rg_cb[RG ? RG_CB_WORDS : 1];
+    __shared__ __align__(128) uint32_t rg_sgn[RG ? RG_SGN_WORDS : 1];
     extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
     uint8_t* smem = smem_raw;
     uint64_t* full = (uint64_t*)smem;                        // [G1_MAX_STAGES]
@@ -148,11 +167,25 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     uint8_t* actq = smem + a.off_actq;               // [n_slices * 1024] staged order
     uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
     constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
-    if (CBN > 0) {
+    if (RG) {
+        // thread e writes the 32 replicas of codebook entry e (and of sign code e): eight 16-byte stores each
+        for (int e = ctid; e < 256; e += NWARPS * 32) {
+            const uint32_t v = a.codebook[e];
+            uint4* dst = (uint4*)(rg_cb + 32 * e);
+#pragma unroll
+            for (int i = 0; i < 8; i++) dst[i] = make_uint4(v, v, v, v);
+        }
+        for (int c = ctid; c < 128; c += NWARPS * 32) {
+            const uint32_t v = ksign_selectors((uint32_t)c);
+            uint4* dst = (uint4*)(rg_sgn + 32 * c);
+#pragma unroll
+            for (int i = 0; i < 8; i++) dst[i] = make_uint4(v, v, v, v);
+        }
+    } else if (CBN > 0) {
         const int rep = 1 << a.cb_rep_log2;
         for (int i = ctid; i < CBN * rep; i += NWARPS * 32) cbw[i] = a.codebook[i >> a.cb_rep_log2];
     }
-    if (FMT == T_IQ3_XXS) {
+    if (FMT == T_IQ3_XXS && !RG) {
         uint32_t* sg = (uint32_t*)(smem + a.off_sgn);
         for (int i = ctid; i < 128 * 16; i += NWARPS * 32) {   // code i / 16, replica i % 16
             uint32_t lo, hi;
@@ -182,7 +215,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             }
             if (lane == 0) actd[sb * 8] = d;
             uint8_t* dst = actq + sb * 256;
-            if (FMT == T_IQ4_XS) {
+            if (RG) {
+                uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
+                *(uint2*)(blk + actr_pos(8 * lane, 0)) = make_uint2(w0, w1);
+                *(uint2*)(blk + actr_pos(8 * lane, 1)) = make_uint2(neg_bytes4(w0), neg_bytes4(w1));
+            } else if (FMT == T_IQ4_XS) {
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     const int k = 8 * lane + e;
@@ -199,7 +236,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         const int sb = i >> 6, wi = i & 63;
         const uint32_t v = sb < a.nsb ? *(const uint32_t*)(a.xq + (size_t)sb * Q8K_BYTES + 4 + 4 * wi) : 0u;
         uint8_t* dst = actq + sb * 256;
-        if (FMT == T_IQ4_XS) {
+        if (RG) {
+            uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
+            *(uint32_t*)(blk + actr_pos(4 * wi, 0)) = v;
+            *(uint32_t*)(blk + actr_pos(4 * wi, 1)) = neg_bytes4(v);
+        } else if (FMT == T_IQ4_XS) {
 #pragma unroll
             for (int b = 0; b < 4; b++) {
                 const int k = 4 * wi + b;
@@ -215,13 +256,14 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
     cb.lane_base = sp_from(cbw) + 4 * (lane & ((1 << cb1_rep_log2(FMT)) - 1));
     cb.sign_base = sp_from(smem + a.off_sgn) + 8 * (lane & 15);
+    const TablesR tabs{sp_from(rg_cb) + 4 * lane, sp_from(rg_sgn) + 4 * lane};
     const SP actq_sp = sp_from(actq), actd_sp = sp_from(actd);
     const SP stage0_sp = sp_from(smem + a.off_stage);
     float* red = (float*)(smem + a.off_red);         // [n_tilebuf][n_slices][8]
 
-    constexpr int LPR = Gran<FMT>::LANES_PER_ROW;    // 32, or 16 when two rows share a warp pass
-    constexpr int PASSES = G1_ROWS * LPR / 32;       // row passes per stage: 8 or 4
-    const int sub = LPR == 32 ? 0 : (lane >> 4);     // which of the two rows of a pass this lane works on
+    constexpr int LPR = RG ? 8 : Gran<FMT>::LANES_PER_ROW;   // 32, or 16 when two rows share a warp pass; 8: row groups
+    constexpr int PASSES = G1_ROWS * LPR / 32;       // row passes per stage
+    const int sub = LPR == 32 ? 0 : LPR == 16 ? (lane >> 4) : (lane >> 3);   // which of the rows of a pass this lane works on
 
     const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
     // The unit's (tile, slice, chunk) and the ring positions of its stage and tile buffer are stepped, never divided.
@@ -238,11 +280,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         const int item = ti * a.n_chunks + chunk;
         while (cur_item < item) { cur_item++; if (++stage == a.n_stages) { stage = 0; stage_par ^= 1u; } }
         while (cur_ti < ti) { cur_ti++; if (++tslot == a.n_tilebuf) { tslot = 0; tile_par ^= 1u; } }
-        typename Gran<FMT>::Acts acts;
-        Gran<FMT>::load_acts(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
-        // granules past the end of the row (K not a multiple of 1024) contribute nothing
-        const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
-        const bool live = gran_sb < a.nsb;
         // A warp reads only some of the stages, so it can reach stage fill `item` while the fill before it of the same
         // barrier is still in flight (bulk copies complete in any order); a parity wait alone would take that older
         // phase for this one.  The producer issues a fill only after the readers of the previous use of the barrier have
@@ -259,6 +296,42 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
         // low address bits of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
         const uint32_t src_lo = w_lo + (uint32_t)(tile * G1_ROWS) * rb32 + (a.contiguous ? 0u : (uint32_t)(chunk * a.chunk_slices * SLICE_BYTES));
+        float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
+        // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
+        const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
+        const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
+        if constexpr (RG) {
+            // row groups: pass ps = rows 4 ps .. 4 ps + 3 (lane / 8 picks the row), the four blocks of the slice in turn
+            const int s = lane & 7;
+            SP rowp[PASSES];
+            float acc[PASSES];
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ps++) {
+                const int r = 4 * ps + sub;
+                rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
+                acc[ps] = 0.0f;
+            }
+            const int sb0 = slice * 4;
+            if (sb0 + 0 < a.nsb) rowgroup_block<FMT, 0, PASSES>(rowp, s, actq_sp + (sb0 + 0) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 0) * 32, tabs, acc);
+            if (sb0 + 1 < a.nsb) rowgroup_block<FMT, 1, PASSES>(rowp, s, actq_sp + (sb0 + 1) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 1) * 32, tabs, acc);
+            if (sb0 + 2 < a.nsb) rowgroup_block<FMT, 2, PASSES>(rowp, s, actq_sp + (sb0 + 2) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 2) * 32, tabs, acc);
+            if (sb0 + 3 < a.nsb) rowgroup_block<FMT, 3, PASSES>(rowp, s, actq_sp + (sb0 + 3) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 3) * 32, tabs, acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ps++) {
+                float v = acc[ps];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (s == 0) rslot[4 * ps + sub] = v;
+            }
+        } else {
+        typename Gran<FMT>::Acts acts;
+        Gran<FMT>::load_acts(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
+        // granules past the end of the row (K not a multiple of 1024) contribute nothing
+        const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
+        const bool live = gran_sb < a.nsb;
         float acc[PASSES];
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
@@ -268,12 +341,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             acc[ps] = live ? v : 0.0f;
         }
         __syncwarp();
-        if (lane == 0) {
-            // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
-            const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
-            const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
-            mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
-        }
+        if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
 
         // sum over the lanes of each row: halving butterflies (each step halves the values a lane holds), then plain ones
         float rowsum;
@@ -305,10 +373,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             for (; bit > 0; bit >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, bit);
             if (LPR == 16) myrow = 2 * myrow + sub;
         }
-        float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
         // one lane per row writes: the lanes whose low bits (those folded by the plain butterflies) are zero
         constexpr int LOW_MASK = (LPR == 32 ? 32 : 16) / PASSES - 1;
         if ((lane & LOW_MASK) == 0) rslot[myrow] = rowsum;
+        }
         __syncwarp();
         const uint32_t tb = smem_u32(&tbar[tslot]);
         if (lane == 0) mbar_arrive(tb);

@@ -24,6 +24,8 @@ struct q38b_ctx {
     uint32_t* peer_flags[8] = {};     // arena bases of all ranks
     size_t arena_bytes = 0, arena_used = 0;
     int peers_connected = 0;
+    const void* configured[96] = {};  // kernels whose opt-in shared-memory size has been set on this context's device
+    int n_configured = 0;
     int pending_sync_seq = -1;        // >= 0: the next merged matvec or SwiGLU launch starts with cross-GPU barrier number seq of the run
 };
 

@@ -9,7 +9,8 @@
 #include <vector>
 
 #include "../../include/q38b200.h"
-#include "q38b_fused.cuh"
+#include "q38b_act.cuh"
+#include "q38b_pipe.cuh"
 #include "q38b_internal.h"
 
 using namespace q38b;
@@ -87,16 +88,17 @@ struct q38b_pass {
     float* pin_in = nullptr;
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
-    // single-column passes on one GPU run as one persistent kernel when the ops allow it
-    int merge_steps = 1;         // single-column replays: one launch for matvecs that share a column, quantize steps folded into them
-    int fused_mode = 0;          // 1: single-column runs use the persistent kernel (opt-in: not faster than the replay yet)
-    int fused_state = 0;         // 0: not planned yet, 1: ready, -1: this pass cannot run fused
-    size_t fused_n_ops = 0;      // ops recorded when the fused plan was made
-    FusedOp* d_fops = nullptr;
-    unsigned* d_done = nullptr;
-    unsigned long long* d_prof = nullptr;   // tracing counters of the persistent kernel (q38b_pass_fused_trace)
-    int fused_groups = 0, fused_smem = 0, fused_grid = 0;
-    FusedArgs fargs = {};
+    int merge_steps = 1;         // replays: one launch for matvecs that share a column, quantize steps folded into single-column launches
+    // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
+    // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
+    struct Captured {
+        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected;
+        bool operator==(const Captured& o) const {
+            return n_ops == o.n_ops && peer_store == o.peer_store && merge_steps == o.merge_steps && uniform_columns == o.uniform_columns &&
+                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected;
+        }
+    };
+    Captured captured[9] = {};
 };
 
 #define PASS_CUDA(p, call)                                \
@@ -155,8 +157,25 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
     const size_t n = ops.size();
     out.clear();
     skip.assign(n, 0);
+    const bool ranks = ctx->n_ranks > 1;
     auto next_real = [&](size_t i) { while (i < n && (ops[i].kind == OP_GATHER || ops[i].kind == OP_BARRIER)) i++; return i; };
     auto on_column = [&](size_t k, int col) { return k < n && ops[k].kind == OP_GEMV && ops[k].b == col; };
+    // The step after matvec k that may still join k's launch, which is emitted at the position of the run's first matvec:
+    // on several ranks a cross-GPU barrier is a hard cut, and an all-gather may only be stepped over by a matvec whose
+    // output does not lie in the gathered range (the recorded order of those two must be kept).  n when there is none.
+    auto next_in_run = [&](size_t k) {
+        size_t j = k + 1;
+        if (!ranks) return next_real(j);
+        const size_t first_skipped = j;
+        while (j < n && ops[j].kind == OP_GATHER) j++;
+        if (j >= n || ops[j].kind != OP_GEMV) return j < n && ops[j].kind == OP_BARRIER ? n : j;
+        const long long lo = ops[j].off, hi = lo + p->mats[ops[j].a].M;
+        for (size_t g = first_skipped; g < j; g++) {
+            const long long glo = ops[g].off, ghi = glo + (long long)ops[g].n * ctx->n_ranks;
+            if (ops[g].a == ops[j].c && lo < ghi && glo < hi) return n;
+        }
+        return j;
+    };
     size_t i = next_real(0);
     while (i < n) {
         int quant = -1;
@@ -167,16 +186,18 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
         }
         if (ops[i].kind == OP_QUANT) {
             const int col = ops[i].b;
-            const size_t j = next_real(i + 1);
-            size_t run_end = j;
-            while (on_column(run_end, col)) run_end = next_real(run_end + 1);
-            bool ok = run_end > j && ops[i].off % 4 == 0;
+            const size_t j = ranks ? i + 1 : next_real(i + 1);   // several ranks: only a matvec right after the quantize step
+            std::vector<size_t> run;                              // the matvecs the quantize step would be folded into
+            for (size_t k = j; on_column(k, col); k = next_in_run(k)) run.push_back(k);
+            const size_t run_end = run.empty() ? j : next_real(run.back() + 1);
+            bool ok = !run.empty() && ops[i].off % 4 == 0;
             for (size_t k = run_end; ok && k < n; k++) {   // nobody else reads the Q8_K buffer before it is written again
                 const Op& o = ops[k];
                 if ((o.kind == OP_QUANT && o.b == col) || (o.kind == OP_SWIGLU && o.c == col)) break;
                 if (o.kind == OP_GEMV && o.b == col) ok = false;
             }
-            for (size_t k = j; ok && k < run_end; k = next_real(k + 1)) {
+            for (size_t k : run) {
+                if (!ok) break;
                 const Mat& m = p->mats[ops[k].a];
                 if (m.K != ops[i].n || !q38b_gemv_group_plannable(ctx, m.type, 1, m.row_bytes, m.K, &m.M)) ok = false;
             }
@@ -190,7 +211,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
         }
         // cut the run of matvecs on this column into launches of up to three
         const int col = ops[g0].b;
-        size_t k = g0;
+        size_t k = g0, resume = g0 + 1;   // resume: the step after the last matvec this run has taken
         while (on_column(k, col)) {
             Merged mg = {(int)k, 0, {0, 0, 0}, quant};
             const Mat& m0 = p->mats[ops[k].a];
@@ -204,10 +225,12 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)
                             : !q38b_gemvn_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms, nb)) break;
                 mg.ops[mg.n++] = (int)k;
-                k = next_real(k + 1);
+                resume = k + 1;
+                k = next_in_run(k);
             }
             if (mg.n == 0) {   // runs on the multi-column kernel only (never after a folded quantize): left alone
-                k = next_real(k + 1);
+                resume = k + 1;
+                k = next_in_run(k);
                 continue;
             }
             if (mg.n > 1 || quant >= 0) {
@@ -215,7 +238,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 out.push_back(mg);
             }
         }
-        i = k;
+        i = next_real(resume);
     }
 }
 
@@ -347,231 +370,6 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
 }
 }  // namespace
 
-namespace {
-
-struct Access { int buf; long long lo, hi; bool write; };
-
-void op_accesses(const q38b_pass* p, const Op& o, std::vector<Access>& acc) {
-    acc.clear();
-    const long long ALL = 1LL << 40;
-    switch (o.kind) {
-        case OP_QUANT:
-            acc.push_back({o.a, o.off, (long long)o.off + o.n, false});
-            acc.push_back({o.b, 0, ALL, true});
-            break;
-        case OP_GEMV:
-            acc.push_back({o.b, 0, ALL, false});
-            acc.push_back({o.c, o.off, (long long)o.off + p->mats[o.a].M, true});
-            break;
-        case OP_SWIGLU:
-            acc.push_back({o.a, o.off, (long long)o.off + o.n, false});
-            acc.push_back({o.b, o.d, (long long)o.d + o.n, false});
-            acc.push_back({o.c, 0, ALL, true});
-            break;
-        default: break;
-    }
-}
-
-bool conflicts(const std::vector<Access>& x, const std::vector<Access>& y) {
-    for (const Access& a : x)
-        for (const Access& b : y)
-            if (a.buf == b.buf && (a.write || b.write) && a.lo < b.hi && b.lo < a.hi) return true;
-    return false;
-}
-
-// Plans the pass as one persistent kernel: shared-memory carve-up, rows per tile of every matvec, groups and the group
-// each one waits for.  Returns false when the pass has to be replayed kernel by kernel.
-bool plan_fused(q38b_pass* p) {
-    q38b_ctx* ctx = p->ctx;
-    if (ctx->n_ranks > 1 || p->ops.empty()) return false;
-    const int G = ctx->sm_count * FU_CTAS_PER_SM;
-    const int smem_budget = FU_CTAS_PER_SM == 1 ? ctx->smem_optin : std::min(ctx->smem_optin, (228 * 1024) / FU_CTAS_PER_SM - 1024);
-    bool use_xxs = false, use_s = false;
-    int max_slices = 1;
-    for (const Op& o : p->ops) {
-        if (o.kind != OP_GEMV) continue;
-        const Mat& m = p->mats[o.a];
-        if (m.row_bytes != q38b_row_bytes(m.type, m.K) || m.row_bytes > 0xFFFFFFFFull) return false;   // rows must be packed
-        const int n_slices = (m.K / 256 + 3) / 4;
-        if (n_slices > FU_BAR_COUNT || m.K / 256 > 255) return false;
-        max_slices = std::max(max_slices, n_slices);
-        use_xxs |= m.type == T_IQ3_XXS;
-        use_s |= m.type == T_IQ3_S;
-    }
-    FusedArgs& a = p->fargs;
-    a = FusedArgs{};
-    auto up = [](int v) { return (v + 127) & ~127; };
-    a.max_slices = max_slices;
-    a.off_actd = FU_HEADER_BYTES;
-    a.off_actq = a.off_actd + max_slices * 128;
-    int off = a.off_actq + max_slices * 1024;
-    a.off_cb_xxs = a.off_sgn = a.off_cb_s = 0;
-    if (use_xxs) { a.off_cb_xxs = off; off += 256 * 128; a.off_sgn = off; off += KSIGN_TABLE_BYTES; }
-    if (use_s) { a.off_cb_s = off; off += 512 * 64; }
-    int n_fops = 0, n_gemv = 0;
-    for (const Op& o : p->ops) {
-        if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;
-        n_fops++;
-        n_gemv += o.kind == OP_GEMV;
-    }
-    if (n_gemv > 32000 || (long long)n_fops * 8 + (long long)n_gemv * 48 > 48 * 1024) return false;
-    a.n_gemv = n_gemv;
-    a.off_optab = up(off);
-    a.off_gemvtab = up(a.off_optab + n_fops * 8);
-    a.off_filltab = a.off_gemvtab + n_gemv * 32;
-    off = a.off_filltab + n_gemv * 16;
-    // rows per tile of every matvec (largest of 8, 4, 2 whose tile stays under 24 KB), then equal ring slots that hold
-    // the largest tile
-    const size_t tile_cap = 24 * 1024;
-    size_t max_tile = 0;
-    for (const Op& o : p->ops) {
-        if (o.kind != OP_GEMV) continue;
-        const Mat& m = p->mats[o.a];
-        size_t tile = 0;
-        for (int rl = 3; rl >= 1 && !tile; rl--)
-            if (((size_t)m.row_bytes << rl) + 160 <= tile_cap) tile = ((size_t)m.row_bytes << rl) + 160;
-        if (!tile) return false;
-        max_tile = std::max(max_tile, tile);
-    }
-    if (!max_tile) return false;
-    a.slot_bytes = up((int)max_tile);
-    a.off_red = up(off);
-    for (a.n_slots = FU_MAX_SLOTS; a.n_slots >= 3; a.n_slots--) {
-        a.off_stage = up(a.off_red + a.n_slots * max_slices * 8 * 4);
-        if (a.off_stage + a.n_slots * a.slot_bytes + FU_RING_SLACK <= smem_budget) break;
-    }
-    if (a.n_slots < 3) return false;
-    p->fused_smem = a.off_stage + a.n_slots * a.slot_bytes + FU_RING_SLACK;
-
-    std::vector<FusedOp> fops;
-    std::vector<std::vector<Access>> accs;     // per fused op
-    std::vector<int> group_first;              // index of the first op of each group
-    std::vector<Access> acc;
-    long long tiles_so_far = 0;
-    int gemv_seen = 0;
-    int cur_src = -1, cur_permute = -1;        // input of the current matvec group, -1: the current group is not one
-    for (const Op& o : p->ops) {
-        if (o.kind == OP_GATHER || o.kind == OP_BARRIER) continue;   // single GPU: nothing to exchange
-        FusedOp f = {};
-        op_accesses(p, o, acc);
-        bool new_group = true;
-        if (o.kind == OP_GEMV) {
-            const Mat& m = p->mats[o.a];
-            int rl = -1;
-            for (int r = 3; r >= 1 && rl < 0; r--)
-                if (((size_t)m.row_bytes << r) + 160 <= (size_t)a.slot_bytes) rl = r;
-            if (rl < 0) return false;
-            f.kind = FOP_GEMV;
-            f.gemv_index = gemv_seen++;
-            f.fmt = (int)m.type;
-            f.rows_log2 = rl;
-            // units of (slice, 4 rows) when that gives ten or more per tile -- then the 16 warps work on one or two tiles
-            // and the other slots hold copies in flight -- else units of (slice, 2 rows)
-            const int n_sl = (m.K / 256 + 3) / 4;
-            f.unit_rows = (rl >= 2 && n_sl * ((1 << rl) / 4) >= 10) ? 4 : 2;
-            if (n_sl * ((1 << rl) / f.unit_rows) > FU_BAR_COUNT) return false;
-            f.M = m.M;
-            f.nsb = m.K / 256;
-            f.n_tiles = (m.M + (1 << rl) - 1) >> rl;
-            f.tile_rot = (int)(tiles_so_far % G);
-            tiles_so_far += f.n_tiles;
-            f.row_bytes = (unsigned)m.row_bytes;
-            f.a = m.W;
-            f.b = p->bufs[o.b].ptr;
-            f.out = (float*)p->bufs[o.c].ptr + o.off;
-            const int permute = m.type == T_IQ4_XS;
-            if (cur_src == o.b && cur_permute == permute) {
-                new_group = false;
-                for (size_t k = group_first.back(); k < fops.size(); k++)
-                    if (conflicts(acc, accs[k])) new_group = true;
-            }
-            cur_src = o.b;
-            cur_permute = permute;
-        } else if (o.kind == OP_QUANT) {
-            f.kind = FOP_QUANT;
-            f.gemv_index = -1;
-            f.nsb = o.n / 256;
-            f.a = (const float*)p->bufs[o.a].ptr + o.off;
-            f.out = p->bufs[o.b].ptr;
-            cur_src = -1;
-        } else {
-            f.kind = FOP_SWIGLU;
-            f.gemv_index = -1;
-            f.nsb = o.n / 256;
-            f.a = (const float*)p->bufs[o.a].ptr + o.off;
-            f.b = (const float*)p->bufs[o.b].ptr + o.d;
-            f.out = p->bufs[o.c].ptr;
-            cur_src = -1;
-        }
-        if (new_group) group_first.push_back((int)fops.size());
-        f.group = (int)group_first.size() - 1;
-        f.wait_group = -1;
-        fops.push_back(f);
-        accs.push_back(acc);
-    }
-    if (fops.empty()) return false;
-    // a group waits for the latest earlier group any of its ops conflicts with (groups complete in order on every CTA)
-    for (size_t j = 0; j < fops.size(); j++) {
-        int wait = -1;
-        for (size_t k = 0; k < (size_t)group_first[fops[j].group]; k++)
-            if (fops[k].group > wait && conflicts(accs[j], accs[k])) wait = fops[k].group;
-        FusedOp& head = fops[group_first[fops[j].group]];
-        head.wait_group = std::max(head.wait_group, wait);
-    }
-    p->fused_groups = (int)group_first.size();
-
-    auto kern = fused_pass_kernel;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->fused_smem) != cudaSuccess) { cudaGetLastError(); return false; }
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FU_THREADS, p->fused_smem) != cudaSuccess || per_sm < FU_CTAS_PER_SM) { cudaGetLastError(); return false; }
-    int coop = 0;
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device);
-    if (!coop) return false;
-    p->fused_grid = G;
-    if (p->d_fops) cudaFree(p->d_fops);
-    if (p->d_done) cudaFree(p->d_done);
-    p->d_fops = nullptr;
-    p->d_done = nullptr;
-    if (cudaMalloc(&p->d_fops, fops.size() * sizeof(FusedOp)) != cudaSuccess) { cudaGetLastError(); return false; }
-    if (cudaMalloc(&p->d_done, (size_t)p->fused_groups * sizeof(unsigned)) != cudaSuccess) { cudaGetLastError(); return false; }
-    if (cudaMemcpy(p->d_fops, fops.data(), fops.size() * sizeof(FusedOp), cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); return false; }
-    a.ops = p->d_fops;
-    a.n_ops = (int)fops.size();
-    a.done = p->d_done;
-    a.status = ctx->d_status;
-    a.cb_xxs = use_xxs ? ctx->d_cb_iq3xxs : nullptr;
-    a.cb_s = use_s ? ctx->d_cb_iq3s : nullptr;
-    a.prof = p->d_prof;
-    return true;
-}
-
-bool fused_ready(q38b_pass* p) {
-    if (!p->fused_mode) return false;
-    if (p->fused_state == 0 || p->fused_n_ops != p->ops.size()) {
-        p->fused_state = plan_fused(p) ? 1 : -1;
-        p->fused_n_ops = p->ops.size();
-    }
-    return p->fused_state == 1;
-}
-
-int launch_fused(q38b_pass* p, cudaStream_t st) {
-    PASS_CUDA(p, cudaMemsetAsync(p->d_done, 0, (size_t)p->fused_groups * sizeof(unsigned), st));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)p->fused_grid);
-    cfg.blockDim = dim3(FU_THREADS);
-    cfg.dynamicSmemBytes = (size_t)p->fused_smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs resident: the group waits cannot starve
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    PASS_CUDA(p, cudaLaunchKernelEx(&cfg, fused_pass_kernel, p->fargs));
-    return Q38B_OK;
-}
-
-}  // namespace
-
 extern "C" {
 
 int q38b_comm_unique_id(void* id128) {
@@ -685,9 +483,6 @@ void q38b_pass_destroy(q38b_pass* p) {
     if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
     if (p->pin_in) cudaFreeHost(p->pin_in);
     if (p->pin_out) cudaFreeHost(p->pin_out);
-    if (p->d_fops) cudaFree(p->d_fops);
-    if (p->d_done) cudaFree(p->d_done);
-    if (p->d_prof) cudaFree(p->d_prof);
     delete p;
 }
 
@@ -781,7 +576,12 @@ int q38b_pass_op_allgather(q38b_pass* p, int buf, int off, int count) {
 int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    if (nb == 1 && fused_ready(p)) return launch_fused(p, st);
+    const q38b_pass::Captured now = {p->ops.size(), p->peer_store, p->merge_steps, p->ctx->uniform_columns, p->ctx->pass_pdl,
+                                     p->ctx->n_ranks, p->ctx->peers_connected};
+    if (p->graphs[nb] && !(now == p->captured[nb])) {
+        cudaGraphExecDestroy(p->graphs[nb]);
+        p->graphs[nb] = nullptr;
+    }
     if (!p->graphs[nb]) {
         cudaGraph_t g = nullptr;
         if (!p->cap_stream) PASS_CUDA(p, cudaStreamCreateWithFlags(&p->cap_stream, cudaStreamNonBlocking));
@@ -793,6 +593,7 @@ int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
         const cudaError_t ei = cudaGraphInstantiate(&p->graphs[nb], g, 0);
         cudaGraphDestroy(g);
         if (ei != cudaSuccess) { p->ctx->last_cuda = (int)ei; p->graphs[nb] = nullptr; return Q38B_ERR_CUDA; }
+        p->captured[nb] = now;
     }
     PASS_CUDA(p, cudaGraphLaunch(p->graphs[nb], st));
     return Q38B_OK;
@@ -837,33 +638,44 @@ long long q38b_pass_weight_bytes(const q38b_pass* p) {
 
 int q38b_pass_set_merge(q38b_pass* p, int enabled) {
     if (!p) return Q38B_ERR_ARG;
-    p->merge_steps = enabled ? 1 : 0;
-    for (auto& g : p->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }   // recorded again at the next run
+    p->merge_steps = enabled ? 1 : 0;   // graphs captured with the other setting are recorded again at their next run
     return Q38B_OK;
 }
 
-int q38b_pass_set_fused(q38b_pass* p, int enabled) {
-    if (!p) return Q38B_ERR_ARG;
-    p->fused_mode = enabled ? 1 : 0;
-    return Q38B_OK;
-}
-
-int q38b_pass_fused_active(q38b_pass* p) { return p && fused_ready(p) ? 1 : 0; }
-
-int q38b_pass_fused_trace(q38b_pass* p, int enable, unsigned long long* counters8) {   // FU_PROF_N counters
-    if (!p) return Q38B_ERR_ARG;
-    if (enable && !p->d_prof) {
-        PASS_CUDA(p, cudaMalloc(&p->d_prof, FU_PROF_N * sizeof(unsigned long long)));
-        PASS_CUDA(p, cudaMemset(p->d_prof, 0, FU_PROF_N * sizeof(unsigned long long)));
+// Test hook (not in the public header): runs the launch planner on a list of steps without touching a device.
+// steps[3 i ..] = {kind (0 quantize, 1 matvec, 2 SwiGLU, 3 all-gather, 4 barrier), column buffer, output offset}; every
+// matvec is a 512 x 1024 Q4_K matrix writing 512 floats at its offset.  launch_of[i] receives the position in the step
+// list at which step i is launched (its own index unless it joined an earlier launch), -1 for folded quantize steps.
+int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, int* launch_of) {
+    if (n_ranks < 1 || nb < 1 || n_steps < 0 || !steps || !launch_of) return Q38B_ERR_ARG;
+    q38b_ctx ctx;
+    ctx.sm_count = 148;
+    ctx.smem_optin = 232448;
+    ctx.n_ranks = n_ranks;
+    q38b_pass p;
+    p.ctx = &ctx;
+    p.mats.push_back({(uint32_t)T_Q4_K, nullptr, 576, 1024, 512, false});
+    for (int b = 0; b < 8; b++) p.bufs.push_back({nullptr, 1 << 20, b >= 4, {}, 0, false});   // 0..3 fp32, 4..7 Q8_K columns
+    for (int i = 0; i < n_steps; i++) {
+        const int kind = steps[3 * i], col = steps[3 * i + 1], off = steps[3 * i + 2];
+        switch (kind) {
+            case 0: p.ops.push_back({OP_QUANT, 0, col, 0, 0, 1024, off}); break;
+            case 1: p.ops.push_back({OP_GEMV, 0, col, 1, 0, 0, off}); break;
+            case 2: p.ops.push_back({OP_SWIGLU, 1, 1, col, 0, 1024, off}); break;
+            case 3: p.ops.push_back({OP_GATHER, 1, 0, 0, 0, 512, off}); break;
+            case 4: p.ops.push_back({OP_BARRIER, 0, 0, 0, 0, 0, 0}); break;
+            default: return Q38B_ERR_ARG;
+        }
     }
-    if (counters8) {
-        if (!p->d_prof) return Q38B_ERR_ARG;
-        PASS_CUDA(p, cudaMemcpy(counters8, p->d_prof, FU_PROF_N * sizeof(unsigned long long), cudaMemcpyDeviceToHost));   // synchronises
-        PASS_CUDA(p, cudaMemset(p->d_prof, 0, FU_PROF_N * sizeof(unsigned long long)));
+    std::vector<Merged> merged;
+    std::vector<char> skip;
+    merge_plan(&p, nb, merged, skip);
+    for (int i = 0; i < n_steps; i++) launch_of[i] = i;
+    for (const Merged& mg : merged) {
+        if (mg.quant >= 0) launch_of[mg.quant] = -1;
+        for (int t = 0; t < mg.n; t++) launch_of[mg.ops[t]] = mg.first_op;
     }
-    if (!enable && p->d_prof) { cudaFree(p->d_prof); p->d_prof = nullptr; }
-    p->fargs.prof = p->d_prof;
-    return Q38B_OK;
+    return (int)merged.size();
 }
 
 int q38b_pass_kernel_count(const q38b_pass* p) {

@@ -1,6 +1,6 @@
 """Times one matvec (or prefill GEMM) shape on cuda:0 and prints one JSON line; also the command ncu profiles.
 
-    python -m qwengine_b200.single --fmt IQ3_XXS --M 17408 --K 5120 --nb 1 [--copies 8] [--reps 5] [--no-pdl] [--fused]
+    python -m qwengine_b200.single --fmt IQ3_XXS --M 17408 --K 5120 --nb 1 [--copies 8] [--reps 5] [--no-pdl]
     python -m qwengine_b200.single --op prefill --fmt Q4_K --M 17408 --K 5120 --tokens 1024
 
 Matvec: `copies` distinct resident matrices (random valid blocks; by default enough to exceed 1.5 GB, far beyond L2)
@@ -25,9 +25,6 @@ def main():
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--distinct-outputs", action="store_true", help="every matvec writes its own buffer: one group, no synchronisation between matvecs")
-    ap.add_argument("--trace", action="store_true", help="print the persistent kernel's wait counters")
-    ap.add_argument("--fused", action="store_true", help="run the matvecs as one persistent kernel instead of replaying them kernel by kernel")
     a = ap.parse_args()
     ctx = Context(0)
     ctx.set_pdl(not a.no_pdl)
@@ -37,13 +34,10 @@ def main():
     if a.op == "gemv":
         copies = a.copies or max(4, int(1.5e9 // (a.M * rb)) + 1)
         ps = Pass(ctx, max_nb=a.nb)
-        ps.set_fused(a.fused)
         xin, xq, yb = ps.buffer_f32(a.K), ps.buffer_q8k(a.K), ps.buffer_f32(a.M)
         ps.quantize(xin, 0, a.K, xq)
         for _ in range(copies):
             w = torch.randint(0, 256, (a.M, rb), dtype=torch.uint8, device="cuda")
-            if a.distinct_outputs:
-                yb = ps.buffer_f32(a.M)
             ps.gemv(ps.matrix_device(f, w, a.K), xq, yb, 0)
         ps.buffer_tensor(xin).normal_()
         for _ in range(2):
@@ -55,14 +49,6 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         ctx.check()
-        if a.trace and ps.fused_active:
-            ps.fused_trace(True)
-            ps.run(a.nb)
-            t = ps.fused_trace(True, read=True)
-            tot = max(1, t["warp_cycles"])
-            print(json.dumps({"trace": t, "frac": {k: round(t[k] / tot, 3) for k in t if k.endswith("_cycles") and k != "warp_cycles"},
-                              "waited_copy_latency_cycles": round(t["waited_copy_latency_cycles_sum"] / max(1, t["waited_copies"]))}))
-            ps.fused_trace(False)
         us = e0.elapsed_time(e1) * 1e3 / (a.reps * copies)
         print(json.dumps({"op": "gemv", "fmt": f.name, "M": a.M, "K": a.K, "nb": a.nb, "copies": copies, "us_per_launch": round(us, 2),
                           "weight_GBps": round(a.M * rb / us / 1e3, 1)}))

@@ -215,3 +215,84 @@ extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const ui
     }
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Row-group mapping of the single-column path (GranR): rows 8 bytes aligned, a pass = one super-block of four rows.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+template <int FMT, int B>
+float block_r(const uint8_t* row, int s, const ActsR& a, const TablesR& t) { return GranR<FMT>::template dot<B>(sp_from(row), s, a, t); }
+
+template <int FMT>
+void run_rowgroup(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* act, const float* actd, const uint32_t* cb, const uint32_t* sgn, float* y) {
+    const int nsb = K / 256, n_slices = (nsb + 3) / 4;
+    for (int r = 0; r < n_rows; r++) {
+        float lane_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int sl = 0; sl < n_slices; sl++)
+            for (int b = 0; b < 4; b++) {
+                const int sb = sl * 4 + b;
+                if (sb >= nsb) continue;
+                for (int s = 0; s < 8; s++) {
+                    const int lane = 8 * (r & 3) + s;
+                    tl_lane = lane;
+                    ActsR a;
+                    GranR<FMT>::load_acts(a, sp_from(act + (size_t)sb * ACTR_BLOCK_BYTES), sp_from(actd + sb * 8), s);
+                    const TablesR t{sp_from(cb) + 4 * lane, sp_from(sgn) + 4 * lane};
+                    const uint8_t* row = rowp[r] + (size_t)sl * 4 * GranR<FMT>::BB;
+                    float v = 0;
+                    switch (b) {
+                        case 0: v = block_r<FMT, 0>(row, s, a, t); break;
+                        case 1: v = block_r<FMT, 1>(row, s, a, t); break;
+                        case 2: v = block_r<FMT, 2>(row, s, a, t); break;
+                        default: v = block_r<FMT, 3>(row, s, a, t); break;
+                    }
+                    lane_acc[s] += v;
+                }
+            }
+        // the butterfly over the row's eight lanes: xor 1, 2, 4
+        for (int bit = 1; bit < 8; bit <<= 1) {
+            float nxt[8];
+            for (int s = 0; s < 8; s++) nxt[s] = lane_acc[s] + lane_acc[s ^ bit];
+            for (int s = 0; s < 8; s++) lane_acc[s] = nxt[s];
+        }
+        y[r] = lane_acc[0];
+    }
+}
+}  // namespace
+
+// W: n_rows rows `row_bytes` apart (a multiple of 8); xq: Q8_K blocks of one column; addr_lo: 0 or 8, the pretended low
+// address bits of row 0; y[n_rows].
+extern "C" int emul_gemv1_rowgroup(int fmt, int K, const uint8_t* W, int row_bytes, int n_rows, const uint8_t* xq, int addr_lo, float* y) {
+    const int bb = block_bytes(fmt), nsb = K / 256, n_slices = (nsb + 3) / 4;
+    if (fmt != T_IQ3_XXS || row_bytes % 8 || (addr_lo & 7) || row_bytes < nsb * bb) return -1;
+    const int slot = (row_bytes + 4 * bb + 15) / 16 * 16 + 16;
+    std::vector<uint8_t> stage((size_t)n_rows * slot + 64, 0x5A);
+    uint8_t* st = (uint8_t*)(((uintptr_t)stage.data() + 15) & ~(uintptr_t)15);
+    std::vector<const uint8_t*> rowp(n_rows);
+    for (int r = 0; r < n_rows; r++) {
+        uint8_t* p = st + (size_t)r * slot + ((addr_lo + r * row_bytes) & 15);
+        memcpy(p, W + (size_t)r * row_bytes, nsb * bb);
+        rowp[r] = p;
+    }
+    std::vector<uint8_t> actbuf((size_t)n_slices * 4 * ACTR_BLOCK_BYTES + 64, 0);
+    uint8_t* act = (uint8_t*)(((uintptr_t)actbuf.data() + 15) & ~(uintptr_t)15);
+    std::vector<float> actd((size_t)n_slices * 32, 0.f);
+    for (int sb = 0; sb < nsb; sb++) {
+        const uint8_t* blk = xq + (size_t)sb * 292;
+        memcpy(&actd[sb * 8], blk, 4);
+        for (int w = 0; w < 64; w++) {
+            uint32_t v;
+            memcpy(&v, blk + 4 + 4 * w, 4);
+            const uint32_t n = neg_bytes4(v);
+            memcpy(act + (size_t)sb * ACTR_BLOCK_BYTES + actr_pos(4 * w, 0), &v, 4);
+            memcpy(act + (size_t)sb * ACTR_BLOCK_BYTES + actr_pos(4 * w, 1), &n, 4);
+        }
+    }
+    std::vector<uint32_t> cb(256 * 32 + 4), sgn(128 * 32 + 4);
+    uint32_t* cba = (uint32_t*)(((uintptr_t)cb.data() + 15) & ~(uintptr_t)15);
+    uint32_t* sga = (uint32_t*)(((uintptr_t)sgn.data() + 15) & ~(uintptr_t)15);
+    for (int i = 0; i < 256 * 32; i++) cba[i] = q38b_iq3xxs_grid[i >> 5];
+    for (int i = 0; i < 128 * 32; i++) sga[i] = ksign_selectors((uint32_t)i >> 5);
+    run_rowgroup<T_IQ3_XXS>(K, rowp.data(), n_rows, act, actd.data(), cba, sga, y);
+    return 0;
+}

@@ -61,3 +61,24 @@ def test_single_column_granules_match_oracle(emul, name, K, addr_lo, rep_log2):
     assert emul.emul_gemv1(f.type_id, K, w.reshape(-1), M, xq.reshape(-1), addr_lo, rep_log2, y) == 0
     ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[0], K)
     assert np.max(np.abs(y - ref) / mag) < 1e-6
+
+
+@pytest.mark.parametrize("K,row_pad,addr_lo", [(1024, 0, 0), (5120, 0, 8), (1280, 6, 0), (2304, 6, 8)])
+def test_row_group_decoder_matches_oracle(emul, K, row_pad, addr_lo):
+    """The eight-lanes-per-row IQ3_XXS decoder (GranR) with every field fetched by its widest aligned load: the host
+    loaders abort on a misaligned access, so this also proves the alignment rules for 8-byte aligned rows."""
+    f = F.get("IQ3_XXS")
+    u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+    emul.emul_gemv1_rowgroup.argtypes = [C.c_int, C.c_int, u8p, C.c_int, C.c_int, u8p, C.c_int, f32p]
+    M = 9
+    w = synth.make_weights(f, M, K, seed=23, scale=2e-4)
+    rb = f.row_bytes(K) + row_pad
+    assert rb % 8 == 0
+    wpad = np.zeros((M, rb), np.uint8)
+    wpad[:, :f.row_bytes(K)] = w
+    xq = oracle.port.quantize_q8k(synth.make_activations(1, K, seed=24))
+    y = np.zeros(M, np.float32)
+    assert emul.emul_gemv1_rowgroup(f.type_id, K, wpad.reshape(-1), rb, M, xq.reshape(-1), addr_lo, y) == 0
+    ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[0], K)
+    assert np.max(np.abs(y - ref) / mag) < 1e-6
