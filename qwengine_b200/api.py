@@ -87,6 +87,7 @@ def load_library():
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
+    lib.q38b_debug_set_rowgroup.argtypes = [vp, i32]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     _LIB = lib
     return lib
@@ -149,6 +150,10 @@ class Context:
 
     def set_uniform_columns(self, enabled):
         self._rc(self.lib.q38b_ctx_set_uniform_columns(self.h, int(bool(enabled))), "q38b_ctx_set_uniform_columns")
+
+    def debug_set_rowgroup(self, enabled):
+        """Test hook: enabled=False keeps the one-column kernel on its lane-per-granule mapping for every format."""
+        self._rc(self.lib.q38b_debug_set_rowgroup(self.h, int(bool(enabled))), "q38b_debug_set_rowgroup")
 
     def set_pdl(self, enabled):
         self._rc(self.lib.q38b_ctx_set_pdl(self.h, int(bool(enabled))), "q38b_ctx_set_pdl")

@@ -156,7 +156,7 @@ bool rowgroup_eligible(uint32_t type, size_t row_bytes, int rows) { return type 
 int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, Plan1* p) {
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
-    const int rg = rowgroup_eligible(type, row_bytes, G1_ROWS) ? 1 : 0;
+    const int rg = ctx->rowgroup && rowgroup_eligible(type, row_bytes, G1_ROWS) ? 1 : 0;
     const int cb_entries = rg ? 0 : type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;   // row groups keep their tables in static shared memory
     const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128 - (rg ? RG_STATIC_BYTES : 0);
     Gemv1Args& a = p->a;
@@ -343,6 +343,14 @@ int q38b_ctx_set_static_weights(q38b_ctx* ctx, int enabled) {
 int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->uniform_columns = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+
+// Test hook (not in the public header): 0 keeps the one-column kernel on its lane-per-granule mapping for every format,
+// so that tests and timings can compare the two mappings on the same inputs.
+int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->rowgroup = enabled ? 1 : 0;
     return Q38B_OK;
 }
 

@@ -11,6 +11,7 @@ struct q38b_ctx {
     int pdl = 0;               // programmatic dependent launch for direct calls (passes use pass_pdl)
     int pass_pdl = 1;          // programmatic dependent launch between the kernels of a recorded pass
     int static_weights = 0;    // 1: matvec producers start streaming W before the previous kernel of the stream has finished
+    int rowgroup = 1;          // 0: the row-group mapping of the one-column kernel is not used (test hook q38b_debug_set_rowgroup)
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     int* d_status = nullptr;
     uint32_t* d_cb_iq3xxs = nullptr;

@@ -106,6 +106,55 @@ def test_gemv_against_oracle(ctx, name, M, K):
     ctx.check()
 
 
+@pytest.mark.parametrize("M,K,pad", [(1000, 5120, 0), (37, 1024, 0), (64, 1280, 6), (300, 17408, 0), (129, 2304, 22)])
+def test_row_group_mapping_against_lane_per_granule(ctx, M, K, pad):
+    """IQ3_XXS rows that are a multiple of 8 bytes apart take the row-group mapping of the one-column kernel (eight
+    lanes per row, widest aligned loads); both mappings form the same exact integer sums, so they agree with the oracle
+    and with each other to float rounding.  Rows padded to a multiple of 8 bytes (K not a multiple of 1024) and ragged
+    row counts included."""
+    f = F.IQ3_XXS
+    w = synth.make_weights(f, M, K, seed=700 + M, scale=scale_for("IQ3_XXS"))
+    rb = f.row_bytes(K) + pad
+    assert rb % 8 == 0
+    wp = np.zeros((M, rb), np.uint8)
+    wp[:, :f.row_bytes(K)] = w
+    xq = oracle.port.quantize_q8k(synth.make_activations(1, K, seed=701))
+    wd, xd = dev(wp), dev(xq)
+    y_rg = ctx.gemv(f, wd, xd, K).cpu().numpy()
+    ctx.debug_set_rowgroup(False)
+    try:
+        y_lane = ctx.gemv(f, wd, xd, K).cpu().numpy()
+    finally:
+        ctx.debug_set_rowgroup(True)
+    ctx.check()
+    ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[0], K)
+    mag = np.where(mag == 0, 1.0, mag)
+    assert np.max(np.abs(y_rg[0] - ref) / mag) < REL_TOL
+    assert np.max(np.abs(y_lane[0] - ref) / mag) < REL_TOL
+    assert np.max(np.abs(y_rg[0] - y_lane[0]) / mag) < REL_TOL
+
+
+@pytest.mark.parametrize("name", ALL)
+@pytest.mark.parametrize("M", [6144, 12288])
+def test_verify_sweep_row_counts(ctx, name, M):
+    """The speculative-verify sweep's middle row counts (M = 6144 and 12288 at K = 5120; 1024 and 17408 are covered by
+    the shape list above and the full-size test) for 1, 2, 4 and 7 columns, every row against the oracle."""
+    f = F.get(name)
+    K = 5120
+    w = synth.make_weights(f, M, K, seed=600 + M, scale=scale_for(name))
+    x = synth.make_activations(7, K, seed=601) * (np.arange(7, dtype=np.float32)[:, None] + 1)
+    xq = oracle.port.quantize_q8k(x)
+    wd, xd = dev(w), dev(xq)
+    refs = [oracle.port.row_ref_mag(f.type_id, w, xq[c], K) for c in range(7)]
+    for nb in (1, 2, 4, 7):
+        y = ctx.gemv(f, wd, xd[:nb], K).cpu().numpy()
+        for c in range(nb):
+            ref, mag = refs[c]
+            err = float(np.max(np.abs(y[c] - ref) / np.where(mag == 0, 1.0, mag)))
+            assert err < REL_TOL, (name, M, nb, c, err)
+    ctx.check()
+
+
 @pytest.mark.parametrize("name", ALL)
 def test_columns_bit_identical_to_single_column(ctx, name):
     """gemv_q8n's promise (src/cuda/gemv.cuh:31-34): every column equals the one-column call.  Holds across all nb

@@ -42,6 +42,33 @@ def test_prefill_shapes(ctx, M, K, B):
     check(ctx, "Q4_K", M, K, B)
 
 
+@pytest.mark.parametrize("name", ["IQ3_XXS", "Q4_K"])
+@pytest.mark.parametrize("M,K", [(17408, 5120), (5120, 17408)])
+def test_prefill_full_size_1024_tokens(ctx, name, M, K):
+    """The prefill chunk at its stated size: 1024 tokens against the 17408 x 5120 up projection and the 5120 x 17408
+    down projection.  All tokens of 192 sampled rows (first and last row tiles, and rows spread over the rest) are held
+    to the bound against the double-precision oracle; the remaining rows are checked for finiteness and, through a
+    second run on a row-permuted copy of the weights, for the same bits wherever a row lands."""
+    f = F.get(name)
+    B = 1024
+    w = synth.make_weights(f, M, K, seed=500 + M, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    x = torch.randn((B, K), generator=torch.Generator().manual_seed(K)).to(torch.bfloat16)
+    wd, xd = torch.from_numpy(w).cuda(), x.cuda()
+    y = ctx.gemm_prefill(f, wd, xd, K)
+    ctx.check()
+    assert bool(torch.isfinite(y).all())
+    rng = np.random.default_rng(M + K)
+    rows = np.unique(np.concatenate([np.arange(64), np.arange(M - 64, M), rng.choice(M, 64, replace=False)]))
+    want, mag = oracle.port.matmul_ref(f.type_id, np.ascontiguousarray(w[rows]), x.float().numpy(), K)
+    got = y[:, torch.from_numpy(rows).cuda()].cpu().numpy().astype(np.float64)
+    err = np.abs(got - want) / np.where(mag == 0, 1, mag)
+    assert err.max() < TOL, (name, M, K, err.max())
+    perm = torch.from_numpy(rng.permutation(M)).cuda()
+    y2 = ctx.gemm_prefill(f, wd[perm].contiguous(), xd, K)
+    ctx.check()
+    assert torch.equal(y2.view(torch.int32), y[:, perm].view(torch.int32))
+
+
 def test_prefill_accumulate_and_stride(ctx):
     check(ctx, "Q6_K", 128, 512, 40, accumulate=True)
 
