@@ -88,6 +88,7 @@ def load_library():
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
     lib.q38b_debug_set_rowgroup.argtypes = [vp, i32]
+    lib.q38b_debug_set_split_tail.argtypes = [vp, i32]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     _LIB = lib
     return lib
@@ -154,6 +155,10 @@ class Context:
     def debug_set_rowgroup(self, enabled):
         """Test hook: enabled=False keeps the one-column kernel on its lane-per-granule mapping for every format."""
         self._rc(self.lib.q38b_debug_set_rowgroup(self.h, int(bool(enabled))), "q38b_debug_set_rowgroup")
+
+    def debug_set_split_tail(self, enabled):
+        """Test hook: enabled=False makes the one-column kernel deal whole tiles only."""
+        self._rc(self.lib.q38b_debug_set_split_tail(self.h, int(bool(enabled))), "q38b_debug_set_split_tail")
 
     def set_pdl(self, enabled):
         self._rc(self.lib.q38b_ctx_set_pdl(self.h, int(bool(enabled))), "q38b_ctx_set_pdl")

@@ -13,61 +13,65 @@ namespace q38b {
 #include "codebooks.inc"
 #undef Q38B_CODEBOOK_QUALIFIER
 
-__device__ __forceinline__ float warp_max_f(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-__device__ __forceinline__ int warp_min_i(int v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+// Two and four int32 values saturated to int8 and packed (cvt.pack: low byte = the last operand of each pair).
+__device__ __forceinline__ uint32_t pack_s8x4(int q0, int q1, int q2, int q3) {
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(q1), "r"(q0), "r"(hi));
+    return w;
 }
 
-// One warp writes one ggml Q8_K block from 256 floats held 8 per lane (lane l: elements 8l..8l+7).
-// Same arithmetic as quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381): the first element of largest
-// magnitude, signed, maps to -127 (iscale = -127 / max); q = min(127, round-half-even(iscale * x));
-// bsums per 16 elements; d = 1 / iscale; an all-zero block is all zero bytes.
-// Core: the 8 int8 values of this lane packed in w0 | w1, their sum s8, and the block's d (the same in every lane).
+// One warp turns 256 floats, eight per lane (lane l: elements 8l .. 8l+7), into the values of a ggml Q8_K block.
+// Arithmetic of quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381): the FIRST element of largest magnitude, with
+// its sign, maps to -127 (iscale = -127 / that element); q = min(127, round-half-even(iscale * x)); d = 1 / iscale; a
+// block of zeros stays all zero.  Outputs: this lane's eight int8 values packed in w0 | w1, their sum s8, and d (the
+// same in every lane).
 __device__ __forceinline__ void q8k_block_core(const float (&v)[8], uint32_t& w0, uint32_t& w1, int& s8, float& d) {
-    const int lane = threadIdx.x & 31;
-    float am = 0.0f;
+    // Magnitudes compare like their bit patterns, so the block maximum is an integer maximum: one REDUX over the warp.
+    uint32_t mag[8], lane_top = 0;
 #pragma unroll
-    for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(v[e]));
-    am = warp_max_f(am);
-    w0 = 0; w1 = 0; s8 = 0; d = 0.0f;
-    if (am != 0.0f) {
-        int idx = 256;
-        float mine = 0.0f;
-#pragma unroll
-        for (int e = 7; e >= 0; e--)
-            if (fabsf(v[e]) == am) { idx = 8 * lane + e; mine = v[e]; }
-        const int first = warp_min_i(idx);
-        const float mx = __shfl_sync(0xffffffffu, mine, first >> 3);
-        const float iscale = __fdiv_rn(-127.0f, mx);
-#pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int q = min(127, __float2int_rn(__fmul_rn(iscale, v[e])));
-            s8 += q;
-            if (e < 4) w0 |= (uint32_t)(q & 0xFF) << (8 * e);
-            else w1 |= (uint32_t)(q & 0xFF) << (8 * (e - 4));
-        }
-        d = __fdiv_rn(1.0f, iscale);
+    for (int e = 0; e < 8; e++) {
+        mag[e] = __float_as_uint(v[e]) & 0x7FFFFFFFu;
+        lane_top = max(lane_top, mag[e]);
     }
+    const uint32_t top = __reduce_max_sync(0xffffffffu, lane_top);
+    w0 = 0u; w1 = 0u; s8 = 0; d = 0.0f;
+    if (top == 0u) return;
+    // First occurrence: the lowest lane that holds the maximum (ballot + find-first-set), its lowest such element.
+    float lead = 0.0f;
+    bool have = false;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const bool hit = !have && mag[e] == top;
+        lead = hit ? v[e] : lead;
+        have = have || hit;
+    }
+    const int owner = __ffs((int)__ballot_sync(0xffffffffu, have)) - 1;
+    const float iscale = __fdiv_rn(-127.0f, __shfl_sync(0xffffffffu, lead, owner));
+    int qv[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) qv[e] = __float2int_rn(__fmul_rn(iscale, v[e]));   // >= -127; the pack clamps at +127
+    w0 = pack_s8x4(qv[0], qv[1], qv[2], qv[3]);
+    w1 = pack_s8x4(qv[4], qv[5], qv[6], qv[7]);
+    s8 = __dp4a((int)w0, 0x01010101, __dp4a((int)w1, 0x01010101, 0));
+    d = __fdiv_rn(1.0f, iscale);
 }
 
+// The block as ggml lays it out (float d | int8 qs[256] | int16 bsums[16], 292 bytes, 4-byte aligned) from the core's
+// outputs: lane l owns qs[8l .. 8l+7]; a bsum covers 16 values, i.e. a pair of lanes.
 __device__ __forceinline__ void q8k_block_from_regs(const float (&v)[8], uint8_t* blk) {
     const int lane = threadIdx.x & 31;
     uint32_t w0, w1;
     int s8;
     float d;
     q8k_block_core(v, w0, w1, s8, d);
-    uint32_t* qs = (uint32_t*)(blk + 4);   // blocks are 4-byte aligned (292 = 4 * 73)
-    qs[2 * lane] = w0;
-    qs[2 * lane + 1] = w1;
-    const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
-    if ((lane & 1) == 0) ((int16_t*)(blk + 260))[lane >> 1] = (int16_t)s16;
-    if (lane == 0) *(float*)blk = d;
+    uint32_t* words = (uint32_t*)blk;
+    words[1 + 2 * lane] = w0;
+    words[2 + 2 * lane] = w1;
+    const int pair_sum = s8 + __shfl_down_sync(0xffffffffu, s8, 1);
+    int16_t* bsums = (int16_t*)(blk + 4 + 256);
+    if (!(lane & 1)) bsums[lane >> 1] = (int16_t)pair_sum;
+    if (lane == 0) words[0] = __float_as_uint(d);
 }
 
 constexpr int ACT_WARPS = 8;

@@ -206,7 +206,23 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
             a.n_stages = stages;
             a.n_tilebuf = tb;
             p->smem = a.off_stage + stages * a.stage_bytes + 128 + align_up(3 * bb, 128);   // granules past a ragged row end are read (and discarded)
-            p->grid = std::max(1, std::min(2 * ctx->sm_count, a.n_tiles));
+            // the grid and the cut of the leftover tiles (see Gemv1Args::full_rounds)
+            const int grid_max = 2 * ctx->sm_count;
+            a.full_rounds = a.n_tiles / grid_max;
+            const int rem = a.n_tiles - a.full_rounds * grid_max;
+            const int rows_per_pass = rg ? 4 : (type == T_Q4_K || type == T_Q5_K) ? 2 : 1;
+            int best_log2 = 0;
+            double best_cost = 1e30;
+            for (int lg = 0; lg <= 2 && (G1_ROWS >> lg) >= rows_per_pass && (G1_ROWS >> lg) >= 2; lg++) {
+                // sub-rounds needed, times the cost of one: its share of a tile's bytes plus what a unit costs whatever its size
+                const long long sub_rounds = (((long long)rem << lg) + grid_max - 1) / grid_max;
+                const double cost = (double)sub_rounds * (1.0 / (1 << lg) + 0.1);
+                if (cost < best_cost - 1e-9) { best_cost = cost; best_log2 = lg; }
+            }
+            if (!ctx->split_tail) best_log2 = 0;
+            a.split_log2 = best_log2;
+            a.n_sub = rem << best_log2;
+            p->grid = a.full_rounds > 0 ? grid_max : std::max(1, std::min(grid_max, a.n_sub));
             return Q38B_OK;
         }
         if (!cb_entries) break;
@@ -351,6 +367,12 @@ int q38b_ctx_set_uniform_columns(q38b_ctx* ctx, int enabled) {
 int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->rowgroup = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+// Test hook: 0 deals whole tiles only (no sub-tiles after the last full round of the grid).
+int q38b_debug_set_split_tail(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->split_tail = enabled ? 1 : 0;
     return Q38B_OK;
 }
 

@@ -42,6 +42,12 @@ struct Gemv1Args {
     int nsb;                // super-blocks per row
     int n_slices;           // ceil(nsb / 4)
     int n_tiles;            // tiles of all matrices
+    // The tiles are dealt to the CTAs round-robin; the ones left over after the last full round of the grid are cut into
+    // `1 << split_log2` sub-tiles of fewer rows, dealt round-robin again, so that the last round costs every CTA a
+    // fraction of a tile instead of a whole tile for some and nothing for the others.
+    int full_rounds;        // rounds in which every CTA takes a whole tile
+    int n_sub;              // sub-tiles after them: (n_tiles - full_rounds * grid) << split_log2
+    int split_log2;
     int n_stages;
     int chunk_slices;       // slices per stage (K-chunk); n_chunks = ceil(n_slices / chunk_slices)
     int n_chunks;
@@ -56,11 +62,32 @@ struct Gemv1Args {
 // One block of the slice for every row pass of a row-group tile (B is a template argument: the alignment of the block's
 // fields follows from it).
 template <int FMT, int B, int NPASS>
-__device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int s, SP act_block, SP actd_block, const TablesR& tabs, float (&acc)[NPASS]) {
+__device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int npass, int s, SP act_block, SP actd_block, const TablesR& tabs, float (&acc)[NPASS]) {
     ActsR ar;
     GranR<FMT>::load_acts(ar, act_block, actd_block, s);
 #pragma unroll
-    for (int ps = 0; ps < NPASS; ps++) acc[ps] += GranR<FMT>::template dot<B>(rowp[ps], s, ar, tabs);
+    for (int ps = 0; ps < NPASS; ps++)
+        if (ps < npass) acc[ps] += GranR<FMT>::template dot<B>(rowp[ps], s, ar, tabs);
+}
+
+// Tile number `ti` of this CTA: the matrix, the first row inside it and the number of rows (fewer for a sub-tile).
+struct TileRef { int mi, row0, nrows; };
+template <int ROWS>
+__device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int ti) {
+    int gtile, sub = 0, nrows = ROWS;
+    if (ti < a.full_rounds) {
+        gtile = (int)blockIdx.x + (int)gridDim.x * ti;
+    } else {
+        const int u = (int)blockIdx.x + (int)gridDim.x * (ti - a.full_rounds);
+        gtile = a.full_rounds * (int)gridDim.x + (u >> a.split_log2);
+        sub = u & ((1 << a.split_log2) - 1);
+        nrows = ROWS >> a.split_log2;
+    }
+    TileRef t;
+    t.mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+    t.row0 = (gtile - a.tile_start[t.mi]) * ROWS + sub * nrows;
+    t.nrows = nrows;
+    return t;
 }
 
 // shared-memory tables of the row-group decoders (static, so that their addresses are immediates of the loads)
@@ -98,7 +125,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     __syncthreads();
     pdl_launch_dependents();
 
-    const int my_tiles = a.n_tiles > (int)blockIdx.x ? (a.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = a.full_rounds + (a.n_sub > (int)blockIdx.x ? (a.n_sub - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0);
     const int n_items = my_tiles * a.n_chunks;       // stages this CTA streams
     const int packed_row = a.nsb * BB;
 
@@ -111,11 +138,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             for (int item = 0; item < n_items; item++) {
                 const uint32_t fb = smem_u32(&full[stage]);
                 mbar_wait_bounded(smem_u32(&empty[stage]), use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
-                const int gtile = (int)blockIdx.x + (int)gridDim.x * ti;
-                const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
+                const TileRef tr = tile_ref<G1_ROWS>(a, ti);
+                const int mi = tr.mi, row0 = tr.row0;
                 const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
                 const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
-                const int row0 = (gtile - a.tile_start[mi]) * G1_ROWS;
+                const int rows_here = min(tr.nrows, Mm - row0);
                 const uintptr_t safe_end = ((uintptr_t)Wm + (uintptr_t)(Mm - 1) * a.row_bytes + packed_row) & ~(uintptr_t)15;
                 uint8_t* sbase = smem + a.off_stage + (size_t)stage * a.stage_bytes;
                 // what this lane copies: the whole tile (lane 0, contiguous rows) or its own row's chunk
@@ -125,9 +152,9 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                 if (a.contiguous) {
                     if (lane == 0) {
                         src = (uintptr_t)Wm + (uintptr_t)row0 * a.row_bytes;
-                        len = (long long)min(G1_ROWS, Mm - row0) * a.row_bytes;
+                        len = (long long)rows_here * a.row_bytes;
                     }
-                } else if (row0 + lane < Mm) {
+                } else if (lane < rows_here) {
                     const int off = chunk * a.chunk_slices * SLICE_BYTES;
                     src = (uintptr_t)Wm + (uintptr_t)(row0 + lane) * a.row_bytes + (uintptr_t)off;
                     len = min(a.chunk_slices * SLICE_BYTES, packed_row - off);
@@ -289,13 +316,12 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             mbar_wait_bounded(smem_u32(&full[stage]), stage_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
         }
         seen_item = item;
-        const int gtile = (int)blockIdx.x + (int)gridDim.x * ti;
-        const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
-        const int tile = gtile - a.tile_start[mi];                 // tile of matrix mi
+        const TileRef tr = tile_ref<G1_ROWS>(a, ti);
+        const int mi = tr.mi;
         const uint32_t w_lo = (uint32_t)(uintptr_t)(mi == 0 ? a.W : a.W_more[mi - 1]);
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
         // low address bits of row 0 of the tile at this stage's first byte (the copy kept its low 4 address bits)
-        const uint32_t src_lo = w_lo + (uint32_t)(tile * G1_ROWS) * rb32 + (a.contiguous ? 0u : (uint32_t)(chunk * a.chunk_slices * SLICE_BYTES));
+        const uint32_t src_lo = w_lo + (uint32_t)tr.row0 * rb32 + (a.contiguous ? 0u : (uint32_t)(chunk * a.chunk_slices * SLICE_BYTES));
         float* rslot = red + ((size_t)tslot * a.n_slices + slice) * G1_ROWS;
         // a short last chunk holds fewer slices than the barrier expects: its last slice makes up the difference
         const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
@@ -312,10 +338,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                 acc[ps] = 0.0f;
             }
             const int sb0 = slice * 4;
-            if (sb0 + 0 < a.nsb) rowgroup_block<FMT, 0, PASSES>(rowp, s, actq_sp + (sb0 + 0) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 0) * 32, tabs, acc);
-            if (sb0 + 1 < a.nsb) rowgroup_block<FMT, 1, PASSES>(rowp, s, actq_sp + (sb0 + 1) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 1) * 32, tabs, acc);
-            if (sb0 + 2 < a.nsb) rowgroup_block<FMT, 2, PASSES>(rowp, s, actq_sp + (sb0 + 2) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 2) * 32, tabs, acc);
-            if (sb0 + 3 < a.nsb) rowgroup_block<FMT, 3, PASSES>(rowp, s, actq_sp + (sb0 + 3) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 3) * 32, tabs, acc);
+            const int npass = (tr.nrows + 3) >> 2;   // a sub-tile has fewer rows: passes past them are skipped
+            if (sb0 + 0 < a.nsb) rowgroup_block<FMT, 0, PASSES>(rowp, npass, s, actq_sp + (sb0 + 0) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 0) * 32, tabs, acc);
+            if (sb0 + 1 < a.nsb) rowgroup_block<FMT, 1, PASSES>(rowp, npass, s, actq_sp + (sb0 + 1) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 1) * 32, tabs, acc);
+            if (sb0 + 2 < a.nsb) rowgroup_block<FMT, 2, PASSES>(rowp, npass, s, actq_sp + (sb0 + 2) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 2) * 32, tabs, acc);
+            if (sb0 + 3 < a.nsb) rowgroup_block<FMT, 3, PASSES>(rowp, npass, s, actq_sp + (sb0 + 3) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 3) * 32, tabs, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
 #pragma unroll
@@ -333,12 +360,16 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
         const bool live = gran_sb < a.nsb;
         float acc[PASSES];
+        const int npass = LPR == 32 ? tr.nrows : (tr.nrows + 1) >> 1;   // a sub-tile has fewer rows: passes past them are skipped
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
-            const int r = LPR == 32 ? ps : 2 * ps + sub;
-            const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
-            const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
-            acc[ps] = live ? v : 0.0f;
+            acc[ps] = 0.0f;
+            if (ps < npass) {
+                const int r = LPR == 32 ? ps : 2 * ps + sub;
+                const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
+                const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
+                acc[ps] = live ? v : 0.0f;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
@@ -383,10 +414,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         if (slice == a.n_slices - 1) {
             // this warp finishes the tile: wait for the other slices, add them in slice order
             mbar_wait_bounded(tb, tile_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-            const int row = tile * G1_ROWS + lane;
+            const int row = tr.row0 + lane;
             float* ym = mi == 0 ? a.y : a.y_more[mi - 1];
             const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
-            if (lane < G1_ROWS && row < Mm) {
+            if (lane < tr.nrows && row < Mm) {
                 const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
                 float v = 0.0f;
                 for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];

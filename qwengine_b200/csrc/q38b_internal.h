@@ -12,6 +12,7 @@ struct q38b_ctx {
     int pass_pdl = 1;          // programmatic dependent launch between the kernels of a recorded pass
     int static_weights = 0;    // 1: matvec producers start streaming W before the previous kernel of the stream has finished
     int rowgroup = 1;          // 0: the row-group mapping of the one-column kernel is not used (test hook q38b_debug_set_rowgroup)
+    int split_tail = 1;        // 0: the one-column kernel deals whole tiles only (test hook q38b_debug_set_split_tail)
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     int* d_status = nullptr;
     uint32_t* d_cb_iq3xxs = nullptr;

@@ -135,6 +135,25 @@ def test_row_group_mapping_against_lane_per_granule(ctx, M, K, pad):
 
 
 @pytest.mark.parametrize("name", ALL)
+@pytest.mark.parametrize("M,K", [(5120, 1024), (2999, 1024), (8 * 296 + 8 * 40 + 3, 512), (700, 5120), (5120, 17408)])
+def test_sub_tiles_of_the_last_round_change_no_bits(ctx, name, M, K):
+    """The one-column kernel cuts the tiles left over after the last full round of the grid into sub-tiles of fewer
+    rows; a row's arithmetic does not depend on the tile it sits in, so the outputs are the bits of the whole-tile
+    schedule."""
+    f = F.get(name)
+    w = dev(synth.make_weights(f, M, K, seed=800 + M % 97, scale=scale_for(name)))
+    xq = dev(oracle.port.quantize_q8k(synth.make_activations(1, K, seed=801)))
+    y_split = ctx.gemv(f, w, xq, K)
+    ctx.debug_set_split_tail(False)
+    try:
+        y_whole = ctx.gemv(f, w, xq, K)
+    finally:
+        ctx.debug_set_split_tail(True)
+    ctx.check()
+    assert torch.equal(y_split.view(torch.int32), y_whole.view(torch.int32))
+
+
+@pytest.mark.parametrize("name", ALL)
 @pytest.mark.parametrize("M", [6144, 12288])
 def test_verify_sweep_row_counts(ctx, name, M):
     """The speculative-verify sweep's middle row counts (M = 6144 and 12288 at K = 5120; 1024 and 17408 are covered by
