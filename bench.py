@@ -27,9 +27,9 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_weight_pass_stream_bandwidth"
 UNIT = "GB/s"
 HBM_NOMINAL_GBS = 8000.0
-# dram__bytes_read of one IQ3_XXS matvec launch (three 17408 x 5120 matrices) divided by its GGUF bytes, from the
-# ncu capture summarised in profiles/gemv1_17408x5120_nb1.md
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0007
+# dram__bytes_read of one IQ3_XXS one-column launch divided by its GGUF bytes, from an ncu capture of the kernel on two
+# 17408 x 5120 matrices (the launch timed below); traffic grows in proportion to the rows, so it is scaled by bytes
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0010
 
 
 def measured_peak():
@@ -38,6 +38,14 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -117,8 +125,13 @@ def cpu_run(seconds_budget=None, steps=None, warmup=1):
                 t += time.perf_counter() - t0
         return t
 
-    for _ in range(max(1, warmup)):
+    # the reference's pool spins its threads up lazily and the weights are first touched here: at least a second of
+    # untimed passes, so that a short timed run measures the steady state
+    t_warm = time.perf_counter()
+    n_warm = 0
+    while n_warm < max(1, warmup) or time.perf_counter() - t_warm < 1.0:
         one_pass()
+        n_warm += 1
     times = []
     t_start = time.perf_counter()
     while True:
@@ -128,7 +141,7 @@ def cpu_run(seconds_budget=None, steps=None, warmup=1):
         if steps is None and time.perf_counter() - t_start > seconds_budget:
             break
     sec = sum(times) / len(times)
-    return {"value": round(nbytes / sec / 1e9, 2), "unit": UNIT, "cores": cores, "kind": kind,
+    return {"value": round(nbytes / sec / 1e9, 2), "unit": UNIT, "cores": cores, "kind": kind, "sample_bytes": nbytes,
             "sample": f"layers 0-3 (8 Q4_K, 8 IQ3_XXS, 4 IQ4_XS matrices) + 1/16 of the Q6_K head = {nbytes / 1e6:.0f} MB per "
                       f"pass, nb=1, {len(times)} timed passes",
             "ms_per_step": sec * 1e3, "steps": len(times)}
@@ -138,15 +151,29 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from qwengine_b200 import decode_pass as dp
     r = cpu_run(steps=max(1, args.steps), warmup=max(1, args.warmup))
+    total_bytes = dp.total_weight_bytes(args.layers, True)
     line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": r["steps"],
             "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 3), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "decode_weight_pass_27b_shape", "nb": 1, "arm": "reference AVX2 CPU kernels, bounded sample"},
+            "config": run_config(args.layers, args.gpus, args.gather),
+            "sample_fraction": round(r["sample_bytes"] / total_bytes, 5),
+            "arm": "the reference's AVX2 CPU kernels on this box's host cores; each step = one pass over a bounded sample of the workload's matrices (same format mix)",
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def run_config(n_layers, world, gather):
+    """The `config` object of both arms: the workload BASELINE.json's configs[4] names."""
+    from qwengine_b200 import decode_pass as dp
+    cfg = {"workload": "decode_weight_pass_27b_shape", "layers": n_layers, "matrices": len(dp.all_specs(n_layers)),
+           "weight_bytes": dp.total_weight_bytes(n_layers, True), "nb": 1,
+           "parallelism": f"row-shard x{world}" + (f" + {gather} gather" if world > 1 else ""),
+           "cache": "12.5 GB of weights per pass, far larger than L2; no flush needed"}
+    return cfg
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -171,6 +198,145 @@ def device_weights(torch, spec, rows, seed, scale):
         d0 = d
         w[:, :, off:off + 2] = d.to(torch.float16).view(torch.uint8).view(rows, nblk, 2)
     return w.view(rows, nblk * f.block_bytes)
+
+
+def time_pass(torch, ps, nb, reps, warm=2):
+    for _ in range(warm):
+        ps.run(nb)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        ps.run(nb)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def per_format_table(torch, q, ctx, peak):
+    """Every format at 17408 x 5120, one matrix per launch, cycling over distinct resident matrices of more than 1 GB in
+    all (far beyond L2), for 1 and 7 activation columns: us per matvec, GB/s of GGUF bytes, fraction of the HBM peak."""
+    from qwengine_b200 import decode_pass as dp, formats as F
+    M, K = dp.FF, dp.HIDDEN
+    out = {}
+    for name in F.FORMATS:
+        f = F.get(name)
+        nbytes = M * f.row_bytes(K)
+        copies = int(1.1e9 // nbytes) + 1
+        ps = q.Pass(ctx, max_nb=7)
+        ps.set_merge(False)                      # one launch per matrix
+        xin, xq, yb = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(M)
+        ps.quantize(xin, 0, K, xq)
+        g = torch.Generator(device="cuda").manual_seed(F.get(name).type_id)
+        for _ in range(copies):
+            w = torch.randint(0, 256, (M, f.row_bytes(K)), dtype=torch.uint8, device="cuda", generator=g)
+            ps.gemv(ps.matrix_device(f, w, K), xq, yb, 0)
+        ps.buffer_tensor(xin).normal_(generator=g)
+        row = {"bytes_per_matvec": nbytes, "distinct_matrices": copies}
+        for nb in (1, 7):
+            us = time_pass(torch, ps, nb, 3) * 1e3 / copies
+            gbs = nbytes / us / 1e3
+            row[f"nb{nb}"] = {"us": round(us, 2), "GBps": round(gbs, 1), "frac": round(gbs / peak, 4)}
+        row["nb7_vs_nb1"] = round(row["nb7"]["us"] / row["nb1"]["us"], 3)
+        out[name] = row
+        ps.close()
+    return out
+
+
+def ffn_block_time(torch, q, ctx):
+    """The decode FFN block: gate and up 17408 x 5120 in Q4_K, SwiGLU, down 5120 x 17408 in Q6_K, one column; eight
+    distinct blocks (1.4 GB) per replay."""
+    from qwengine_b200 import decode_pass as dp, formats as F
+    ps = q.Pass(ctx, max_nb=1)
+    x, xq, gu, hq = ps.buffer_f32(dp.HIDDEN), ps.buffer_q8k(dp.HIDDEN), ps.buffer_f32(2 * dp.FF), ps.buffer_q8k(dp.FF)
+    g = torch.Generator(device="cuda").manual_seed(4242)
+    n = 8
+    nbytes = 0
+    for _ in range(n):
+        ps.quantize(x, 0, dp.HIDDEN, xq)
+        for off in (0, dp.FF):
+            w = torch.randint(0, 256, (dp.FF, F.Q4_K.row_bytes(dp.HIDDEN)), dtype=torch.uint8, device="cuda", generator=g)
+            w[:, 0::144] = 0; w[:, 1::144] = 0; w[:, 2::144] = 0; w[:, 3::144] = 0      # d = dmin = 0: the chain stays finite
+            ps.gemv(ps.matrix_device(F.Q4_K, w, dp.HIDDEN), xq, gu, off)
+            nbytes += w.numel()
+        ps.swiglu(gu, 0, gu, dp.FF, dp.FF, hq)
+        w = torch.randint(0, 256, (dp.HIDDEN, F.Q6_K.row_bytes(dp.FF)), dtype=torch.uint8, device="cuda", generator=g)
+        w[:, 208::210] = 0; w[:, 209::210] = 0
+        ps.gemv(ps.matrix_device(F.Q6_K, w, dp.FF), hq, x, 0)
+        nbytes += w.numel()
+    us = time_pass(torch, ps, 1, 5) * 1e3 / n
+    ps.close()
+    return {"us_per_block": round(us, 2), "bytes_per_block": nbytes // n, "GBps": round(nbytes / n / us / 1e3, 1), "kernels_per_block": 3}
+
+
+def prefill_table(torch, ctx):
+    """The prefill chunk GEMM: 1024 bf16 tokens against 17408 x 5120 and 5120 x 17408 weights in IQ3_XXS and Q4_K."""
+    from qwengine_b200 import formats as F
+    peak, kind = measured_tensor_peak()
+    out = {"tokens": 1024, "peak_TFLOPs": peak, "peak_source": kind + " cuBLAS bf16 burst", "cases": {}}
+    g = torch.Generator(device="cuda").manual_seed(99)
+    best = 0.0
+    for name in ("IQ3_XXS", "Q4_K"):
+        f = F.get(name)
+        for M, K in ((17408, 5120), (5120, 17408)):
+            w = torch.randint(0, 256, (M, f.row_bytes(K)), dtype=torch.uint8, device="cuda", generator=g)
+            x = torch.randn((1024, K), device="cuda", generator=g).to(torch.bfloat16)
+            y = torch.empty((1024, M), device="cuda")
+            for _ in range(2):
+                ctx.gemm_prefill(f, w, x, K, out=y)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                ctx.gemm_prefill(f, w, x, K, out=y)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 5
+            tf = 2.0 * 1024 * M * K / ms / 1e9
+            best = max(best, tf)
+            out["cases"][f"{name}_{M}x{K}"] = {"ms": round(ms, 4), "TFLOPs": round(tf, 1), "frac": round(tf / peak, 4)}
+    out["roofline"] = {"bound": "tensor", "achieved": round(best, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(best / peak, 4)}
+    return out
+
+
+def sharded_equals_single(torch, dist, q, ctx, rank, world, gather):
+    """Correctness of the row-sharded pass at this world size: a 4-layer + head pass on seeded weights, sharded over the
+    ranks, against the same pass unsharded on rank 0's GPU (a context of its own), bit for bit, for 1 and 7 columns."""
+    from qwengine_b200 import decode_pass as dp, formats as F
+    n_layers = 4
+
+    def weights(spec, rows_from, rows):
+        # the whole matrix from a seed that does not depend on the rank, then this rank's rows
+        w = device_weights(torch, spec, spec.M, seed=777 + sum(map(ord, spec.name)), scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
+        return w[rows_from:rows_from + rows].contiguous()
+
+    x0 = torch.randn((7, dp.HIDDEN), device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+    ps = q.Pass(ctx, max_nb=7)
+    io = dp.build(ps, lambda spec, rows: ps.matrix_device(spec.fmt, weights(spec, rank * rows, rows), spec.K), n_layers=n_layers, head=True,
+                  rank=rank, world=world, gather=gather)
+    outs = {}
+    for nb in (1, 7):
+        ps.buffer_tensor(io["in_buf"]).copy_(x0)
+        ps.run(nb)
+        torch.cuda.synchronize()
+        dist.barrier()
+        outs[nb] = ps.buffer_tensor(io["out_buf"])[:nb].clone()
+    ok = True
+    if rank == 0:
+        c1 = q.Context(torch.cuda.current_device())
+        p1 = q.Pass(c1, max_nb=7)
+        io1 = dp.build(p1, lambda spec, rows: p1.matrix_device(spec.fmt, weights(spec, 0, rows), spec.K), n_layers=n_layers, head=True)
+        for nb in (1, 7):
+            p1.buffer_tensor(io1["in_buf"]).copy_(x0)
+            p1.run(nb)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(p1.buffer_tensor(io1["out_buf"])[:nb].view(torch.int32), outs[nb].view(torch.int32)))
+        c1.check()
+        p1.close()
+        c1.close()
+    ps.close()
+    dist.barrier()
+    return ok
 
 
 def run_ours(args):
@@ -210,6 +376,10 @@ def run_ours(args):
 
     if world > 1 and args.gather == "peer":
         ctx.peer_connect(world, rank, exchange(ctx.peer_arena_create()))
+
+    shard_ok = None
+    if world > 1:
+        shard_ok = sharded_equals_single(torch, dist, q, ctx, rank, world, args.gather)
 
     n_layers = args.layers
     ps = q.Pass(ctx, max_nb=7)
@@ -309,7 +479,17 @@ def run_ours(args):
                 "peak": peak, "peak_source": peak_kind + " copy bandwidth", "unit": UNIT, "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8TBps": round(achieved / HBM_NOMINAL_GBS, 4), "us_per_launch": round(kern_us, 2),
                 "algorithmic_bytes_per_launch": alg_bytes,
-                "traffic": int(alg_bytes * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE)}
+                "traffic": int(alg_bytes * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                "traffic_source": "dram bytes of an ncu capture of this launch shape on one GPU, scaled by the launch's GGUF bytes"}
+    rp.close()
+    del mats
+    extras = {}
+    if rank == 0 and world == 1 and not args.no_extras:
+        torch.cuda.empty_cache()
+        extras["per_format_17408x5120"] = per_format_table(torch, q, ctx, peak)
+        extras["ffn_block"] = ffn_block_time(torch, q, ctx)
+        extras["prefill_1024_tokens"] = prefill_table(torch, ctx)
+        ctx.check()
 
     line = None
     if rank == 0:
@@ -319,9 +499,8 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": round(ms1, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "decode_weight_pass_27b_shape", "layers": n_layers, "matrices": len(dp.all_specs(n_layers)),
-                       "weight_bytes": total_bytes, "nb": 1, "parallelism": f"row-shard x{world}" + (f" + {args.gather} gather" if world > 1 else ""),
-                       "cache": "12.5 GB of weights per pass, far larger than L2; no flush needed", "outputs_finite": finite},
+            "config": run_config(n_layers, world, args.gather),
+            "checks": {"outputs_finite": finite, "sharded_bits_equal_single": shard_ok},
             "tokens_per_s": round(1e3 / ms1, 1),
             "frac_of_nominal_8TBps": round(value / world / HBM_NOMINAL_GBS, 4),
             "nb7": {"ms_per_step": round(ms7, 4), "value": round(total_bytes / ms7 / 1e6, 1), "tokens_per_s": round(7e3 / ms7, 1),
@@ -332,6 +511,9 @@ def run_ours(args):
             "roofline": roofline,
             "clocks": clocks.summary(),
         }
+        line.update(extras)
+        if "prefill_1024_tokens" in extras:
+            line["roofline_prefill"] = extras["prefill_1024_tokens"]["roofline"]
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
@@ -350,6 +532,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="number of layers of the pass (64 = the benchmark configuration)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="multi-GPU output exchange: fused peer stores or NCCL")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-format, FFN-block and prefill legs (one GPU only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -49,6 +49,12 @@ void q38b_ctx_destroy(q38b_ctx* ctx);
 int q38b_ctx_check(q38b_ctx* ctx, void* stream);
 int q38b_last_cuda_error(const q38b_ctx* ctx);
 const char* q38b_status_string(int status);
+/* Bounded waits: a kernel that waits for another GPU (the cross-GPU barrier of the peer-store gather) gives up after
+ * this many SM clocks, sets a status bit that q38b_ctx_check reports as Q38B_ERR_DEVICE_WAIT, and runs to its end; the
+ * context stays usable.  Default 4e9 (about two seconds).  Waits inside one GPU (shared-memory barriers) keep a fixed
+ * budget of about a second. */
+int q38b_ctx_set_wait_budget_cycles(q38b_ctx* ctx, long long cycles);
+
 /* Programmatic dependent launch lets a matvec start (and prefetch) while the previous KERNEL of the stream drains.  It
  * is always used between the kernels of a recorded pass.  For direct calls it is off by default, because a direct call
  * may follow a memcpy that fills its operands, which a programmatic launch does not wait for; 1 turns it on for
@@ -101,6 +107,22 @@ int q38b_gemv_f32(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_by
                   long long x_ld, int nb, float* y_dev, long long y_ld, int accumulate, void* q8k_scratch_dev,
                   size_t scratch_bytes, void* stream);
 
+/* The reference GPU path's own activation format (ActQ8, src/cuda/gemv.cuh:14-21): int8 q[K], one scale d per 32 values
+ * and s = d * sum(q) per 32 values; n_rows rows of K values, row r at q + r * K, d + r * K / 32, s + r * K / 32.
+ * Replaces quantize_act_q8 (src/cuda/gemv.cu:31-47, 200-204), same arithmetic: d = amax / 127, q = round-half-even(v / d).
+ * K must be a multiple of 32. */
+int q38b_quantize_act_q8(q38b_ctx* ctx, const float* x_dev, int K, int n_rows, int8_t* q_dev, float* d_dev, float* s_dev,
+                         void* stream);
+
+/* Replaces gemv_q8n / gemv_q8 on ActQ8 activations (src/cuda/gemv.cuh:23-34, src/cuda/gemv.cu:206-233):
+ * y_dev[c * y_ld + r] (+)= W[r,:] . x_c for c < nb, where x_c is the per-32 quantized column at q_dev + c * act_ld with
+ * its scales at d_dev + c * act_ld / 32 (act_ld a multiple of 32, >= K).  The integer sums per 32 weights are exact and
+ * each is scaled by its own activation scale.  Every column is computed by the one-column kernel, so column c equals
+ * the nb = 1 call on that column bit for bit (the promise of src/cuda/gemv.cuh:31-34) and the cost grows linearly
+ * with nb; the Q8_K entry points above are the fast path for several columns. */
+int q38b_gemv_act_q8(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const int8_t* q_dev,
+                     const float* d_dev, int nb, int act_ld, float* y_dev, int y_ld, int accumulate, void* stream);
+
 /* No counterpart in the reference.  q38b_gemv_f32 for callers that may not allocate device memory (an engine that
  * sized its arena at start-up, code running during stream capture, a loop that must not synchronise): the Q8_K
  * scratch is a fixed array inside the library, q38b_gemv_f32_static_capacity() bytes (158,848: up to 8 columns of
@@ -133,10 +155,21 @@ int q38b_dequant_rows(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t ro
 /* Replaces dequant_rows_f16 + gemm_f16 (src/cuda/prefill.cu:802-851; call site Engine::gemm_split,
  * src/runtime/engine.cpp:2308-2354) by one kernel: Y_dev[t * ldy + r] (+)= sum_k X[t][k] * W[r][k] for t < B tokens,
  * r < M rows; X_dev is bf16 [B][ldx] (16-byte aligned, ldx a multiple of 8), weights are GGUF blocks dequantized on
- * the fly to bf16 (each the exact dequantize_row_ref value rounded once) and multiplied on tcgen05 tensor cores with
- * fp32 accumulation in tensor memory. */
+ * the fly to bf16 in shared memory and multiplied on tcgen05 tensor cores with fp32 accumulation in tensor memory.
+ * What the tensor core multiplies, per format: Q8_0, IQ3_XXS, IQ3_S, IQ4_XS: the exact dequantize_row_ref value
+ * (src/quant/quant_ref.cpp:323-351) rounded once to bf16; Q4_K, Q5_K, Q6_K: scale (d * sc) and minimum (dmin * m) are
+ * rounded to bf16 first and applied to the exact integer by one bf16 fused multiply-add, so a weight may differ from
+ * the rounded exact value by 2^-8 of its magnitude (outputs stay within 4e-3 of sum |w x|; the path's bound is 1e-2). */
 int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* X_dev,
                       long long ldx, int B, float* Y_dev, long long ldy, int accumulate, void* stream);
+
+/* The same with fp16 operands, which is what the reference's own prefill path multiplies (dequant_rows_f16 writes fp16
+ * weights, gemm_f16 takes fp16 activations: src/cuda/prefill.cuh:17-24): X_dev is fp16 [B][ldx]; weights are
+ * dequantized to fp16 (the codebook formats and Q8_0: the exact value rounded once, i.e. dequant_rows_f16's output; the
+ * K-quants: scale and minimum rounded to fp16 first, 2^-11 relative).  Y differs from dequant_rows_f16 + gemm_f16 only
+ * by the order of the fp32 additions (and that scale rounding for the K-quants). */
+int q38b_gemm_prefill_f16(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int M, const void* X_dev,
+                          long long ldx, int B, float* Y_dev, long long ldy, int accumulate, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * All-HBM planner.  Replaces the reference's residency planner and split upload (plan_residency,
@@ -201,6 +234,24 @@ int q38b_pass_kernel_count(const q38b_pass* pass);
  * column share a launch (q38b_gemv_group), and a quantize step whose output only feeds the matvecs right after it is
  * folded into them.  Results are bit-identical either way; enabled = 0 replays one kernel per recorded step. */
 int q38b_pass_set_merge(q38b_pass* pass, int enabled);
+/* ------------------------------------------------------------------------------------------------------------
+ * GGUF files -> planner.  Replaces, for this path, the reference's GGUF v3 parser and split upload
+ * (src/runtime/gguf_parser.h:70-146, src/runtime/engine.cpp:594-629): the file is memory-mapped, the key-value table
+ * is skipped (general.alignment is honoured), the tensor-info table is read with bounds checks, and a 2-D weight
+ * tensor goes to the pass row-sharded exactly like q38b_pass_matrix_upload.  GGUF stores dims[0] = row length K first.
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct q38b_gguf q38b_gguf;
+int q38b_gguf_open(const char* path, q38b_gguf** out);      /* Q38B_ERR_UNSUPPORTED: not GGUF v2/v3; Q38B_ERR_ARG: malformed */
+void q38b_gguf_close(q38b_gguf* file);
+int q38b_gguf_tensor_count(const q38b_gguf* file);
+int q38b_gguf_find(const q38b_gguf* file, const char* name);   /* index, or -1 */
+/* Any out pointer may be NULL.  type: ggml type id; dims: 4 entries, unused ones 1; data: inside the read-only mapping;
+ * nbytes: 0 for a type whose block size this library does not know. */
+int q38b_gguf_tensor(const q38b_gguf* file, int index, const char** name, uint32_t* type, int* n_dims, long long dims[4],
+                     const void** data, size_t* nbytes);
+/* Rows [shard * M / n_shards, (shard + 1) * M / n_shards) of tensor `index` (2-D, a supported format) -> matrix id. */
+int q38b_pass_matrix_from_gguf(q38b_pass* pass, const q38b_gguf* file, int index, int shard, int n_shards);
+
 #ifdef __cplusplus
 }
 #endif

@@ -161,3 +161,29 @@ def _get_port():
 port = _get_port()
 _ref_lib = _load(os.path.join(_HERE, "_ref", "libq38ref.so"))
 ref = _Ref(_ref_lib) if _ref_lib is not None else None
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Per-32 activation format of the reference's GPU path (ActQ8: int8 q[K], float d[K/32], float s[K/32] = d * sum q),
+# restated with numpy float32 arithmetic: src/cuda/gemv.cu:31-47 of the reference project (one warp per 32 values:
+# d = amax / 127, q = round-half-even(v / d), zero block stays zero, s = d * (float) sum q).
+# ---------------------------------------------------------------------------------------------------------------
+def quantize_act_q8(x):
+    """x float32 [n_rows, K] -> (q int8 [n_rows, K], d float32 [n_rows, K/32], s float32 [n_rows, K/32])."""
+    x = np.ascontiguousarray(x, np.float32)
+    n, K = x.shape
+    v = x.reshape(n, K // 32, 32)
+    amax = np.abs(v).max(axis=2)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        qf = np.rint((v / d[:, :, None]).astype(np.float32))
+    qf = np.where(d[:, :, None] > 0, qf, np.float32(0))
+    q = qf.astype(np.int8)
+    s = (d * qf.sum(axis=2, dtype=np.float32)).astype(np.float32)
+    return q.reshape(n, K), d, s
+
+
+def act_q8_dequant(q, d):
+    """The activations an ActQ8 row stands for: d[k / 32] * q[k], float32 [n_rows, K]."""
+    n, K = q.shape
+    return (q.reshape(n, K // 32, 32).astype(np.float32) * d[:, :, None]).reshape(n, K)

@@ -5,4 +5,4 @@ The product is ``libq38b200.so`` (hand-written sm_100a CUDA behind the C ABI of
 wrapper.  There is no CPU fallback: without the built library or without a GPU the calls raise.
 """
 from . import formats, synth            # noqa: F401
-from .api import Context, Pass, Q38BError, load_library, library_path   # noqa: F401
+from .api import Context, GgufFile, Pass, Q38BError, load_library, library_path   # noqa: F401

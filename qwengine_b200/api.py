@@ -61,6 +61,7 @@ def load_library():
     lib.q38b_gemv_f32_static.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_gemv_f32_static_capacity.restype = sz
     lib.q38b_gemm_prefill.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
+    lib.q38b_gemm_prefill_f16.argtypes = [vp, u32, vp, sz, i32, i32, vp, ll, i32, vp, ll, i32, vp]
     lib.q38b_comm_unique_id.argtypes = [vp]
     lib.q38b_comm_init.argtypes = [vp, i32, i32, vp]
     lib.q38b_peer_arena_create.argtypes = [vp, sz, vp]
@@ -87,7 +88,17 @@ def load_library():
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
+    lib.q38b_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.q38b_gguf_close.argtypes = [vp]
+    lib.q38b_gguf_find.argtypes = [vp, C.c_char_p]
+    lib.q38b_pass_matrix_from_gguf.argtypes = [vp, vp, i32, i32, i32]
+    lib.q38b_ctx_set_wait_budget_cycles.argtypes = [vp, ll]
+    lib.q38b_debug_fake_silent_peer.argtypes = [vp, i32]
+    lib.q38b_quantize_act_q8.argtypes = [vp, vp, i32, i32, vp, vp, vp, vp]
+    lib.q38b_gemv_act_q8.argtypes = [vp, u32, vp, sz, i32, i32, vp, vp, i32, i32, vp, i32, i32, vp]
     lib.q38b_debug_set_rowgroup.argtypes = [vp, i32]
+    lib.q38b_debug_set_dynamic_tiles.argtypes = [vp, i32]
+    lib.q38b_debug_set_line_phase.argtypes = [vp, i32]
     lib.q38b_debug_set_split_tail.argtypes = [vp, i32]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     _LIB = lib
@@ -156,9 +167,20 @@ class Context:
         """Test hook: enabled=False keeps the one-column kernel on its lane-per-granule mapping for every format."""
         self._rc(self.lib.q38b_debug_set_rowgroup(self.h, int(bool(enabled))), "q38b_debug_set_rowgroup")
 
+    def debug_set_line_phase(self, enabled):
+        """Test hook: enabled=False lands the weight copies at their source's phase inside 16 bytes, not 128."""
+        self._rc(self.lib.q38b_debug_set_line_phase(self.h, int(bool(enabled))), "q38b_debug_set_line_phase")
+
+    def debug_set_dynamic_tiles(self, enabled):
+        """Test hook: enabled=False deals the one-column kernel's tiles round-robin instead of by tickets."""
+        self._rc(self.lib.q38b_debug_set_dynamic_tiles(self.h, int(bool(enabled))), "q38b_debug_set_dynamic_tiles")
+
     def debug_set_split_tail(self, enabled):
         """Test hook: enabled=False makes the one-column kernel deal whole tiles only."""
         self._rc(self.lib.q38b_debug_set_split_tail(self.h, int(bool(enabled))), "q38b_debug_set_split_tail")
+
+    def set_wait_budget_cycles(self, cycles):
+        self._rc(self.lib.q38b_ctx_set_wait_budget_cycles(self.h, int(cycles)), "q38b_ctx_set_wait_budget_cycles")
 
     def set_pdl(self, enabled):
         self._rc(self.lib.q38b_ctx_set_pdl(self.h, int(bool(enabled))), "q38b_ctx_set_pdl")
@@ -201,6 +223,29 @@ class Context:
         self._rc(self.lib.q38b_gemv_q8k(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, xq.data_ptr(),
                                         xq.stride(0) // F.Q8K_BLOCK_BYTES, nb, out.data_ptr(), out.stride(0),
                                         int(bool(accumulate)), _stream()), "q38b_gemv_q8k")
+        return out
+
+    def quantize_act_q8(self, x):
+        """x float32 [n_rows, K] -> (q int8 [n_rows, K], d float32 [n_rows, K/32], s float32 [n_rows, K/32]): the per-32
+        activation format of the reference GPU path."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        n, K = x.shape
+        q = torch.empty((n, K), dtype=torch.int8, device=x.device)
+        d = torch.empty((n, K // 32), dtype=torch.float32, device=x.device)
+        s = torch.empty_like(d)
+        self._rc(self.lib.q38b_quantize_act_q8(self.h, x.data_ptr(), K, n, q.data_ptr(), d.data_ptr(), s.data_ptr(), _stream()),
+                 "q38b_quantize_act_q8")
+        return q, d, s
+
+    def gemv_act_q8(self, fmt, W, q, d, K, out=None, accumulate=False):
+        """W uint8 [M, row_bytes]; q int8 [nb, K], d float32 [nb, K/32] (contiguous); returns y float32 [nb, M]."""
+        f = F.get(fmt)
+        M, nb = W.shape[0], q.shape[0]
+        if out is None:
+            out = torch.empty((nb, M), dtype=torch.float32, device=W.device)
+        self._rc(self.lib.q38b_gemv_act_q8(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, q.data_ptr(), d.data_ptr(), nb,
+                                           q.stride(0), out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()),
+                 "q38b_gemv_act_q8")
         return out
 
     def gemv_group(self, fmt, Ws, K, xq=None, x_f32=None):
@@ -246,14 +291,16 @@ class Context:
                                       accumulate, _stream())
 
     def gemm_prefill(self, fmt, W, X, K, out=None, accumulate=False):
-        """W uint8 [M, row_bytes]; X bfloat16 [B, K]; returns Y float32 [B, M] = X @ dequant(W)^T."""
+        """W uint8 [M, row_bytes]; X bfloat16 or float16 [B, K] (the operand type of the tensor-core product follows X);
+        returns Y float32 [B, M] = X @ dequant(W)^T."""
         f = F.get(fmt)
-        assert X.dtype == torch.bfloat16 and X.stride(1) == 1
+        assert X.dtype in (torch.bfloat16, torch.float16) and X.stride(1) == 1
         M, B = W.shape[0], X.shape[0]
         if out is None:
             out = torch.empty((B, M), dtype=torch.float32, device=W.device)
-        self._rc(self.lib.q38b_gemm_prefill(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, X.data_ptr(), X.stride(0), B,
-                                            out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()), "q38b_gemm_prefill")
+        fn = self.lib.q38b_gemm_prefill if X.dtype == torch.bfloat16 else self.lib.q38b_gemm_prefill_f16
+        self._rc(fn(self.h, f.type_id, W.data_ptr(), W.stride(0), K, M, X.data_ptr(), X.stride(0), B,
+                    out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()), "q38b_gemm_prefill")
         return out
 
     def dequant_rows(self, fmt, W, K, kind=OUT_F32):
@@ -307,6 +354,13 @@ class Pass:
         return self._id(self.lib.q38b_pass_matrix_upload(self.h, f.type_id, w_host.ctypes.data, rb, K, M, shard, n_shards),
                         "q38b_pass_matrix_upload")
 
+    def matrix_from_gguf(self, gguf_file, name, shard=0, n_shards=1):
+        """Uploads this rank's rows of the named 2-D tensor of an open GGUF file (GgufFile); returns the matrix id."""
+        idx = self.lib.q38b_gguf_find(gguf_file.h, name.encode())
+        if idx < 0:
+            raise KeyError(name)
+        return self._id(self.lib.q38b_pass_matrix_from_gguf(self.h, gguf_file.h, idx, shard, n_shards), "q38b_pass_matrix_from_gguf")
+
     def matrix_device(self, fmt, W, K):
         f = F.get(fmt)
         self._keep.append(W)
@@ -350,6 +404,23 @@ class Pass:
     @property
     def kernel_count(self):
         return int(self.lib.q38b_pass_kernel_count(self.h))
+
+
+class GgufFile:
+    """A memory-mapped GGUF model file (q38b_gguf_open)."""
+
+    def __init__(self, path):
+        import ctypes
+        self.lib = load_library()
+        self.h = ctypes.c_void_p()
+        rc = self.lib.q38b_gguf_open(str(path).encode(), ctypes.byref(self.h))
+        if rc != 0:
+            raise Q38BError(rc, "q38b_gguf_open")
+
+    def close(self):
+        if self.h:
+            self.lib.q38b_gguf_close(self.h)
+            self.h = None
 
 
 def _tensor_from_ptr(ptr, shape, device):

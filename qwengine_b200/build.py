@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq38b200.so")
-SOURCES = ["q38b_api.cu", "q38b_plan.cu", "q38b_prefill.cu", "q38b_static.cu"]
+SOURCES = ["q38b_api.cu", "q38b_plan.cu", "q38b_prefill.cu", "q38b_static.cu", "q38b_gguf.cpp"]
 
 
 def _stale():

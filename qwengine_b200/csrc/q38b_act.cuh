@@ -115,6 +115,26 @@ static __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_q8k_kernel(con
     quantize_block<false>(x + (size_t)r * x_ld + (size_t)sb * 256, out + ((size_t)r * out_stride + sb) * 292);
 }
 
+// The reference GPU path's activation format (ActQ8, src/cuda/gemv.cuh:14-21; quantizer src/cuda/gemv.cu:31-47): one
+// warp per 32 values, d = amax / 127, q = round-half-even(v / d) (an all-zero block stays zero), s = d * sum q.
+static __global__ void __launch_bounds__(ACT_WARPS * 32) quantize_act_q8_kernel(const float* __restrict__ x, long long n_blocks,
+                                                                          int8_t* __restrict__ q, float* __restrict__ d,
+                                                                          float* __restrict__ s) {
+    const long long blk = (long long)blockIdx.x * ACT_WARPS + (threadIdx.x >> 5);
+    if (blk >= n_blocks) return;
+    const int lane = threadIdx.x & 31;
+    const float v = x[blk * 32 + lane];
+    const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v) & 0x7FFFFFFFu));
+    const float dd = __fdiv_rn(amax, 127.0f);
+    const int qi = dd > 0.0f ? __float2int_rn(__fdiv_rn(v, dd)) : 0;
+    q[blk * 32 + lane] = (int8_t)qi;
+    const int sum = __reduce_add_sync(0xffffffffu, qi);
+    if (lane == 0) {
+        d[blk] = dd;
+        s[blk] = __fmul_rn(dd, (float)sum);
+    }
+}
+
 static __global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                                                      long long ld, int n, int n_rows, float* __restrict__ h,
                                                                      uint8_t* __restrict__ out, long long out_stride,

@@ -170,10 +170,12 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
         if (i < n_mats) a.n_tiles += (Ms[i] + G1_ROWS - 1) / G1_ROWS;
     }
     for (int i = n_mats; i < G1_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
-    a.off_actd = 2048;
+    a.off_actd = 2176;   // barriers (1536 bytes), flags, ring of tile numbers
     a.off_actq = a.off_actd + a.n_slices * 4 * 32;
     a.off_cb = a.off_actq + a.n_slices * (rg ? 4 * ACTR_BLOCK_BYTES : 1024);
     const int packed = nsb * bb;
+    a.phase_mask = ctx->line_phase ? 127 : 15;
+    const int phase_slack = a.phase_mask - 15;
     // stage shape: 8 whole rows in one bulk copy when the rows are packed and small enough, else 8 per-row copies of a
     // K-chunk of `chunk_slices` slices (bulk copies are issue-rate limited: keep each above ~2 KB)
     const int target = 28 * 1024;
@@ -181,14 +183,14 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
         a.contiguous = 1;
         a.chunk_slices = a.n_slices;
         a.slot_stride = packed;
-        a.stage_bytes = align_up(G1_ROWS * packed + 64, 128);
+        a.stage_bytes = align_up(G1_ROWS * packed + 64 + phase_slack, 128);
     } else {
         a.contiguous = 0;
         int cs = std::max(1, std::min(a.n_slices, (target / G1_ROWS - 32) / (4 * bb)));
         const int nch = (a.n_slices + cs - 1) / cs;
         cs = (a.n_slices + nch - 1) / nch;          // even chunks
         a.chunk_slices = cs;
-        a.slot_stride = align_up(cs * 4 * bb + 32, 16);
+        a.slot_stride = align_up(cs * 4 * bb + 32 + phase_slack, 16);
         a.stage_bytes = align_up(G1_ROWS * a.slot_stride + 64, 128);
     }
     a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
@@ -223,6 +225,7 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
             a.split_log2 = best_log2;
             a.n_sub = rem << best_log2;
             p->grid = a.full_rounds > 0 ? grid_max : std::max(1, std::min(grid_max, a.n_sub));
+            a.n_sched = a.full_rounds * p->grid + a.n_sub;
             return Q38B_OK;
         }
         if (!cb_entries) break;
@@ -242,11 +245,15 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_m
     return Q38B_ERR_NOMEM;
 }
 
-template <int FMT, int ROWS, bool RG>
+template <int FMT, int ROWS, bool RG, bool A32 = false>
 int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS, RG>;
+    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS, RG, A32>;
     const int rc = ensure_kernel_smem(ctx, (const void*)kern, G1_SMEM_BUDGET - (RG ? RG_STATIC_BYTES : 0), true);
     if (rc != Q38B_OK) return rc;
+    Gemv1Args args = p.a;
+    // Consecutive launches take the counter pairs in turn: a launch may start while the one before it is still running
+    // (programmatic dependent launch), and a pair is zero again when the kernel that used it has finished.
+    args.sched = ctx->dynamic_tiles && ctx->d_sched ? ctx->d_sched + 2 * (ctx->sched_seq++ % Q38B_SCHED_PAIRS) : nullptr;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)p.grid);
@@ -258,12 +265,21 @@ int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
-    Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p.a));
+    Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args));
     return Q38B_OK;
 }
 
 template <int FMT>
 int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
+    if (p.a.xd32) {   // per-32 activations: lane-per-granule mapping only
+        if (p.rg) return Q38B_ERR_ARG;
+        switch (p.rows) {
+            case 8: return launch_gemv1_rows<FMT, 8, false, true>(ctx, p, st);
+            case 4: return launch_gemv1_rows<FMT, 4, false, true>(ctx, p, st);
+            case 2: return launch_gemv1_rows<FMT, 2, false, true>(ctx, p, st);
+            default: return Q38B_ERR_ARG;
+        }
+    }
     if constexpr (FMT == T_IQ3_XXS) {
         if (p.rg && p.rows == 8) return launch_gemv1_rows<FMT, 8, true>(ctx, p, st);
         if (p.rg && p.rows == 4) return launch_gemv1_rows<FMT, 4, true>(ctx, p, st);
@@ -313,6 +329,8 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
         cudaDeviceGetAttribute(&c->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
         if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         cudaMemset(c->d_status, 0, sizeof(int));
+        if (cudaMalloc(&c->d_sched, 2 * Q38B_SCHED_PAIRS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
+        cudaMemset(c->d_sched, 0, 2 * Q38B_SCHED_PAIRS * sizeof(int));
         const void *xxs = nullptr, *s = nullptr;
         if (cudaGetSymbolAddress((void**)&xxs, q38b_iq3xxs_grid) != cudaSuccess ||
             cudaGetSymbolAddress((void**)&s, q38b_iq3s_grid) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
@@ -322,6 +340,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
     if (rc != Q38B_OK) {
         c->last_cuda = (int)cudaGetLastError();
         if (c->d_status) cudaFree(c->d_status);
+        if (c->d_sched) cudaFree(c->d_sched);
         delete c;
         return rc;
     }
@@ -332,6 +351,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
 void q38b_ctx_destroy(q38b_ctx* ctx) {
     if (!ctx) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_sched) cudaFree(ctx->d_sched);
     if (ctx->d_flags) cudaFree(ctx->d_flags);
     delete ctx;
 }
@@ -369,10 +389,52 @@ int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
     ctx->rowgroup = enabled ? 1 : 0;
     return Q38B_OK;
 }
+// Test hook: 0 lands every copy at its source's phase inside 16 bytes instead of inside a 128-byte line.
+int q38b_debug_set_line_phase(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->line_phase = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+int q38b_debug_set_trace(q38b_ctx* ctx, void* dev_buf) { ctx->dbg_trace = dev_buf; return 0; }   // TEMP
+// Test hook: 0 deals the tiles of the one-column kernel round-robin instead of by tickets.
+int q38b_debug_set_dynamic_tiles(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    ctx->dynamic_tiles = enabled ? 1 : 0;
+    return Q38B_OK;
+}
 // Test hook: 0 deals whole tiles only (no sub-tiles after the last full round of the grid).
 int q38b_debug_set_split_tail(q38b_ctx* ctx, int enabled) {
     if (!ctx) return Q38B_ERR_ARG;
     ctx->split_tail = enabled ? 1 : 0;
+    return Q38B_OK;
+}
+
+int q38b_ctx_set_wait_budget_cycles(q38b_ctx* ctx, long long cycles) {
+    if (!ctx || cycles < 1000) return Q38B_ERR_ARG;
+    ctx->wait_budget_cycles = cycles;
+    return Q38B_OK;
+}
+
+// Test hook: makes this context believe it is rank 0 of 2 whose peer's flag block is its own arena, which nobody
+// signals, so that a cross-GPU barrier runs into its bounded wait on one GPU (enabled = 0 undoes it).
+int q38b_debug_fake_silent_peer(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return Q38B_ERR_ARG;
+    if (enabled) {
+        if (!ctx->d_flags) {
+            unsigned char handle[64];
+            const int rc = q38b_peer_arena_create(ctx, 1 << 20, handle);
+            if (rc != Q38B_OK) return rc;
+        }
+        ctx->peer_flags[0] = ctx->d_flags;
+        ctx->peer_flags[1] = ctx->d_flags + 64;   // rank 1 "writes" into words nobody reads; its own word [1] of the local block stays 0
+        ctx->n_ranks = 2;
+        ctx->rank = 0;
+        ctx->peers_connected = 1;
+    } else {
+        ctx->n_ranks = 1;
+        ctx->rank = 0;
+        ctx->peers_connected = 0;
+    }
     return Q38B_OK;
 }
 
@@ -432,6 +494,7 @@ static PeerSync take_pending_sync(q38b_ctx* ctx) {
         ps.n = ctx->n_ranks;
         ps.rank = ctx->rank;
         ps.seq = ctx->pending_sync_seq;
+        ps.budget = ctx->wait_budget_cycles;
     }
     ctx->pending_sync_seq = -1;
     return ps;
@@ -602,6 +665,17 @@ int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, si
     return plan_gemv1(ctx, type, K, M, n_mats, row_bytes, &p1) == Q38B_OK;
 }
 
+// Test hook: rows per tile the one-column kernel would use on a 148-SM device (0: the shape does not fit it).
+int q38b_debug_gemv1_rows(uint32_t type, int K, int M, size_t row_bytes, int rowgroup) {
+    q38b_ctx ctx;
+    ctx.sm_count = 148;
+    ctx.smem_optin = 232448;
+    ctx.rowgroup = rowgroup;
+    Plan1 p1;
+    if (!known_format(type) || K <= 0 || K % 256 || plan_gemv1(&ctx, type, K, &M, 1, row_bytes, &p1) != Q38B_OK) return 0;
+    return p1.rows * 100 + p1.a.n_stages;
+}
+
 int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                     const void* q8k, const float* x_f32, float* const* y, void* stream) {
     return q38b_gemv_group_peers(ctx, type, n_mats, W, row_bytes, K, M, q8k, x_f32, y, nullptr, 0, stream);
@@ -637,6 +711,7 @@ int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* 
     g.xq = (const uint8_t*)q8k;
     g.x_f32 = x_f32;
     g.sync = take_pending_sync(ctx);
+    g.trace = (unsigned long long*)ctx->dbg_trace;
     g.n_peers = n_peers;
     for (int i = 0; i < n_mats; i++)
         for (int pr = 0; pr < n_peers; pr++) (i == 0 ? g.y_peer[pr] : g.y_peer_more[i - 1][pr]) = y_peers[i * n_peers + pr];
@@ -656,6 +731,62 @@ int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* 
         case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
         default: return Q38B_ERR_UNSUPPORTED;
     }
+}
+
+int q38b_quantize_act_q8(q38b_ctx* ctx, const float* x, int K, int n_rows, int8_t* q, float* d, float* s, void* stream) {
+    if (!ctx || !x || !q || !d || !s || K <= 0 || K % 32 || n_rows < 1) return Q38B_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)d | (uintptr_t)s) & 3) return Q38B_ERR_ALIGN;
+    const long long blocks = (long long)n_rows * (K / 32);
+    quantize_act_q8_kernel<<<(unsigned)((blocks + ACT_WARPS - 1) / ACT_WARPS), ACT_WARPS * 32, 0, (cudaStream_t)stream>>>(x, blocks, q, d, s);
+    Q38B_CUDA(ctx, cudaGetLastError());
+    return Q38B_OK;
+}
+
+int q38b_gemv_act_q8(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const int8_t* q, const float* d,
+                     int nb, int act_ld, float* y, int y_ld, int accumulate, void* stream) {
+    if (!ctx || !W || !q || !d || !y) return Q38B_ERR_ARG;
+    if (!known_format(type)) return Q38B_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 256 || M < 1 || nb < 1 || nb > 8 || y_ld < M || act_ld < K || act_ld % 32) return Q38B_ERR_ARG;
+    if (row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
+    const int al = format_alignment(type);
+    if (((uintptr_t)W & 15) || (row_bytes % al) || ((uintptr_t)q & 3) || (act_ld & 3) || ((uintptr_t)d & 3) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
+    // One launch of the one-column kernel per column: every column is the single-column result by construction (the
+    // promise of src/cuda/gemv.cuh:31-34 of the reference), at nb times the cost of one column.
+    const int saved_rg = ctx->rowgroup;
+    ctx->rowgroup = 0;
+    int rc = Q38B_OK;
+    for (int c = 0; c < nb && rc == Q38B_OK; c++) {
+        Plan1 p1;
+        memset(&p1, 0, sizeof(p1));
+        if (plan_gemv1(ctx, type, K, &M, 1, row_bytes, &p1) != Q38B_OK) { rc = Q38B_ERR_NOMEM; break; }
+        Gemv1Args& g = p1.a;
+        g.W = (const uint8_t*)W;
+        g.row_bytes = (long long)row_bytes;
+        g.xq = (const uint8_t*)(q + (size_t)c * act_ld);
+        g.xd32 = d + (size_t)c * (act_ld / 32);
+        g.x_f32 = nullptr;
+        g.y = y + (size_t)c * y_ld;
+        g.n_peers = 0;
+        g.static_weights = ctx->static_weights;
+        g.status = ctx->d_status;
+        g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+        g.K = K;
+        g.M = M;
+        g.accumulate = accumulate ? 1 : 0;
+        cudaStream_t st = (cudaStream_t)stream;
+        switch (type) {
+            case T_Q8_0: rc = launch_gemv1<T_Q8_0>(ctx, p1, st); break;
+            case T_Q4_K: rc = launch_gemv1<T_Q4_K>(ctx, p1, st); break;
+            case T_Q5_K: rc = launch_gemv1<T_Q5_K>(ctx, p1, st); break;
+            case T_Q6_K: rc = launch_gemv1<T_Q6_K>(ctx, p1, st); break;
+            case T_IQ3_XXS: rc = launch_gemv1<T_IQ3_XXS>(ctx, p1, st); break;
+            case T_IQ3_S: rc = launch_gemv1<T_IQ3_S>(ctx, p1, st); break;
+            case T_IQ4_XS: rc = launch_gemv1<T_IQ4_XS>(ctx, p1, st); break;
+            default: rc = Q38B_ERR_UNSUPPORTED;
+        }
+    }
+    ctx->rowgroup = saved_rg;
+    return rc;
 }
 
 int q38b_gemv_f32(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const float* x, long long x_ld,

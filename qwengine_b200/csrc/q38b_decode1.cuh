@@ -119,8 +119,11 @@ Q38B_HD constexpr int cb1_rep_log2(int fmt) { return fmt == T_IQ3_S ? 4 : 5; }
 // what a lane needs from the activations for one slice
 template <int NWORDS> struct ActRegs {
     uint32_t q[NWORDS];   // int8 activations of the granule, in the format's staged order
-    float dx;             // Q8_K block scale of the granule's super-block
+    float dx;             // Q8_K block scale of the granule's super-block (per-32 activations: the scale of the granule's 32)
 };
+// Activation scales come in two layouts of the same array (32 floats per slice = 8 per super-block): Q8_K activations
+// keep one scale per super-block in slot 8 * sb; per-32 activations (the reference GPU path's ActQ8,
+// src/cuda/gemv.cuh:14-21) one scale per 32 weights in slot 8 * sb + j.  A32 selects the second.
 
 template <int FMT> struct Gran;
 
@@ -131,14 +134,17 @@ template <int FMT> struct Gran;
 template <> struct Gran<T_IQ3_XXS> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
         sp_ld128(aq, 32 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
         sp_ld128(aq, 32 * lane + 16, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
-        a.dx = sp_ldf(ad, (lane >> 3) * 32) * 0.25f;
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32) * 0.25f;
     }
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) { return dot(row, a, cb, lane); }
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
         const SP p = row + 98 * (lane >> 3);
         const int s = lane & 7;
@@ -169,14 +175,17 @@ template <> struct Gran<T_IQ3_XXS> {
 template <> struct Gran<T_IQ3_S> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
         sp_ld128(aq, 32 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
         sp_ld128(aq, 32 * lane + 16, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
-        a.dx = sp_ldf(ad, (lane >> 3) * 32);
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) { return dot(row, a, cb, lane); }
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
         const SP p = row + 110 * (lane >> 3);
         const int s = lane & 7;
@@ -209,14 +218,17 @@ template <> struct Gran<T_IQ3_S> {
 template <> struct Gran<T_IQ4_XS> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
         sp_ld128(aq, 32 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
         sp_ld128(aq, 32 * lane + 16, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
-        a.dx = sp_ldf(ad, (lane >> 3) * 32);
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) { return dot(row, a, cb, lane); }
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const SP p = row + 136 * (lane >> 3);
         const int s = lane & 7;
@@ -246,7 +258,8 @@ template <> struct Gran<T_IQ4_XS> {
 template <int NBITS> struct GranQ45K {
     static constexpr int WORDS = 16, LANES_PER_ROW = 16;
     static constexpr int BB = NBITS == 5 ? 176 : 144, QS = NBITS == 5 ? 48 : 16;
-    struct Acts { uint32_t q[16]; float dx; int bs0, bs1; };
+    struct Acts { uint32_t q[16]; float dx, dx1; int bs0, bs1; };   // dx1: scale of the second sub-block (per-32 activations)
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         const int pr = lane & 15;
 #pragma unroll
@@ -255,11 +268,13 @@ template <int NBITS> struct GranQ45K {
             sp_ld128(aq, 64 * pr + 16 * i, v);
             a.q[4 * i] = v[0]; a.q[4 * i + 1] = v[1]; a.q[4 * i + 2] = v[2]; a.q[4 * i + 3] = v[3];
         }
-        a.dx = sp_ldf(ad, (pr >> 2) * 32);
+        a.dx = sp_ldf(ad, A32 ? 8 * pr : (pr >> 2) * 32);
+        a.dx1 = A32 ? sp_ldf(ad, 8 * pr + 4) : a.dx;
         a.bs0 = 0; a.bs1 = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) { a.bs0 = dp4a_ss(0x01010101u, a.q[i], a.bs0); a.bs1 = dp4a_ss(0x01010101u, a.q[8 + i], a.bs1); }
     }
+    template <bool A32>
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const int pr = lane & 15, pp = pr & 3;
         const SP p = row + BB * (pr >> 2);
@@ -305,9 +320,11 @@ template <int NBITS> struct GranQ45K {
                 hi = dp4a_ss(((w[i] >> 4) & 0x0F0F0F0Fu) | ((hb << 3) & 0x10101010u), a.q[8 + i], hi);
             }
         }
+        const float d = fp16_bits_to_float(dd & 0xFFFFu), dmin = fp16_bits_to_float(dd >> 16);
+        if (A32)   // each sub-block of the pair has its own activation scale
+            return d * (a.dx * (float)(sc0 * lo) + a.dx1 * (float)(sc1 * hi)) - dmin * (a.dx * (float)(mn0 * a.bs0) + a.dx1 * (float)(mn1 * a.bs1));
         const int sumi = sc0 * lo + sc1 * hi;
         const int msum = mn0 * a.bs0 + mn1 * a.bs1;
-        const float d = fp16_bits_to_float(dd & 0xFFFFu), dmin = fp16_bits_to_float(dd >> 16);
         return d * a.dx * (float)sumi - dmin * a.dx * (float)msum;
     }
 };
@@ -320,13 +337,17 @@ template <> struct Gran<T_Q5_K> : GranQ45K<5> {};
 // ---------------------------------------------------------------------------------------------------------------
 template <> struct Gran<T_Q6_K> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
-    using Acts = ActRegs<WORDS>;
+    struct Acts { uint32_t q[8]; float dx; float dxs[4]; };   // dxs: scales of the granule's four 32-weight groups (per-32 activations)
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         const int sb = lane >> 3, n = (lane >> 2) & 1, i = lane & 3;
 #pragma unroll
         for (int j = 0; j < 4; j++) sp_ld64(aq, 256 * sb + 128 * n + 32 * j + 8 * i, a.q[2 * j], a.q[2 * j + 1]);
         a.dx = sp_ldf(ad, sb * 32);
+#pragma unroll
+        for (int j = 0; j < 4; j++) a.dxs[j] = A32 ? sp_ldf(ad, sb * 32 + 16 * n + 4 * j) : a.dx;
     }
+    template <bool A32>
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const int n = (lane >> 2) & 1, i = lane & 3;
         const SP p = row + 210 * (lane >> 3);
@@ -344,6 +365,12 @@ template <> struct Gran<T_Q6_K> {
             d4[3] = dp4a_ss(Unit<T_Q6_K>::q6(qb[k] >> 4, qh[k] >> 2), a.q[6 + k], d4[3]);
         }
         const SP sc = p + (192 + 8 * n + (i >> 1));          // scale of group 8n + 2j + (i >> 1)
+        if (A32) {   // group j of the granule lies in 32-weight block 4n + j of the super-block
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc += a.dxs[j] * (float)(sp_ld8s(sc, 2 * j) * d4[j]);
+            return fp16_bits_to_float(sp_ld16(p, 208)) * acc;
+        }
         int sumi = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) sumi += sp_ld8s(sc, 2 * j) * d4[j];
@@ -357,14 +384,17 @@ template <> struct Gran<T_Q6_K> {
 template <> struct Gran<T_Q8_0> {
     static constexpr int WORDS = 8, LANES_PER_ROW = 32;
     using Acts = ActRegs<WORDS>;
+    template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
         sp_ld128(aq, 32 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
         sp_ld128(aq, 32 * lane + 16, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
-        a.dx = sp_ldf(ad, (lane >> 3) * 32);
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) { return dot(row, a, cb, lane); }
     static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
         const SP p = row + 34 * lane;
         const uint32_t mis = sp_low2(p) ^ 2u;                // the int8 values start 2 bytes into the block

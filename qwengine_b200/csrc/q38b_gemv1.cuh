@@ -28,6 +28,7 @@ struct Gemv1Args {
     int M_more[G1_MAX_MATS - 1];
     int tile_start[G1_MAX_MATS];   // first tile of each matrix in the sequence (tile_start[0] = 0; unused ones = n_tiles)
     long long row_bytes;
+    const float* xd32;      // per-32 activations (kernels instantiated with A32): xq = K int8 values, xd32 = K / 32 scales
     const uint8_t* xq;      // Q8_K blocks of the single column, or nullptr:
     const float* x_f32;     // then the K floats of the column, quantized to Q8_K blocks by every CTA in its prologue
     float* y;
@@ -48,6 +49,13 @@ struct Gemv1Args {
     int full_rounds;        // rounds in which every CTA takes a whole tile
     int n_sub;              // sub-tiles after them: (n_tiles - full_rounds * grid) << split_log2
     int split_log2;
+    // Dynamic tile scheduling: sched[0] = tickets handed out beyond each CTA's first tile, sched[1] = CTAs that have
+    // fetched their last ticket (the last one of them zeroes both for the next launch that uses this pair).  nullptr:
+    // tiles are dealt round-robin (CTA b takes b, b + grid, ...).
+    int* sched;
+    int n_sched;            // tiles and sub-tiles in all: full_rounds * grid + n_sub
+    unsigned long long* trace;   // TEMP timing probe: 8 words per CTA
+    int phase_mask;         // 127: a copy lands at the phase of its source inside a 128-byte line (one shared-memory line per line read); 15: inside 16 bytes
     int n_stages;
     int chunk_slices;       // slices per stage (K-chunk); n_chunks = ceil(n_slices / chunk_slices)
     int n_chunks;
@@ -73,14 +81,13 @@ __device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int npas
 // Tile number `ti` of this CTA: the matrix, the first row inside it and the number of rows (fewer for a sub-tile).
 struct TileRef { int mi, row0, nrows; };
 template <int ROWS>
-__device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int ti) {
-    int gtile, sub = 0, nrows = ROWS;
-    if (ti < a.full_rounds) {
-        gtile = (int)blockIdx.x + (int)gridDim.x * ti;
-    } else {
-        const int u = (int)blockIdx.x + (int)gridDim.x * (ti - a.full_rounds);
-        gtile = a.full_rounds * (int)gridDim.x + (u >> a.split_log2);
-        sub = u & ((1 << a.split_log2) - 1);
+__device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int u) {   // u: number of the tile or sub-tile in the launch's sequence
+    const int n_whole = a.full_rounds * (int)gridDim.x;
+    int gtile = u, sub = 0, nrows = ROWS;
+    if (u >= n_whole) {
+        const int v = u - n_whole;
+        gtile = n_whole + (v >> a.split_log2);
+        sub = v & ((1 << a.split_log2) - 1);
         nrows = ROWS >> a.split_log2;
     }
     TileRef t;
@@ -88,6 +95,22 @@ __device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int ti) {
     t.row0 = (gtile - a.tile_start[t.mi]) * ROWS + sub * nrows;
     t.nrows = nrows;
     return t;
+}
+
+constexpr int G1_TILE_RING = 128;   // sequence numbers of this CTA's latest tiles (more than stages can be in flight)
+
+// Consumers wait until stage fill `item` has been issued, or learn that the CTA's last fill came before it.
+__device__ __forceinline__ bool wait_item_or_end(uint32_t issued_addr, uint32_t end_addr, int item, volatile int* abort_flag, int* status) {
+    const long long t0 = clock64();
+    for (;;) {
+        if (ld_acquire_shared(issued_addr) > item) return true;
+        if (ld_acquire_shared(end_addr) <= item) return false;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, ST_WAIT_FULL_TIMEOUT);
+    return false;
 }
 
 // shared-memory tables of the row-group decoders (static, so that their addresses are immediates of the loads)
@@ -98,10 +121,12 @@ constexpr int RG_STATIC_BYTES = 4 * (RG_CB_WORDS + RG_SGN_WORDS);
 // prologue of one (or of the next kernel of the stream) overlaps the streaming of the other.
 // RG: the row-group mapping of q38b_decode1.cuh (IQ3_XXS, rows 8 bytes aligned): lane = (row of a group of four,
 // sub-block), tables in static shared memory, activations staged in the layout of actr_pos.
-template <int FMT, int NWARPS, int ROWS, bool RG>
+// A32: the column is given in the reference GPU path's per-32 format (ActQ8: xq = int8 values, xd32 = one scale per 32).
+template <int FMT, int NWARPS, int ROWS, bool RG, bool A32>
 __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1Args a) {
     constexpr int G1_ROWS = ROWS;
     static_assert(!RG || (FMT == T_IQ3_XXS && ROWS % 4 == 0), "row-group mapping: IQ3_XXS, tiles of 4 or 8 rows");
+    static_assert(!(RG && A32), "per-32 activations run on the lane-per-granule mapping");
     __shared__ __align__(128) uint32_t rg_cb[RG ? RG_CB_WORDS : 1];
     __shared__ __align__(128) uint32_t rg_sgn[RG ? RG_SGN_WORDS : 1];
     extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
@@ -111,6 +136,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     uint64_t* tbar = empty + G1_MAX_STAGES;                  // [G1_MAX_TILEBUF]
     volatile int* abort_flag = (volatile int*)(tbar + G1_MAX_TILEBUF);
     int* issued = (int*)abort_flag + 1;                      // stage fills the producer has issued so far
+    int* end_item = issued + 1;                              // fills this CTA issues in all (known once the producer ran out of tiles)
+    int* tile_seq = end_item + 1;                            // [G1_TILE_RING] sequence number of tile ti of this CTA at [ti % ring]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int BB = Unit<FMT>::BLOCK_BYTES;
     constexpr int SLICE_BYTES = 4 * BB;
@@ -118,27 +145,35 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     if (tid == 0) {
         *abort_flag = 0;
         *issued = 0;
+        *end_item = 0x7fffffff;
         for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), a.chunk_slices); }
         for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&tbar[t]), a.n_slices);
         mbar_fence_init();
     }
     __syncthreads();
     pdl_launch_dependents();
+    unsigned long long gt0 = 0;
+    if (a.trace && tid == 32) { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0)); a.trace[blockIdx.x * 8 + 0] = gt0; }
 
-    const int my_tiles = a.full_rounds + (a.n_sub > (int)blockIdx.x ? (a.n_sub - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0);
-    const int n_items = my_tiles * a.n_chunks;       // stages this CTA streams
     const int packed_row = a.nsb * BB;
 
     if (warp == 0) {
         // ---------------- producer ----------------
         if (!a.static_weights) pdl_wait_prior();   // W may be the output of the kernel before this one
         if (lane < G1_ROWS) {
-            int ti = 0, chunk = 0, stage = 0;
+            constexpr uint32_t PMASK = (1u << G1_ROWS) - 1u;     // the producing lanes
+            int ti = 0, chunk = 0, stage = 0, item = 0;
             uint32_t use = 0;                      // parity of the number of earlier fills of this stage
-            for (int item = 0; item < n_items; item++) {
+            // This CTA's first tile is its own number; the following ones are tickets from the launch's counter (fetched one
+            // tile ahead, so that the round trip of the atomic is off the critical path), or every grid-th tile without one.
+            int u = (int)blockIdx.x < a.n_sched ? (int)blockIdx.x : -1;
+            int ticket = 0;
+            if (a.sched && lane == 0) ticket = atomicAdd(a.sched, 1);
+            while (u >= 0) {
+                if (chunk == 0 && lane == 0) tile_seq[ti & (G1_TILE_RING - 1)] = u;
                 const uint32_t fb = smem_u32(&full[stage]);
                 mbar_wait_bounded(smem_u32(&empty[stage]), use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
-                const TileRef tr = tile_ref<G1_ROWS>(a, ti);
+                const TileRef tr = tile_ref<G1_ROWS>(a, u);
                 const int mi = tr.mi, row0 = tr.row0;
                 const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
                 const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
@@ -164,6 +199,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                     mbar_arrive(fb);
                 } else {
                     const uintptr_t lo = src & ~(uintptr_t)15;
+                    slot += lo & (uintptr_t)(a.phase_mask & ~15);
                     uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
                     if (hi > safe_end) {   // the tensor's last bytes do not fill a 16-byte unit: plain loads
                         hi = safe_end > lo ? safe_end : lo;
@@ -178,10 +214,36 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                         mbar_arrive(fb);
                     }
                 }
-                if (++chunk == a.n_chunks) { chunk = 0; ti++; }
                 if (++stage == a.n_stages) { stage = 0; use ^= 1u; }
-                __syncwarp((1u << G1_ROWS) - 1u);
-                if (lane == 0) st_release_shared(smem_u32(issued), item + 1);
+                __syncwarp(PMASK);
+                item++;
+                if (lane == 0) st_release_shared(smem_u32(issued), item);
+                if (++chunk == a.n_chunks) {   // next tile
+                    chunk = 0;
+                    ti++;
+                    if (a.sched) {
+                        int nu = 0;
+                        if (lane == 0) {
+                            nu = ticket + (int)gridDim.x;
+                            if (nu < a.n_sched) ticket = atomicAdd(a.sched, 1);
+                        }
+                        u = __shfl_sync(PMASK, nu, 0);
+                    } else {
+                        u += (int)gridDim.x;
+                    }
+                    if (u >= a.n_sched) u = -1;
+                }
+            }
+            if (lane == 0) {
+                st_release_shared(smem_u32(end_item), item);
+                if (a.sched) {   // the last CTA to get here leaves the pair of counters at zero for its next user
+                    __threadfence();
+                    if (atomicAdd(a.sched + 1, 1) == (int)gridDim.x - 1) {
+                        a.sched[0] = 0;
+                        a.sched[1] = 0;
+                        __threadfence();
+                    }
+                }
             }
         }
         return;
@@ -221,47 +283,67 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             sg[2 * i + 1] = hi;
         }
     }
+    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 1] = t; }
     pdl_wait_prior();
+    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 2] = t; }
     if (a.sync.n > 0) {
         peer_sync_wait(a.sync, blockIdx.x == 0, ctid, a.status);
         named_bar_sync(14, NWARPS * 32);
     }
     if (a.x_f32) {
-        // quantize the column here (every CTA, the same arithmetic as quantize_q8k_kernel): one warp per 256 values
-        for (int sb = cw; sb < a.n_slices * 4; sb += NWARPS) {
-            uint32_t w0 = 0, w1 = 0;
-            float d = 0.0f;
-            if (sb < a.nsb) {
-                float v[8];
-                const float4 lo4 = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane);
-                const float4 hi4 = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane + 4);
-                v[0] = lo4.x; v[1] = lo4.y; v[2] = lo4.z; v[3] = lo4.w;
-                v[4] = hi4.x; v[5] = hi4.y; v[6] = hi4.z; v[7] = hi4.w;
-                int s8;
-                q8k_block_core(v, w0, w1, s8, d);
-            }
-            if (lane == 0) actd[sb * 8] = d;
-            uint8_t* dst = actq + sb * 256;
-            if (RG) {
-                uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
-                *(uint2*)(blk + actr_pos(8 * lane, 0)) = make_uint2(w0, w1);
-                *(uint2*)(blk + actr_pos(8 * lane, 1)) = make_uint2(neg_bytes4(w0), neg_bytes4(w1));
-            } else if (FMT == T_IQ4_XS) {
+        // quantize the column here (every CTA, the same arithmetic as quantize_q8k_kernel): one warp per 256 values.  The
+        // loads of three blocks go out together, so the warp pays the round trip to L2 once per three blocks.
+        constexpr int QB = 3;
+        for (int sb0 = cw; sb0 < a.n_slices * 4; sb0 += QB * NWARPS) {
+            float4 lo4[QB], hi4[QB];
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const int k = 8 * lane + e;
-                    dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
+            for (int j = 0; j < QB; j++) {
+                const int sb = sb0 + j * NWARPS;
+                lo4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                hi4[j] = lo4[j];
+                if (sb < a.nsb) {
+                    lo4[j] = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane);
+                    hi4[j] = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane + 4);
                 }
-            } else {
-                *(uint2*)(dst + 8 * lane) = make_uint2(w0, w1);
+            }
+#pragma unroll
+            for (int j = 0; j < QB; j++) {
+                const int sb = sb0 + j * NWARPS;
+                if (sb >= a.n_slices * 4) continue;
+                uint32_t w0 = 0, w1 = 0;
+                float d = 0.0f;
+                if (sb < a.nsb) {
+                    const float v[8] = {lo4[j].x, lo4[j].y, lo4[j].z, lo4[j].w, hi4[j].x, hi4[j].y, hi4[j].z, hi4[j].w};
+                    int s8;
+                    q8k_block_core(v, w0, w1, s8, d);
+                }
+                if (lane == 0) actd[sb * 8] = d;
+                uint8_t* dst = actq + sb * 256;
+                if (RG) {
+                    uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
+                    *(uint2*)(blk + actr_pos(8 * lane, 0)) = make_uint2(w0, w1);
+                    *(uint2*)(blk + actr_pos(8 * lane, 1)) = make_uint2(neg_bytes4(w0), neg_bytes4(w1));
+                } else if (FMT == T_IQ4_XS) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int k = 8 * lane + e;
+                        dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
+                    }
+                } else {
+                    *(uint2*)(dst + 8 * lane) = make_uint2(w0, w1);
+                }
             }
         }
     } else {
-    for (int i = ctid; i < a.n_slices * 4; i += NWARPS * 32)
-        actd[i * 8] = i < a.nsb ? *(const float*)(a.xq + (size_t)i * Q8K_BYTES) : 0.0f;
+    if (A32) {
+        for (int i = ctid; i < a.n_slices * 32; i += NWARPS * 32) actd[i] = i < a.nsb * 8 ? a.xd32[i] : 0.0f;
+    } else {
+        for (int i = ctid; i < a.n_slices * 4; i += NWARPS * 32)
+            actd[i * 8] = i < a.nsb ? *(const float*)(a.xq + (size_t)i * Q8K_BYTES) : 0.0f;
+    }
     for (int i = ctid; i < a.n_slices * 256; i += NWARPS * 32) {   // word i of the (zero padded) activation vector
         const int sb = i >> 6, wi = i & 63;
-        const uint32_t v = sb < a.nsb ? *(const uint32_t*)(a.xq + (size_t)sb * Q8K_BYTES + 4 + 4 * wi) : 0u;
+        const uint32_t v = sb >= a.nsb ? 0u : A32 ? *(const uint32_t*)(a.xq + 4 * (size_t)i) : *(const uint32_t*)(a.xq + (size_t)sb * Q8K_BYTES + 4 + 4 * wi);
         uint8_t* dst = actq + sb * 256;
         if (RG) {
             uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
@@ -279,6 +361,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     }
     }
     named_bar_sync(15, NWARPS * 32);
+    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 3] = t; }
 
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
     cb.lane_base = sp_from(cbw) + 4 * (lane & ((1 << cb1_rep_log2(FMT)) - 1));
@@ -292,7 +375,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     constexpr int PASSES = G1_ROWS * LPR / 32;       // row passes per stage
     const int sub = LPR == 32 ? 0 : LPR == 16 ? (lane >> 4) : (lane >> 3);   // which of the rows of a pass this lane works on
 
-    const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
+    // (tile, slice) units are dealt round-robin to the warps until the producer runs out of tiles
     // The unit's (tile, slice, chunk) and the ring positions of its stage and tile buffer are stepped, never divided.
     int ti = 0, slice = cw;
     while (slice >= a.n_slices) { slice -= a.n_slices; ti++; }
@@ -303,7 +386,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     int seen_item = -1;                              // last stage fill this warp has waited for
     const uint32_t rb32 = (uint32_t)a.row_bytes;
     const uint32_t rb_step = a.contiguous ? 0u : rb32;   // rows of a contiguous stage share the copy's low address bits
-    for (int unit = cw; unit < n_units; unit += NWARPS) {
+    for (;;) {
         const int item = ti * a.n_chunks + chunk;
         while (cur_item < item) { cur_item++; if (++stage == a.n_stages) { stage = 0; stage_par ^= 1u; } }
         while (cur_ti < ti) { cur_ti++; if (++tslot == a.n_tilebuf) { tslot = 0; tile_par ^= 1u; } }
@@ -312,11 +395,12 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         // phase for this one.  The producer issues a fill only after the readers of the previous use of the barrier have
         // released it, i.e. after that phase completed: once `issued` has passed `item` the parity is unambiguous.
         if (item > seen_item) {
-            wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            if (!wait_item_or_end(smem_u32(issued), smem_u32(end_item), item, abort_flag, a.status)) break;
             mbar_wait_bounded(smem_u32(&full[stage]), stage_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
         }
+        if (a.trace && tid == 32 && seen_item < 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 4] = t; }
         seen_item = item;
-        const TileRef tr = tile_ref<G1_ROWS>(a, ti);
+        const TileRef tr = tile_ref<G1_ROWS>(a, tile_seq[ti & (G1_TILE_RING - 1)]);
         const int mi = tr.mi;
         const uint32_t w_lo = (uint32_t)(uintptr_t)(mi == 0 ? a.W : a.W_more[mi - 1]);
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
@@ -334,7 +418,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 #pragma unroll
             for (int ps = 0; ps < PASSES; ps++) {
                 const int r = 4 * ps + sub;
-                rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
+                rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & (uint32_t)a.phase_mask));
                 acc[ps] = 0.0f;
             }
             const int sb0 = slice * 4;
@@ -355,7 +439,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             }
         } else {
         typename Gran<FMT>::Acts acts;
-        Gran<FMT>::load_acts(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
+        Gran<FMT>::template load_acts<A32>(acts, actq_sp + slice * 1024, actd_sp + slice * 128, lane);
         // granules past the end of the row (K not a multiple of 1024) contribute nothing
         const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
         const bool live = gran_sb < a.nsb;
@@ -366,8 +450,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             acc[ps] = 0.0f;
             if (ps < npass) {
                 const int r = LPR == 32 ? ps : 2 * ps + sub;
-                const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
-                const float v = Gran<FMT>::dot(rowp, acts, cb, lane);
+                const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & (uint32_t)a.phase_mask));
+                const float v = Gran<FMT>::template dot<A32>(rowp, acts, cb, lane);
                 acc[ps] = live ? v : 0.0f;
             }
         }
@@ -433,6 +517,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         cslice = slice;
         while (cslice >= a.chunk_slices) { cslice -= a.chunk_slices; chunk++; }
     }
+    if (a.trace && lane == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); atomicMax(&a.trace[blockIdx.x * 8 + 5], t); }
 }
 
 }  // namespace q38b

@@ -3,6 +3,8 @@
 #include <cstddef>
 #include <cstdint>
 
+constexpr int Q38B_SCHED_PAIRS = 8;
+
 struct q38b_ctx {
     int device = 0;
     int sm_count = 0;
@@ -12,9 +14,15 @@ struct q38b_ctx {
     int pass_pdl = 1;          // programmatic dependent launch between the kernels of a recorded pass
     int static_weights = 0;    // 1: matvec producers start streaming W before the previous kernel of the stream has finished
     int rowgroup = 1;          // 0: the row-group mapping of the one-column kernel is not used (test hook q38b_debug_set_rowgroup)
+    void* dbg_trace = nullptr;   // TEMP
+    int line_phase = 1;        // one-column kernel: copies keep their source's phase inside a 128-byte line (test hook q38b_debug_set_line_phase)
     int split_tail = 1;        // 0: the one-column kernel deals whole tiles only (test hook q38b_debug_set_split_tail)
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
+    long long wait_budget_cycles = 4000000000LL;   // bounded waits on other GPUs (q38b_ctx_set_wait_budget_cycles)
     int* d_status = nullptr;
+    int* d_sched = nullptr;    // Q38B_SCHED_PAIRS pairs of tile-scheduling counters (see Gemv1Args::sched), all zero between launches
+    unsigned sched_seq = 0;
+    int dynamic_tiles = 1;     // 0: tiles are dealt round-robin (test hook q38b_debug_set_dynamic_tiles)
     uint32_t* d_cb_iq3xxs = nullptr;
     uint32_t* d_cb_iq3s = nullptr;
     void* comm = nullptr;   // ncclComm_t when q38b_comm_init was called

@@ -100,7 +100,9 @@ struct PeerSync {
     uint32_t* local;
     uint32_t* peer[8];
     int n, rank, seq;
+    long long budget;   // SM clocks a rank waits for a peer before it gives up (q38b_ctx_set_wait_budget_cycles)
 };
+constexpr long long PEER_WAIT_BUDGET_CYCLES = 4000000000LL;   // default: about two seconds
 constexpr int ST_PEER_TIMEOUT = 16;
 // Threads t = 0 .. n - 1 of every CTA call this once the stream's earlier kernels are complete (their stores into the
 // peers' buffers are done); `signaller` is true in one CTA.  Thread t tells rank t and waits (bounded) for rank t.
@@ -116,7 +118,7 @@ __device__ __forceinline__ void peer_sync_wait(const PeerSync& ps, bool signalle
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ps.local + t) : "memory");
         if ((int)(v - e) >= 0) break;
-        if (clock64() - t0 > 4000000000LL) { if (status) atomicOr(status, ST_PEER_TIMEOUT); break; }
+        if (clock64() - t0 > ps.budget) { if (status) atomicOr(status, ST_PEER_TIMEOUT); break; }
     }
 }
 

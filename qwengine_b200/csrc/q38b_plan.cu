@@ -92,10 +92,10 @@ struct q38b_pass {
     // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
     // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
     struct Captured {
-        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, split_tail;
+        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, split_tail, line_phase, dynamic_tiles;
         bool operator==(const Captured& o) const {
             return n_ops == o.n_ops && peer_store == o.peer_store && merge_steps == o.merge_steps && uniform_columns == o.uniform_columns &&
-                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && split_tail == o.split_tail;
+                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && split_tail == o.split_tail && line_phase == o.line_phase && dynamic_tiles == o.dynamic_tiles;
         }
     };
     Captured captured[9] = {};
@@ -122,6 +122,7 @@ PeerSync make_sync(const q38b_ctx* ctx, int seq) {
     ps.n = ctx->n_ranks;
     ps.rank = ctx->rank;
     ps.seq = seq;
+    ps.budget = ctx->wait_budget_cycles;
     return ps;
 }
 int launch_barrier(q38b_ctx* ctx, int n_new, int do_barrier, int seq, cudaStream_t st) {
@@ -577,7 +578,7 @@ int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const q38b_pass::Captured now = {p->ops.size(), p->peer_store, p->merge_steps, p->ctx->uniform_columns, p->ctx->pass_pdl,
-                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->split_tail};
+                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->split_tail, p->ctx->line_phase, p->ctx->dynamic_tiles};
     if (p->graphs[nb] && !(now == p->captured[nb])) {
         cudaGraphExecDestroy(p->graphs[nb]);
         p->graphs[nb] = nullptr;

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "../../include/q38b200.h"
 #include "q38b_act.cuh"
@@ -53,8 +54,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
            ((uint64_t)2 << 61);
 }
 
-// D format f32, A and B bf16, both K-major, N = 256, M = 128
-constexpr uint32_t PF_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PF_NTILE >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
+// D format f32, A and B both bf16 (format code 1) or both fp16 (code 0), K-major, N = 256, M = 128
+__host__ __device__ constexpr uint32_t pf_idesc(bool f16) {
+    return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(PF_NTILE >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -73,14 +76,35 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ uint32_t bf2_u32(__nv_bfloat162 v) { return *(const uint32_t*)&v; }
 __device__ __forceinline__ __nv_bfloat162 u32_bf2(uint32_t v) { return *(const __nv_bfloat162*)&v; }
 __device__ __forceinline__ __nv_bfloat162 bf2_splat(float x) { return __float2bfloat162_rn(x); }
-// bytes b0..b3 of t (each < 128) -> bf16 pairs (b0, b1) and (b2, b3), minus `bias`
-__device__ __forceinline__ void bytes_to_bf2(uint32_t t, __nv_bfloat162 bias, __nv_bfloat162& lo, __nv_bfloat162& hi) {
-    lo = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5140)), bias);
-    hi = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5342)), bias);
-}
+// The same for fp16 operands (the reference's prefill path multiplies fp16 weights, src/cuda/prefill.cu:30-85): an integer
+// n < 1024 becomes the half 1024 + n under the bit pattern 0x6400.
+struct OpBf16 {
+    using V2 = __nv_bfloat162;
+    static __device__ __forceinline__ V2 splat(float x) { return __float2bfloat162_rn(x); }
+    static __device__ __forceinline__ V2 bias(int extra) { const uint32_t h = 0x4300u + (uint32_t)extra; const uint32_t v = h | (h << 16); return *(const V2*)&v; }
+    static __device__ __forceinline__ void bytes(uint32_t t, V2 bs, V2& lo, V2& hi) {
+        lo = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5140)), bs);
+        hi = __hsub2(u32_bf2(__byte_perm(t, 0x43434343u, 0x5342)), bs);
+    }
+    static __device__ __forceinline__ uint32_t bits(V2 v) { return *(const uint32_t*)&v; }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) { return bf2_u32(__floats2bfloat162_rn(a, b)); }
+};
+struct OpF16 {
+    using V2 = __half2;
+    static __device__ __forceinline__ V2 splat(float x) { return __float2half2_rn(x); }
+    static __device__ __forceinline__ V2 bias(int extra) { const uint32_t h = 0x6400u + (uint32_t)extra; const uint32_t v = h | (h << 16); return *(const V2*)&v; }   // 1024 + extra: one ulp = 1 up to 2047
+    static __device__ __forceinline__ void bytes(uint32_t t, V2 bs, V2& lo, V2& hi) {
+        const uint32_t l = __byte_perm(t, 0x64646464u, 0x5140), h = __byte_perm(t, 0x64646464u, 0x5342);
+        lo = __hsub2(*(const V2*)&l, bs);
+        hi = __hsub2(*(const V2*)&h, bs);
+    }
+    static __device__ __forceinline__ uint32_t bits(V2 v) { return *(const uint32_t*)&v; }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) { const V2 v = __floats2half2_rn(a, b); return *(const uint32_t*)&v; }
+};
 
-template <int FMT>
-__device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t (&p)[16]) {
+template <int FMT, typename OP>
+__device__ __forceinline__ bool fast_sub(const uint8_t* b, int s, uint32_t (&p)[16]) {
+    using V2 = typename OP::V2;
     if (FMT == T_Q4_K || FMT == T_Q5_K) {
         if (((uintptr_t)b & 3) != 0) return false;   // the 32-bit loads below need it (blocks are multiples of 16 bytes; GGUF tensors are 32-byte aligned)
         const uint32_t dd = *(const uint32_t*)b;
@@ -89,8 +113,8 @@ __device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t 
         int scv, mv;
         if (s < 4) { scv = sc[s] & 63; mv = sc[s + 4] & 63; }
         else { scv = (sc[s + 4] & 0xF) | ((sc[s - 4] >> 6) << 4); mv = (sc[s + 4] >> 4) | ((sc[s] >> 6) << 4); }
-        const __nv_bfloat162 a2 = bf2_splat(d * (float)scv), c2 = bf2_splat(-(mn * (float)mv));
-        const __nv_bfloat162 bias = u32_bf2(0x43004300u);
+        const V2 a2 = OP::splat(d * (float)scv), c2 = OP::splat(-(mn * (float)mv));
+        const V2 bias = OP::bias(0);
         const uint32_t* q = (const uint32_t*)(b + (FMT == T_Q5_K ? 48 : 16) + 32 * (s >> 1));
         const uint32_t* qh = (const uint32_t*)(b + 16);
         const int sh = (s & 1) ? 4 : 0;
@@ -98,10 +122,10 @@ __device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t 
         for (int i = 0; i < 8; i++) {
             uint32_t t = (q[i] >> sh) & 0x0F0F0F0Fu;
             if (FMT == T_Q5_K) t |= ((qh[i] >> s) & 0x01010101u) << 4;
-            __nv_bfloat162 lo, hi;
-            bytes_to_bf2(t, bias, lo, hi);
-            p[2 * i] = bf2_u32(__hfma2(lo, a2, c2));
-            p[2 * i + 1] = bf2_u32(__hfma2(hi, a2, c2));
+            V2 lo, hi;
+            OP::bytes(t, bias, lo, hi);
+            p[2 * i] = OP::bits(__hfma2(lo, a2, c2));
+            p[2 * i + 1] = OP::bits(__hfma2(hi, a2, c2));
         }
         return true;
     }
@@ -112,18 +136,18 @@ __device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t 
         const uint16_t* ql = (const uint16_t*)(b + 64 * h + 32 * (j & 1));   // Q6_K blocks are 210 bytes: 2-byte aligned only
         const uint16_t* qh = (const uint16_t*)(b + 128 + 32 * h);
         const int8_t* sc = (const int8_t*)(b + 192 + 8 * h + 2 * j);
-        const __nv_bfloat162 bias = u32_bf2(0x43204320u);                   // 128 + 32
-        const __nv_bfloat162 a0 = bf2_splat(d * (float)sc[0]), a1 = bf2_splat(d * (float)sc[1]);
+        const V2 bias = OP::bias(32);                                        // the base + 32
+        const V2 a0 = OP::splat(d * (float)sc[0]), a1 = OP::splat(d * (float)sc[1]);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t lw = (uint32_t)ql[2 * i] | ((uint32_t)ql[2 * i + 1] << 16);
             const uint32_t hw = (uint32_t)qh[2 * i] | ((uint32_t)qh[2 * i + 1] << 16);
             const uint32_t t = ((lw >> (4 * (j >> 1))) & 0x0F0F0F0Fu) | (((hw >> (2 * j)) & 0x03030303u) << 4);
-            __nv_bfloat162 lo, hi;
-            bytes_to_bf2(t, bias, lo, hi);
-            const __nv_bfloat162 a2 = i < 4 ? a0 : a1;
-            p[2 * i] = bf2_u32(__hmul2(lo, a2));
-            p[2 * i + 1] = bf2_u32(__hmul2(hi, a2));
+            V2 lo, hi;
+            OP::bytes(t, bias, lo, hi);
+            const V2 a2 = i < 4 ? a0 : a1;
+            p[2 * i] = OP::bits(__hmul2(lo, a2));
+            p[2 * i + 1] = OP::bits(__hmul2(hi, a2));
         }
         return true;
     }
@@ -132,8 +156,10 @@ __device__ __forceinline__ bool fast_sub_bf16(const uint8_t* b, int s, uint32_t 
 
 constexpr int PF_PREFETCH_BLOCKS = 3;   // super-blocks (256 weights) of look-ahead of the L2 prefetch
 
-template <int FMT>
+// F16: operands are fp16 (weights dequantized to fp16, activations fp16) instead of bf16.
+template <int FMT, bool F16>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
+    using OP = typename std::conditional<F16, OpF16, OpBf16>::type;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full_a = (uint64_t*)smem;              // [stages] 256 decode threads arrive
     uint64_t* full_b = full_a + PF_STAGES;           // [stages] TMA bytes
@@ -187,11 +213,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             }
             uint32_t p[16];
             const uint8_t* blk = wrow + (size_t)(sub >> 3) * Unit<FMT>::BLOCK_BYTES;
-            if (!fast_sub_bf16<FMT>(blk, sub & 7, p)) {
+            if (!fast_sub<FMT, OP>(blk, sub & 7, p)) {
                 float y[32];
                 dequant_sub<FMT>(blk, sub & 7, y);
 #pragma unroll
-                for (int j = 0; j < 16; j++) p[j] = bf2_u32(__floats2bfloat162_rn(y[2 * j], y[2 * j + 1]));
+                for (int j = 0; j < 16; j++) p[j] = OP::pack(y[2 * j], y[2 * j + 1]);
             }
             // row r of the tile: 128 bytes; 16-byte chunk c goes to chunk c ^ (r & 7) (128-byte swizzle)
             uint8_t* arow = stages + (size_t)st * PF_STAGE_BYTES + (size_t)r * 128;
@@ -236,7 +262,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                            ::"r"(tmem_base + (uint32_t)(n * PF_NTILE)), "l"(adesc), "l"(bdesc), "r"(PF_IDESC), "r"(accum)
+                            ::"r"(tmem_base + (uint32_t)(n * PF_NTILE)), "l"(adesc), "l"(bdesc), "r"(pf_idesc(F16)), "r"(accum)
                             : "memory");
                     }
                 }
@@ -301,14 +327,15 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int FMT>
-int launch_prefill(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, dim3 grid, cudaStream_t st) {
-    auto kern = prefill_kernel<FMT>;
-    static int configured_device = -1;
-    if (configured_device != ctx->device) {
+template <int FMT, bool F16>
+int launch_prefill_op(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, dim3 grid, cudaStream_t st) {
+    auto kern = prefill_kernel<FMT, F16>;
+    bool known = false;   // opt-in shared-memory size: once per context (= device) and kernel
+    for (int i = 0; i < ctx->n_configured; i++) known |= ctx->configured[i] == (const void*)kern;
+    if (!known) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
         if (e != cudaSuccess) { ctx->last_cuda = (int)e; return Q38B_ERR_CUDA; }
-        configured_device = ctx->device;
+        if (ctx->n_configured < (int)(sizeof(ctx->configured) / sizeof(ctx->configured[0]))) ctx->configured[ctx->n_configured++] = (const void*)kern;
     }
     kern<<<grid, PF_THREADS, PF_SMEM, st>>>(a, map);
     cudaError_t e = cudaGetLastError();
@@ -316,10 +343,29 @@ int launch_prefill(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, 
     return Q38B_OK;
 }
 
+template <int FMT>
+int launch_prefill(q38b_ctx* ctx, const PrefillArgs& a, const CUtensorMap& map, dim3 grid, cudaStream_t st, bool f16) {
+    return f16 ? launch_prefill_op<FMT, true>(ctx, a, map, grid, st) : launch_prefill_op<FMT, false>(ctx, a, map, grid, st);
+}
+
+int gemm_prefill_any(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* X, long long ldx, int B,
+                     float* Y, long long ldy, int accumulate, void* stream, bool f16);
+
 }  // namespace
 
 extern "C" int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* X,
                                  long long ldx, int B, float* Y, long long ldy, int accumulate, void* stream) {
+    return gemm_prefill_any(ctx, type, W, row_bytes, K, M, X, ldx, B, Y, ldy, accumulate, stream, false);
+}
+
+extern "C" int q38b_gemm_prefill_f16(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* X,
+                                     long long ldx, int B, float* Y, long long ldy, int accumulate, void* stream) {
+    return gemm_prefill_any(ctx, type, W, row_bytes, K, M, X, ldx, B, Y, ldy, accumulate, stream, true);
+}
+
+namespace {
+int gemm_prefill_any(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* X, long long ldx, int B,
+                     float* Y, long long ldy, int accumulate, void* stream, bool f16) {
     if (!ctx || !W || !X || !Y || K <= 0 || K % 256 || M < 1 || B < 1 || ldx < K || ldy < M) return Q38B_ERR_ARG;
     if (!q38b_format_supported(type)) return Q38B_ERR_UNSUPPORTED;
     if (row_bytes < q38b_row_bytes(type, K)) return Q38B_ERR_ARG;
@@ -331,7 +377,7 @@ extern "C" int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W, si
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
     const cuuint32_t box[2] = {PF_KSLAB, PF_NTILE};
     const cuuint32_t estr[2] = {1, 1};
-    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)X, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    if (enc(&map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)X, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return Q38B_ERR_ARG;
     PrefillArgs a;
@@ -350,13 +396,14 @@ extern "C" int q38b_gemm_prefill(q38b_ctx* ctx, uint32_t type, const void* W, si
     const dim3 grid((unsigned)row_tiles, (unsigned)((B + tok_per_cta - 1) / tok_per_cta));
     cudaStream_t st = (cudaStream_t)stream;
     switch (type) {
-        case T_Q8_0: return launch_prefill<T_Q8_0>(ctx, a, map, grid, st);
-        case T_Q4_K: return launch_prefill<T_Q4_K>(ctx, a, map, grid, st);
-        case T_Q5_K: return launch_prefill<T_Q5_K>(ctx, a, map, grid, st);
-        case T_Q6_K: return launch_prefill<T_Q6_K>(ctx, a, map, grid, st);
-        case T_IQ3_XXS: return launch_prefill<T_IQ3_XXS>(ctx, a, map, grid, st);
-        case T_IQ3_S: return launch_prefill<T_IQ3_S>(ctx, a, map, grid, st);
-        case T_IQ4_XS: return launch_prefill<T_IQ4_XS>(ctx, a, map, grid, st);
+        case T_Q8_0: return launch_prefill<T_Q8_0>(ctx, a, map, grid, st, f16);
+        case T_Q4_K: return launch_prefill<T_Q4_K>(ctx, a, map, grid, st, f16);
+        case T_Q5_K: return launch_prefill<T_Q5_K>(ctx, a, map, grid, st, f16);
+        case T_Q6_K: return launch_prefill<T_Q6_K>(ctx, a, map, grid, st, f16);
+        case T_IQ3_XXS: return launch_prefill<T_IQ3_XXS>(ctx, a, map, grid, st, f16);
+        case T_IQ3_S: return launch_prefill<T_IQ3_S>(ctx, a, map, grid, st, f16);
+        case T_IQ4_XS: return launch_prefill<T_IQ4_XS>(ctx, a, map, grid, st, f16);
         default: return Q38B_ERR_UNSUPPORTED;
     }
 }
+}  // namespace

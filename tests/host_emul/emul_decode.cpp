@@ -150,7 +150,7 @@ extern "C" int emul_tile(int fmt, int K, const uint8_t* W, const uint8_t* xq, in
 #include "../../qwengine_b200/csrc/q38b_decode1.cuh"
 
 namespace {
-template <int FMT>
+template <int FMT, bool A32>
 void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* actq, const float* actd, const Codebook1* cbs, float* y) {
     constexpr int LPR = Gran<FMT>::LANES_PER_ROW;
     const int nsb = K / 256, n_slices = (nsb + 3) / 4;
@@ -163,8 +163,8 @@ void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* ac
                 const int gran_sb = s * 4 + (LPR == 32 ? (lane >> 3) : (lane >> 2));
                 if (gran_sb >= nsb) continue;
                 typename Gran<FMT>::Acts acts;
-                Gran<FMT>::load_acts(acts, sp_from(actq + s * 1024), sp_from(actd + s * 32), lane);
-                ssum += Gran<FMT>::dot(sp_from(rowp[r] + (size_t)s * 4 * Unit<FMT>::BLOCK_BYTES), acts, cbs[lane], lane);
+                Gran<FMT>::template load_acts<A32>(acts, sp_from(actq + s * 1024), sp_from(actd + s * 32), lane);
+                ssum += Gran<FMT>::template dot<A32>(sp_from(rowp[r] + (size_t)s * 4 * Unit<FMT>::BLOCK_BYTES), acts, cbs[lane], lane);
             }
             sum += ssum;
         }
@@ -174,7 +174,15 @@ void run_slices(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* ac
 }  // namespace
 
 // W: n_rows packed rows; xq: Q8_K blocks of one column; y[n_rows].
+static int emul_gemv1_any(int fmt, int K, const uint8_t* W, int n_rows, const uint8_t* xq, const float* d32, int addr_lo, int rep_log2, float* y);
 extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const uint8_t* xq, int addr_lo, int rep_log2, float* y) {
+    return emul_gemv1_any(fmt, K, W, n_rows, xq, nullptr, addr_lo, rep_log2, y);
+}
+// the same with the column in the per-32 format: q = K int8 values, d32 = K / 32 scales
+extern "C" int emul_gemv1_act32(int fmt, int K, const uint8_t* W, int n_rows, const int8_t* q, const float* d32, int addr_lo, float* y) {
+    return emul_gemv1_any(fmt, K, W, n_rows, (const uint8_t*)q, d32, addr_lo, 0, y);
+}
+static int emul_gemv1_any(int fmt, int K, const uint8_t* W, int n_rows, const uint8_t* xq, const float* d32, int addr_lo, int rep_log2, float* y) {
     const int bb = block_bytes(fmt), nsb = K / 256, row_bytes = nsb * bb, n_slices = (nsb + 3) / 4;
     if (!bb) return -1;
     const int slot = (row_bytes + 64 + 15) / 16 * 16;
@@ -191,6 +199,11 @@ extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const ui
     std::vector<float> actd((size_t)n_slices * 32, 0.f);
     for (int sb = 0; sb < nsb; sb++) {
         const uint8_t* blk = xq + (size_t)sb * 292;
+        if (d32) {
+            for (int j = 0; j < 8; j++) actd[sb * 8 + j] = d32[sb * 8 + j];
+            for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = xq[sb * 256 + k];
+            continue;
+        }
         memcpy(&actd[sb * 8], blk, 4);
         for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
     }
@@ -204,13 +217,13 @@ extern "C" int emul_gemv1(int fmt, int K, const uint8_t* W, int n_rows, const ui
     Codebook1 cbs[32];
     for (int l = 0; l < 32; l++) cbs[l] = Codebook1{sp_from(cb.data()) + 4 * (l & (reps - 1)), sp_from(sgn.data()) + 8 * (l & 15)};
     switch (fmt) {
-        case T_Q8_0: run_slices<T_Q8_0>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_Q4_K: run_slices<T_Q4_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_Q5_K: run_slices<T_Q5_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_Q6_K: run_slices<T_Q6_K>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_IQ3_XXS: run_slices<T_IQ3_XXS>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_IQ3_S: run_slices<T_IQ3_S>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
-        case T_IQ4_XS: run_slices<T_IQ4_XS>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q8_0: if (d32) run_slices<T_Q8_0, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q8_0, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q4_K: if (d32) run_slices<T_Q4_K, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q4_K, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q5_K: if (d32) run_slices<T_Q5_K, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q5_K, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q6_K: if (d32) run_slices<T_Q6_K, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q6_K, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ3_XXS: if (d32) run_slices<T_IQ3_XXS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ3_XXS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ3_S: if (d32) run_slices<T_IQ3_S, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ3_S, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ4_XS: if (d32) run_slices<T_IQ4_XS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ4_XS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         default: return -1;
     }
     return 0;

@@ -82,3 +82,25 @@ def test_row_group_decoder_matches_oracle(emul, K, row_pad, addr_lo):
     assert emul.emul_gemv1_rowgroup(f.type_id, K, wpad.reshape(-1), rb, M, xq.reshape(-1), addr_lo, y) == 0
     ref, mag = oracle.port.row_ref_mag(f.type_id, w, xq[0], K)
     assert np.max(np.abs(y - ref) / mag) < 1e-6
+
+
+@pytest.mark.parametrize("name", list(F.FORMATS))
+@pytest.mark.parametrize("K,addr_lo", [(1024, 0), (1280, 8)])
+def test_single_column_granules_with_per32_activations(emul, name, K, addr_lo):
+    """The same decoders fed with the reference GPU path's activation format (int8 values, one scale per 32): the
+    result is the exact dot of the dequantized weights with d[k / 32] * q[k]."""
+    f = F.get(name)
+    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8}.get(name, 2):
+        addr_lo = 0
+    u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+    f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+    emul.emul_gemv1_act32.argtypes = [C.c_int, C.c_int, u8p, C.c_int, i8p, f32p, C.c_int, f32p]
+    M = 5
+    w = synth.make_weights(f, M, K, seed=33, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    x = synth.make_activations(1, K, seed=34) * np.linspace(0.1, 3.0, K, dtype=np.float32)   # scales differ from block to block
+    q8, d32, _ = oracle.quantize_act_q8(x)
+    y = np.zeros(M, np.float32)
+    assert emul.emul_gemv1_act32(f.type_id, K, w.reshape(-1), M, q8.reshape(-1), d32.reshape(-1), addr_lo, y) == 0
+    want, mag = oracle.port.matmul_ref(f.type_id, w, oracle.act_q8_dequant(q8, d32), K)
+    assert np.max(np.abs(y - want[0]) / mag[0]) < 1e-6

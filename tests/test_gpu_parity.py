@@ -151,6 +151,15 @@ def test_sub_tiles_of_the_last_round_change_no_bits(ctx, name, M, K):
         ctx.debug_set_split_tail(True)
     ctx.check()
     assert torch.equal(y_split.view(torch.int32), y_whole.view(torch.int32))
+    # the same holds for who computes a tile: tickets from a counter (default) or every grid-th tile
+    ctx.debug_set_dynamic_tiles(False)
+    try:
+        y_static = ctx.gemv(f, w, xq, K)
+    finally:
+        ctx.debug_set_dynamic_tiles(True)
+    for _ in range(3):   # the counters are back at zero after every launch
+        assert torch.equal(ctx.gemv(f, w, xq, K).view(torch.int32), y_static.view(torch.int32))
+    ctx.check()
 
 
 @pytest.mark.parametrize("name", ALL)

@@ -242,3 +242,36 @@ def test_recorded_graph_follows_later_changes(ctx):
         ctx.set_uniform_columns(False)
     ctx.check()
     ps.close()
+
+
+def test_pass_from_gguf_file(ctx, tmp_path):
+    """Weights read from a GGUF file (written here with gguf-py) and row-sharded by the planner give the bits of the same
+    bytes uploaded directly."""
+    gguf = pytest.importorskip("gguf")
+    f, M, K = F.IQ4_XS, 64, 1024
+    w = synth.make_weights(f, M, K, seed=90)
+    path = str(tmp_path / "one.gguf")
+    wr = gguf.GGUFWriter(path, "qwen35")
+    wr.add_tensor("blk.0.ffn_down.weight", w, raw_shape=w.shape, raw_dtype=gguf.GGMLQuantizationType(f.type_id))
+    wr.write_header_to_file(); wr.write_kv_data_to_file(); wr.write_tensors_to_file(); wr.close()
+    x = synth.make_activations(1, K, seed=91)
+    want = ctx.gemv(f, torch.from_numpy(w).cuda(), ctx.quantize_q8k(torch.from_numpy(x).cuda()), K).cpu().numpy()
+    g = q.GgufFile(path)
+    out = np.zeros((1, M), np.float32)
+    for shard in range(2):
+        ps = q.Pass(ctx, max_nb=1)
+        xin, xq, yb = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(M)
+        ps.quantize(xin, 0, K, xq)
+        ps.gemv(ps.matrix_from_gguf(g, "blk.0.ffn_down.weight", shard, 2), xq, yb, shard * (M // 2))
+        y = np.empty((1, M), np.float32)
+        ps.run_host(1, xin, x, yb, 0, y)
+        out[0, shard * (M // 2):(shard + 1) * (M // 2)] = y[0, shard * (M // 2):(shard + 1) * (M // 2)]
+        ps.close()
+    g.close()
+    assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    with pytest.raises(KeyError):
+        g2 = q.GgufFile(path)
+        try:
+            q.Pass(ctx).matrix_from_gguf(g2, "missing")
+        finally:
+            g2.close()

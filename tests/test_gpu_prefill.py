@@ -89,3 +89,27 @@ def test_prefill_equals_bf16_reference_gemm(ctx, name, bound):
     ref = (x.float() @ wb.float().t())
     mag = (x.float().abs() @ wb.float().abs().t())
     assert float(((y - ref).abs() / mag).max()) < bound
+
+
+@pytest.mark.parametrize("name,bound", [("Q8_0", 1e-5), ("IQ3_XXS", 1e-5), ("IQ3_S", 1e-5), ("IQ4_XS", 1e-5), ("Q4_K", 1e-3), ("Q5_K", 1e-3), ("Q6_K", 1e-3)])
+def test_prefill_fp16_operands_equal_the_reference_path(ctx, name, bound):
+    """fp16 operands: what the reference's prefill path multiplies (dequant_rows_f16 + gemm_f16, src/cuda/prefill.cu:
+    802-851).  Against torch on the fp16 dequantized weights (q38b_dequant_rows, bit-exact to dequant_rows_f16's
+    arithmetic) with fp32 accumulation: the same operands for the codebook formats and Q8_0 (only the summation order
+    differs); the K-quants round scale and minimum to fp16 before the multiplication (2^-11 per weight).  And against
+    the double-precision oracle at the path's 1e-2 bound."""
+    from qwengine_b200 import api
+    f = F.get(name)
+    M, K, B = 384, 5120, 300
+    wn = synth.make_weights(f, M, K, seed=91, scale=2e-4 if name == "IQ3_XXS" else 1e-3)
+    w = torch.from_numpy(wn).cuda()
+    x = torch.randn((B, K), device="cuda", dtype=torch.float16)
+    y = ctx.gemm_prefill(f, w, x, K)
+    ctx.check()
+    wh = ctx.dequant_rows(f, w, K, api.OUT_F16)
+    ref = x.float() @ wh.float().t()
+    mag = x.float().abs() @ wh.float().abs().t()
+    assert float(((y - ref).abs() / mag).max()) < bound
+    want, omag = oracle.port.matmul_ref(f.type_id, wn, x.float().cpu().numpy(), K)
+    err = np.abs(y.cpu().numpy().astype(np.float64) - want) / np.where(omag == 0, 1, omag)
+    assert err.max() < TOL
