@@ -147,6 +147,25 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_
 int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g_dev, const float* u_dev, long long ld, int n, int n_rows, float* h_dev,
                     void* q8k_dev, long long q8k_stride, void* stream);
 
+/* Replaces add_rmsnorm / add_rmsnorm_rows in front of the matvecs (src/cuda/ops.cuh:35-42, src/cuda/ops.cu:78-123): for
+ * n_rows rows of n values (row stride ld floats) x += a (+ b) is written back when a or b is given (either may be NULL),
+ * then xn = x * rsqrt(mean(x^2) + eps) * w is written as fp32 to xn_dev (may be NULL) and as Q8_K blocks to q8k_dev (may
+ * be NULL; row r at q8k_dev + r * q8k_stride * 292): the residual add, the norm and the activation quantizer of the next
+ * matvecs in one pass over the row.  n a multiple of 256, at most 8192; pointers 16-byte aligned. */
+int q38b_add_rmsnorm_q8k(q38b_ctx* ctx, float* x_dev, const float* a_dev, const float* b_dev, const float* w_dev, int n,
+                         long long ld, int n_rows, float eps, float* xn_dev, void* q8k_dev, long long q8k_stride, void* stream);
+
+/* Replaces gemv_bf16 (src/cuda/gemv.cuh:27-28, src/cuda/gemv.cu:127-146): y[r] = W[r,:] . x for dense bf16 weights
+ * W [N][K] (row-major, 16-byte aligned, K a multiple of 8), fp32 x and y, fp32 accumulation. */
+int q38b_gemv_bf16(q38b_ctx* ctx, const void* W_bf16_dev, int K, int N, const float* x_dev, float* y_dev, void* stream);
+
+/* Replaces swiglu_rows_inplace (src/cuda/prefill.cuh:33-35, src/cuda/prefill.cu:132-151): for B rows of n values (row
+ * stride ld floats) silu(G) * U is written IN PLACE over the first 2 n bytes of each row of G, as fp16
+ * (out_kind = Q38B_OUT_F16, the reference's choice) or bf16 (Q38B_OUT_BF16, for q38b_gemm_prefill): the next GEMM reads
+ * G as a 16-bit matrix with row stride 2 ld.  n a multiple of 8, ld a multiple of 4, 2 n bytes of shared memory. */
+int q38b_swiglu_rows_inplace(q38b_ctx* ctx, float* G_dev, const float* U_dev, int B, int n, long long ld, int out_kind,
+                             void* stream);
+
 /* Replaces dequant_rows_f16 (src/cuda/prefill.cu:802-822): rows of GGUF blocks -> dense [rows][K] values, each the
  * exact dequantize_row_ref value (src/quant/quant_ref.cpp:323-351) as fp32, or rounded once to fp16 / bf16. */
 int q38b_dequant_rows(q38b_ctx* ctx, uint32_t type, const void* W_dev, size_t row_bytes, int K, int rows, void* out_dev,

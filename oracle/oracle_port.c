@@ -28,7 +28,8 @@
 
 /* ggml type ids, include/q38rt/q38rt_types.h:36-67 */
 enum {
-    T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ3_XXS = 18, T_IQ3_S = 21, T_IQ4_XS = 23
+    T_Q8_0 = 8, T_Q2_K = 10, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18,
+    T_IQ1_S = 19, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23, T_IQ1_M = 29
 };
 
 /* ---------------------------------------------------------------------------------------------
@@ -44,6 +45,12 @@ enum {
 #define BB_IQ3_S 110
 #define BB_IQ4_XS 136
 #define BB_Q8_K 292
+#define BB_Q2_K 84
+#define BB_IQ2_XXS 66
+#define BB_IQ2_XS 74
+#define BB_IQ2_S 82
+#define BB_IQ1_S 50
+#define BB_IQ1_M 56
 
 static inline uint16_t ld16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 static inline uint32_t ld32(const uint8_t* p) { uint32_t v; memcpy(&v, p, 4); return v; }
@@ -101,6 +108,12 @@ size_t q38o_row_bytes(uint32_t t, int K) {
         case T_IQ3_XXS: return (size_t)(K / QK_K) * BB_IQ3_XXS;
         case T_IQ3_S: return (size_t)(K / QK_K) * BB_IQ3_S;
         case T_IQ4_XS: return (size_t)(K / QK_K) * BB_IQ4_XS;
+        case T_Q2_K: return (size_t)(K / QK_K) * BB_Q2_K;
+        case T_IQ2_XXS: return (size_t)(K / QK_K) * BB_IQ2_XXS;
+        case T_IQ2_XS: return (size_t)(K / QK_K) * BB_IQ2_XS;
+        case T_IQ2_S: return (size_t)(K / QK_K) * BB_IQ2_S;
+        case T_IQ1_S: return (size_t)(K / QK_K) * BB_IQ1_S;
+        case T_IQ1_M: return (size_t)(K / QK_K) * BB_IQ1_M;
         default: return 0;
     }
 }
@@ -246,6 +259,113 @@ static void dq_iq4_xs(const uint8_t* b, float* y, int64_t n) {
 }
 
 /* src/quant/quant_ref.cpp:323-351 (the seven formats of the hot path). Returns 0 on success. */
+/* Value j (0..7) of an entry of the IQ2 grids ({8, 25, 43}) and of the IQ1 grid ({-1, 0, 1}): the tables keep eight
+ * 2-bit level indices per entry (src/quant/iq_tables.inc:12-270, 440-959 hold the same grids as 8 bytes per entry). */
+static inline int iq2_grid(uint32_t code, int j) { static const int lv[4] = {8, 25, 43, 0}; return lv[(code >> (2 * j)) & 3]; }
+static inline int iq1_grid(uint32_t code, int j) { return (int)((code >> (2 * j)) & 3) - 1; }
+#define IQ1S_DELTA 0.125f
+
+/* src/quant/quant_ref.cpp:33-55 */
+static void dq_q2_K(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_Q2_K) {
+        const float d = q38o_fp16_to_fp32(ld16(b + 80)), mn = q38o_fp16_to_fp32(ld16(b + 82));
+        const uint8_t* q = b + 16;
+        int is = 0;
+        for (int h = 0; h < 2; h++, q += 32) {
+            int shift = 0;
+            for (int j = 0; j < 4; j++, shift += 2)
+                for (int half = 0; half < 2; half++) {
+                    const uint8_t sc = b[is++];
+                    const float dl = d * (sc & 0xF), ml = mn * (sc >> 4);
+                    for (int l = 0; l < 16; l++) *y++ = dl * ((int8_t)((q[l + 16 * half] >> shift) & 3)) - ml;
+                }
+        }
+    }
+}
+
+/* src/quant/quant_ref.cpp:105-124 */
+static void dq_iq2_xxs(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_IQ2_XXS) {
+        const float d = q38o_fp16_to_fp32(ld16(b));
+        for (int ib = 0; ib < 8; ib++) {
+            const uint32_t a0 = ld32(b + 2 + 8 * ib), a1 = ld32(b + 6 + 8 * ib);
+            const float db = d * (0.5f + (a1 >> 28)) * 0.25f;
+            for (int l = 0; l < 4; l++) {
+                const uint32_t code = q38b_iq2xxs_codes[(a0 >> (8 * l)) & 0xFF], sg = ksign8((a1 >> (7 * l)) & 127);
+                for (int j = 0; j < 8; j++) *y++ = db * iq2_grid(code, j) * (((sg >> j) & 1) ? -1.f : 1.f);
+            }
+        }
+    }
+}
+
+/* src/quant/quant_ref.cpp:126-144 */
+static void dq_iq2_xs(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_IQ2_XS) {
+        const float d = q38o_fp16_to_fp32(ld16(b));
+        for (int ib = 0; ib < 8; ib++) {
+            const uint8_t sc = b[66 + ib];
+            const float db[2] = {d * (0.5f + (sc & 0xF)) * 0.25f, d * (0.5f + (sc >> 4)) * 0.25f};
+            for (int l = 0; l < 4; l++) {
+                const uint32_t qv = ld16(b + 2 + 2 * (4 * ib + l));
+                const uint32_t code = q38b_iq2xs_codes[qv & 511], sg = ksign8(qv >> 9);
+                for (int j = 0; j < 8; j++) *y++ = db[l / 2] * iq2_grid(code, j) * (((sg >> j) & 1) ? -1.f : 1.f);
+            }
+        }
+    }
+}
+
+/* src/quant/quant_ref.cpp:146-168 */
+static void dq_iq2_s(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_IQ2_S) {
+        const float d = q38o_fp16_to_fp32(ld16(b));
+        const uint8_t *qs = b + 2, *signs = b + 34, *qh = b + 66, *scl = b + 74;
+        for (int ib = 0; ib < 8; ib++) {
+            const float db[2] = {d * (0.5f + (scl[ib] & 0xF)) * 0.25f, d * (0.5f + (scl[ib] >> 4)) * 0.25f};
+            for (int l = 0; l < 4; l++) {
+                const uint32_t code = q38b_iq2s_codes[qs[4 * ib + l] | (((uint32_t)qh[ib] << (8 - 2 * l)) & 0x300)];
+                const uint32_t sg = signs[4 * ib + l];
+                for (int j = 0; j < 8; j++) *y++ = db[l / 2] * iq2_grid(code, j) * (((sg >> j) & 1) ? -1.f : 1.f);
+            }
+        }
+    }
+}
+
+/* src/quant/quant_ref.cpp:227-245 */
+static void dq_iq1_s(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_IQ1_S) {
+        const float d = q38o_fp16_to_fp32(ld16(b));
+        for (int ib = 0; ib < 8; ib++) {
+            const uint32_t qh = ld16(b + 34 + 2 * ib);
+            const float dl = d * (2 * ((qh >> 12) & 7) + 1);
+            const float delta = (qh & 0x8000) ? -IQ1S_DELTA : IQ1S_DELTA;
+            for (int l = 0; l < 4; l++) {
+                const uint32_t code = q38b_iq1s_codes[b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+                for (int j = 0; j < 8; j++) *y++ = dl * (iq1_grid(code, j) + delta);
+            }
+        }
+    }
+}
+
+/* src/quant/quant_ref.cpp:247-283 */
+static void dq_iq1_m(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / QK_K; i++, b += BB_IQ1_M) {
+        uint16_t sc[4];
+        memcpy(sc, b + 48, 8);
+        const uint16_t su = (uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000));
+        const float d = q38o_fp16_to_fp32(su);
+        const uint8_t *qs = b, *qh = b + 32;
+        for (int ib = 0; ib < 8; ib++, qs += 4, qh += 2) {
+            const float dl[2] = {d * (2 * ((sc[ib / 2] >> (6 * (ib % 2) + 0)) & 0x7) + 1), d * (2 * ((sc[ib / 2] >> (6 * (ib % 2) + 3)) & 0x7) + 1)};
+            for (int l = 0; l < 4; l++) {
+                const uint32_t hn = (qh[l / 2] >> (4 * (l & 1))) & 0xF;       /* this group's nibble: 3 index bits + delta sign */
+                const uint32_t code = q38b_iq1s_codes[qs[l] | ((hn & 7) << 8)];
+                const float delta = (hn & 8) ? -IQ1S_DELTA : IQ1S_DELTA;
+                for (int j = 0; j < 8; j++) *y++ = dl[l / 2] * (iq1_grid(code, j) + delta);
+            }
+        }
+    }
+}
+
 int q38o_dequantize_row(uint32_t t, const void* src, float* dst, int64_t n) {
     const uint8_t* b = (const uint8_t*)src;
     switch (t) {
@@ -256,6 +376,12 @@ int q38o_dequantize_row(uint32_t t, const void* src, float* dst, int64_t n) {
         case T_IQ3_XXS: dq_iq3_xxs(b, dst, n); return 0;
         case T_IQ3_S: dq_iq3_s(b, dst, n); return 0;
         case T_IQ4_XS: dq_iq4_xs(b, dst, n); return 0;
+        case T_Q2_K: dq_q2_K(b, dst, n); return 0;
+        case T_IQ2_XXS: dq_iq2_xxs(b, dst, n); return 0;
+        case T_IQ2_XS: dq_iq2_xs(b, dst, n); return 0;
+        case T_IQ2_S: dq_iq2_s(b, dst, n); return 0;
+        case T_IQ1_S: dq_iq1_s(b, dst, n); return 0;
+        case T_IQ1_M: dq_iq1_m(b, dst, n); return 0;
         default: return -1;
     }
 }
@@ -440,6 +566,112 @@ static void blk_q8_0x8(const uint8_t* b, const uint8_t* xb, col_acc* c) {
     }
 }
 
+/* the same with one integer scale for the first 16 weights (lanes 0-3) and one for the last 16 (lanes 4-7) */
+static inline void sub_dot2(int32_t* sumi, const int* w, const int8_t* q, int sc_lo, int sc_hi) {
+    for (int l = 0; l < 8; l++) {
+        int s = 0;
+        for (int j = 0; j < 4; j++) s += w[4 * l + j] * q[4 * l + j];
+        sumi[l] += (l < 4 ? sc_lo : sc_hi) * s;
+    }
+}
+
+/* src/cpu/cpu_kernels.cpp:191-217 */
+static void blk_iq2_xxs(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    for (int s = 0; s < 8; s++) {
+        const uint32_t a0 = ld32(b + 2 + 8 * s), a1 = ld32(b + 6 + 8 * s);
+        int w[32];
+        for (int l = 0; l < 4; l++) {
+            const uint32_t code = q38b_iq2xxs_codes[(a0 >> (8 * l)) & 0xFF], sg = ksign8((a1 >> (7 * l)) & 127);
+            for (int j = 0; j < 8; j++) w[8 * l + j] = ((sg >> j) & 1) ? -iq2_grid(code, j) : iq2_grid(code, j);
+        }
+        sub_dot(sumi, w, xq_qs(xb) + 32 * s, (int)(2 * (a1 >> 28) + 1));
+    }
+    block_fma(c, q38o_fp16_to_fp32(ld16(b)) * xq_d(xb) * 0.125f, sumi);
+}
+
+/* src/cpu/cpu_kernels.cpp:219-249 */
+static void blk_iq2_xs(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    for (int s = 0; s < 8; s++) {
+        int w[32];
+        for (int l = 0; l < 4; l++) {
+            const uint32_t qv = ld16(b + 2 + 2 * (4 * s + l));
+            const uint32_t code = q38b_iq2xs_codes[qv & 511], sg = ksign8(qv >> 9);
+            for (int j = 0; j < 8; j++) w[8 * l + j] = ((sg >> j) & 1) ? -iq2_grid(code, j) : iq2_grid(code, j);
+        }
+        sub_dot2(sumi, w, xq_qs(xb) + 32 * s, 2 * (b[66 + s] & 0xF) + 1, 2 * (b[66 + s] >> 4) + 1);
+    }
+    block_fma(c, q38o_fp16_to_fp32(ld16(b)) * xq_d(xb) * 0.125f, sumi);
+}
+
+/* src/cpu/cpu_kernels.cpp:251-281 */
+static void blk_iq2_s(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    const uint8_t *qs = b + 2, *signs = b + 34, *qh = b + 66, *scl = b + 74;
+    for (int s = 0; s < 8; s++) {
+        int w[32];
+        for (int l = 0; l < 4; l++) {
+            const uint32_t code = q38b_iq2s_codes[qs[4 * s + l] | (((uint32_t)qh[s] << (8 - 2 * l)) & 0x300)];
+            const uint32_t sg = signs[4 * s + l];
+            for (int j = 0; j < 8; j++) w[8 * l + j] = ((sg >> j) & 1) ? -iq2_grid(code, j) : iq2_grid(code, j);
+        }
+        sub_dot2(sumi, w, xq_qs(xb) + 32 * s, 2 * (scl[s] & 0xF) + 1, 2 * (scl[s] >> 4) + 1);
+    }
+    block_fma(c, q38o_fp16_to_fp32(ld16(b)) * xq_d(xb) * 0.125f, sumi);
+}
+
+/* src/cpu/cpu_kernels.cpp:283-313: weights 8 * (grid + delta) = 8 * grid +- 1, block scale / 8 */
+static void blk_iq1_s(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    for (int s = 0; s < 8; s++) {
+        const uint32_t qh = ld16(b + 34 + 2 * s);
+        const int dsgn = (qh & 0x8000) ? -1 : 1;
+        int w[32];
+        for (int l = 0; l < 4; l++) {
+            const uint32_t code = q38b_iq1s_codes[b[2 + 4 * s + l] | (((qh >> (3 * l)) & 7) << 8)];
+            for (int j = 0; j < 8; j++) w[8 * l + j] = 8 * iq1_grid(code, j) + dsgn;
+        }
+        sub_dot(sumi, w, xq_qs(xb) + 32 * s, (int)(2 * ((qh >> 12) & 7) + 1));
+    }
+    block_fma(c, q38o_fp16_to_fp32(ld16(b)) * xq_d(xb) * 0.125f, sumi);
+}
+
+/* src/cpu/cpu_kernels.cpp:315-349 */
+static void blk_iq1_m(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    uint16_t sc[4];
+    memcpy(sc, b + 48, 8);
+    const uint16_t su = (uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000));
+    for (int s = 0; s < 8; s++) {
+        int w[32];
+        for (int l = 0; l < 4; l++) {
+            const uint32_t hn = (b[32 + 2 * s + l / 2] >> (4 * (l & 1))) & 0xF;
+            const uint32_t code = q38b_iq1s_codes[b[4 * s + l] | ((hn & 7) << 8)];
+            for (int j = 0; j < 8; j++) w[8 * l + j] = 8 * iq1_grid(code, j) + ((hn & 8) ? -1 : 1);
+        }
+        const int t = sc[s / 2] >> (6 * (s % 2));
+        sub_dot2(sumi, w, xq_qs(xb) + 32 * s, 2 * (t & 7) + 1, 2 * ((t >> 3) & 7) + 1);
+    }
+    block_fma(c, q38o_fp16_to_fp32(su) * xq_d(xb) * 0.125f, sumi);
+}
+
+/* src/cpu/cpu_kernels.cpp:435-477 */
+static void blk_q2_K(const uint8_t* b, const uint8_t* xb, col_acc* c) {
+    int32_t sumi[8] = {0};
+    for (int sb = 0; sb < 8; sb++) {
+        const int n = sb >> 2, j = sb & 3;
+        int w[32];
+        for (int l = 0; l < 32; l++) w[l] = (b[16 + 32 * n + l] >> (2 * j)) & 3;
+        sub_dot2(sumi, w, xq_qs(xb) + 32 * sb, b[2 * sb] & 0xF, b[2 * sb + 1] & 0xF);
+    }
+    int msum = 0;
+    for (int g = 0; g < 16; g++) msum += (b[g] >> 4) * xq_bsum(xb, g);
+    const float dw = q38o_fp16_to_fp32(ld16(b + 80)), dmin = q38o_fp16_to_fp32(ld16(b + 82));
+    block_fma(c, dw * xq_d(xb), sumi);
+    c->acc_m = fmaf(dmin * xq_d(xb), (float)msum, c->acc_m);   /* :474, contracted by the reference build */
+}
+
 /* y[c] = W_row . x_c for c < nb; x_c = xq + c * x_stride blocks (src/cpu/cpu_kernels.h:19-22). */
 int q38o_vec_dot_n(uint32_t t, int K, const void* w_row, const void* xq, size_t x_stride, int nb, float* y) {
     const size_t bb = q38o_row_bytes(t, QK_K);
@@ -458,6 +690,12 @@ int q38o_vec_dot_n(uint32_t t, int K, const void* w_row, const void* xq, size_t 
                 case T_Q5_K: blk_q45_K(b, xb, &c, 5); break;
                 case T_Q6_K: blk_q6_K(b, xb, &c); break;
                 case T_Q8_0: blk_q8_0x8(b, xb, &c); break;
+                case T_Q2_K: blk_q2_K(b, xb, &c); break;
+                case T_IQ2_XXS: blk_iq2_xxs(b, xb, &c); break;
+                case T_IQ2_XS: blk_iq2_xs(b, xb, &c); break;
+                case T_IQ2_S: blk_iq2_s(b, xb, &c); break;
+                case T_IQ1_S: blk_iq1_s(b, xb, &c); break;
+                case T_IQ1_M: blk_iq1_m(b, xb, &c); break;
             }
         }
         y[cidx] = hsum8(c.acc) - c.acc_m;

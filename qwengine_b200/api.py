@@ -88,6 +88,10 @@ def load_library():
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
+    lib.q38b_debug_pass_set_fuse_swiglu.argtypes = [vp, i32]
+    lib.q38b_add_rmsnorm_q8k.argtypes = [vp, vp, vp, vp, vp, i32, ll, i32, C.c_float, vp, vp, ll, vp]
+    lib.q38b_gemv_bf16.argtypes = [vp, vp, i32, i32, vp, vp, vp]
+    lib.q38b_swiglu_rows_inplace.argtypes = [vp, vp, vp, i32, i32, ll, i32, vp]
     lib.q38b_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
     lib.q38b_gguf_close.argtypes = [vp]
     lib.q38b_gguf_find.argtypes = [vp, C.c_char_p]
@@ -97,9 +101,8 @@ def load_library():
     lib.q38b_quantize_act_q8.argtypes = [vp, vp, i32, i32, vp, vp, vp, vp]
     lib.q38b_gemv_act_q8.argtypes = [vp, u32, vp, sz, i32, i32, vp, vp, i32, i32, vp, i32, i32, vp]
     lib.q38b_debug_set_rowgroup.argtypes = [vp, i32]
-    lib.q38b_debug_set_dynamic_tiles.argtypes = [vp, i32]
-    lib.q38b_debug_set_line_phase.argtypes = [vp, i32]
-    lib.q38b_debug_set_split_tail.argtypes = [vp, i32]
+    lib.q38b_debug_occupancy_shortfalls.argtypes = [vp, i32]
+    lib.q38b_debug_set_one_cta.argtypes = [vp, i32]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     _LIB = lib
     return lib
@@ -167,17 +170,9 @@ class Context:
         """Test hook: enabled=False keeps the one-column kernel on its lane-per-granule mapping for every format."""
         self._rc(self.lib.q38b_debug_set_rowgroup(self.h, int(bool(enabled))), "q38b_debug_set_rowgroup")
 
-    def debug_set_line_phase(self, enabled):
-        """Test hook: enabled=False lands the weight copies at their source's phase inside 16 bytes, not 128."""
-        self._rc(self.lib.q38b_debug_set_line_phase(self.h, int(bool(enabled))), "q38b_debug_set_line_phase")
-
-    def debug_set_dynamic_tiles(self, enabled):
-        """Test hook: enabled=False deals the one-column kernel's tiles round-robin instead of by tickets."""
-        self._rc(self.lib.q38b_debug_set_dynamic_tiles(self.h, int(bool(enabled))), "q38b_debug_set_dynamic_tiles")
-
-    def debug_set_split_tail(self, enabled):
-        """Test hook: enabled=False makes the one-column kernel deal whole tiles only."""
-        self._rc(self.lib.q38b_debug_set_split_tail(self.h, int(bool(enabled))), "q38b_debug_set_split_tail")
+    def debug_set_one_cta(self, mode):
+        """Test hook: one CTA per SM for the one-column kernel: 0 never, 1 chosen shapes, 2 always."""
+        self._rc(self.lib.q38b_debug_set_one_cta(self.h, int(mode)), "q38b_debug_set_one_cta")
 
     def set_wait_budget_cycles(self, cycles):
         self._rc(self.lib.q38b_ctx_set_wait_budget_cycles(self.h, int(cycles)), "q38b_ctx_set_wait_budget_cycles")
@@ -247,6 +242,28 @@ class Context:
                                            q.stride(0), out.data_ptr(), out.stride(0), int(bool(accumulate)), _stream()),
                  "q38b_gemv_act_q8")
         return out
+
+    def add_rmsnorm_q8k(self, x, w, a=None, b=None, eps=1e-6, want_xn=True):
+        """x float32 [rows, n] (updated in place when a or b is given); returns (xn float32 or None, q8k uint8 [rows, n/256*292])."""
+        rows, n = x.shape
+        xn = torch.empty_like(x) if want_xn else None
+        q8 = torch.empty((rows, n // 256 * F.Q8K_BLOCK_BYTES), dtype=torch.uint8, device=x.device)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        self._rc(self.lib.q38b_add_rmsnorm_q8k(self.h, x.data_ptr(), ptr(a), ptr(b), w.data_ptr(), n, x.stride(0), rows, eps, ptr(xn),
+                                               q8.data_ptr(), n // 256, _stream()), "q38b_add_rmsnorm_q8k")
+        return xn, q8
+
+    def gemv_bf16(self, W, x):
+        """W bfloat16 [N, K], x float32 [K] -> y float32 [N]."""
+        N, K = W.shape
+        y = torch.empty(N, dtype=torch.float32, device=W.device)
+        self._rc(self.lib.q38b_gemv_bf16(self.h, W.data_ptr(), K, N, x.data_ptr(), y.data_ptr(), _stream()), "q38b_gemv_bf16")
+        return y
+
+    def swiglu_rows_inplace(self, G, U, n, kind):
+        """G, U float32 [B, ld]; writes silu(G[:, :n]) * U[:, :n] over the start of every row of G as 16-bit floats."""
+        self._rc(self.lib.q38b_swiglu_rows_inplace(self.h, G.data_ptr(), U.data_ptr(), G.shape[0], n, G.stride(0), kind, _stream()),
+                 "q38b_swiglu_rows_inplace")
 
     def gemv_group(self, fmt, Ws, K, xq=None, x_f32=None):
         """q38b_gemv_group: up to three matrices [M_i, row_bytes] of one format on one column, given as Q8_K blocks
@@ -382,6 +399,10 @@ class Pass:
     def set_merge(self, enabled):
         """enabled=False: single-column runs launch one kernel per recorded step (no shared launches, no folded quantize)."""
         self.ctx._rc(self.lib.q38b_pass_set_merge(self.h, int(bool(enabled))), "q38b_pass_set_merge")
+
+    def debug_set_fuse_swiglu(self, enabled):
+        """Test hook: enabled=False keeps SwiGLU steps as kernels of their own."""
+        self.ctx._rc(self.lib.q38b_debug_pass_set_fuse_swiglu(self.h, int(bool(enabled))), "q38b_debug_pass_set_fuse_swiglu")
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -151,6 +151,114 @@ static __global__ void __launch_bounds__(ACT_WARPS * 32) swiglu_q8k_kernel(const
     swiglu_block<false>(g + off, u + off, h ? h + off : nullptr, out ? out + ((size_t)r * out_stride + sb) * 292 : nullptr);
 }
 
+// Residual add + RMSNorm + Q8_K in one pass over the row (replaces k_add_rmsnorm feeding the matvecs,
+// src/cuda/ops.cu:78-123): x += a (+ b) is written back (the residual stream), xn = x * rsqrt(mean(x^2) + eps) * w goes
+// out as fp32 (optional) and as the Q8_K blocks the next matvecs read.  One CTA per row, one warp per 256 values: every
+// value stays in a register from the load to the quantizer.  n a multiple of 256, at most 32 * 256.
+static __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float* __restrict__ x, const float* __restrict__ a,
+                                                                      const float* __restrict__ b, const float* __restrict__ w, int n,
+                                                                      long long ld, float eps, float* __restrict__ xn,
+                                                                      uint8_t* __restrict__ q8k, long long q8k_stride) {
+    __shared__ float part[32];
+    __shared__ float s_scale;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const size_t ro = (size_t)blockIdx.x * ld, at = ro + (size_t)warp * 256 + 8 * lane;
+    float v[8];
+    {
+        const float4 lo = *(const float4*)(x + at), hi = *(const float4*)(x + at + 4);
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    }
+    if (a) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = __fadd_rn(v[e], a[at + e]);
+    }
+    if (b) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = __fadd_rn(v[e], b[at + e]);
+    }
+    if (a || b) {
+        *(float4*)(x + at) = make_float4(v[0], v[1], v[2], v[3]);
+        *(float4*)(x + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? part[lane] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) s_scale = rsqrtf(t / (float)n + eps);
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    const float4 wl = *(const float4*)(w + (size_t)warp * 256 + 8 * lane), wh = *(const float4*)(w + (size_t)warp * 256 + 8 * lane + 4);
+    const float ww[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = __fmul_rn(__fmul_rn(v[e], scale), ww[e]);
+    if (xn) {
+        *(float4*)(xn + at) = make_float4(v[0], v[1], v[2], v[3]);
+        *(float4*)(xn + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (q8k) q8k_block_from_regs(v, q8k + ((size_t)blockIdx.x * q8k_stride + warp) * 292);
+}
+
+// y[r] = W[r,:] . x for dense bf16 weights (the model's two small per-layer projections, 48 x 5120; replaces gemv_bf16,
+// src/cuda/gemv.cu:127-146, 235-238).  One CTA of BF16_THREADS per row: every thread takes 16-byte pieces (eight bf16) of
+// the row, fp32 multiply-adds, a shuffle tree per warp and a last add over the warps in shared memory.
+constexpr int BF16_THREADS = 128;
+static __global__ void __launch_bounds__(BF16_THREADS) gemv_bf16_kernel(const uint16_t* __restrict__ W, int K, int N,
+                                                                       const float* __restrict__ x, float* __restrict__ y) {
+    __shared__ float part[BF16_THREADS / 32];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const uint4* w = (const uint4*)(W + (size_t)row * K);
+    float acc = 0.0f;
+    for (int i = tid; i < K / 8; i += BF16_THREADS) {
+        const uint4 p = w[i];
+        const float4 xa = *(const float4*)(x + 8 * i), xb = *(const float4*)(x + 8 * i + 4);
+        // a bf16 is the upper half of an fp32
+        acc = fmaf(__uint_as_float(p.x << 16), xa.x, acc); acc = fmaf(__uint_as_float(p.x & 0xFFFF0000u), xa.y, acc);
+        acc = fmaf(__uint_as_float(p.y << 16), xa.z, acc); acc = fmaf(__uint_as_float(p.y & 0xFFFF0000u), xa.w, acc);
+        acc = fmaf(__uint_as_float(p.z << 16), xb.x, acc); acc = fmaf(__uint_as_float(p.z & 0xFFFF0000u), xb.y, acc);
+        acc = fmaf(__uint_as_float(p.w << 16), xb.z, acc); acc = fmaf(__uint_as_float(p.w & 0xFFFF0000u), xb.w, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((tid & 31) == 0) part[tid >> 5] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < BF16_THREADS / 32; i++) s += part[i];
+        y[row] = s;
+    }
+}
+
+// Prefill SwiGLU in place (replaces swiglu_rows_inplace, src/cuda/prefill.cu:132-151): row b of silu(G) * U, n values,
+// overwrites the first 2 n bytes of G's row b as 16-bit floats (fp16 like the reference, or bf16 for the bf16 GEMM).
+// One CTA per row: the whole result row is formed in shared memory first (2 n bytes), then copied over the row's start,
+// so no read of G can see a half written earlier.  n, ld multiples of 8; 2 n bytes of shared memory.
+template <bool BF16>
+static __global__ void __launch_bounds__(256) swiglu_rows_inplace_kernel(float* G, const float* __restrict__ U, int n, long long ld) {
+    extern __shared__ __align__(16) uint8_t row_smem[];
+    uint32_t* h2 = (uint32_t*)row_smem;
+    float* g = G + (size_t)blockIdx.x * ld;
+    const float* u = U + (size_t)blockIdx.x * ld;
+    for (int i = threadIdx.x; i < n / 2; i += 256) {
+        const float2 a = *(const float2*)(g + 2 * i), b = *(const float2*)(u + 2 * i);
+        const float h0 = a.x / (1.0f + __expf(-a.x)) * b.x, h1 = a.y / (1.0f + __expf(-a.y)) * b.y;
+        if (BF16) { const __nv_bfloat162 v = __floats2bfloat162_rn(h0, h1); h2[i] = *(const uint32_t*)&v; }
+        else { const __half2 v = __floats2half2_rn(h0, h1); h2[i] = *(const uint32_t*)&v; }
+    }
+    __syncthreads();
+    uint4* dst = (uint4*)g;
+    const uint4* src = (const uint4*)row_smem;
+    for (int i = threadIdx.x; i < n / 8; i += 256) dst[i] = src[i];
+}
+
 // ---------------------------------------------------------------------------------------------
 // Exact dequantizer: one thread per 32-weight sub-block.  Float operations are the ones of
 // dequantize_row_ref (src/quant/quant_ref.cpp:57-103, 165-225, 284-308) in the same order, each
@@ -224,6 +332,74 @@ __device__ __forceinline__ void dequant_sub(const uint8_t* b, int s, float (&y)[
                 for (int j = 0; j < 4; j++)
                     y[8 * l + 4 * hh + j] = __fmul_rn(__fmul_rn(db, (float)((gw >> (8 * j)) & 0xFF)), ((sg >> (4 * hh + j)) & 1) ? -1.f : 1.f);
             }
+        }
+    } else if (FMT == T_Q2_K) {            // src/quant/quant_ref.cpp:33-55
+        const float d = g_f16(b + 80), mn = g_f16(b + 82);
+        const int n = s >> 2, j = s & 3;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const uint32_t sc = b[2 * s + half];
+            const float dl = __fmul_rn(d, (float)(sc & 0xF)), ml = __fmul_rn(mn, (float)(sc >> 4));
+#pragma unroll
+            for (int l = 0; l < 16; l++)
+                y[16 * half + l] = __fsub_rn(__fmul_rn(dl, (float)((b[16 + 32 * n + 16 * half + l] >> (2 * j)) & 3)), ml);
+        }
+    } else if (FMT == T_IQ2_XXS || FMT == T_IQ2_XS || FMT == T_IQ2_S) {   // src/quant/quant_ref.cpp:105-168
+        const float d = g_f16(b);
+        const uint32_t a1 = FMT == T_IQ2_XXS ? g_u32a2(b + 6 + 8 * s) : 0u;
+        const uint32_t scb = FMT == T_IQ2_XXS ? 0u : b[(FMT == T_IQ2_XS ? 66 : 74) + s];
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            uint32_t code, sg;
+            float db;
+            if (FMT == T_IQ2_XXS) {
+                code = q38b_iq2xxs_codes[b[2 + 8 * s + l]];
+                const uint32_t s7 = (a1 >> (7 * l)) & 127u;
+                sg = s7 | ((uint32_t)(__popc(s7) & 1) << 7);
+                db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(a1 >> 28))), 0.25f);
+            } else if (FMT == T_IQ2_XS) {
+                const uint32_t qv = g_u16(b + 2 + 2 * (4 * s + l));
+                code = q38b_iq2xs_codes[qv & 511u];
+                const uint32_t s7 = qv >> 9;
+                sg = s7 | ((uint32_t)(__popc(s7) & 1) << 7);
+                db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)((l < 2 ? scb : scb >> 4) & 0xF))), 0.25f);
+            } else {
+                code = q38b_iq2s_codes[b[2 + 4 * s + l] | (((uint32_t)b[66 + s] << (8 - 2 * l)) & 0x300u)];
+                sg = b[34 + 4 * s + l];
+                db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)((l < 2 ? scb : scb >> 4) & 0xF))), 0.25f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint32_t lv = (code >> (2 * j)) & 3u;
+                const float g = lv == 0 ? 8.f : lv == 1 ? 25.f : 43.f;
+                y[8 * l + j] = __fmul_rn(__fmul_rn(db, g), ((sg >> j) & 1) ? -1.f : 1.f);
+            }
+        }
+    } else if (FMT == T_IQ1_S) {           // src/quant/quant_ref.cpp:227-245
+        const float d = g_f16(b);
+        const uint32_t qh = g_u16(b + 34 + 2 * s);
+        const float dl = __fmul_rn(d, (float)(2 * (int)((qh >> 12) & 7) + 1));
+        const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t code = q38b_iq1s_codes[b[2 + 4 * s + l] | (((qh >> (3 * l)) & 7u) << 8)];
+#pragma unroll
+            for (int j = 0; j < 8; j++) y[8 * l + j] = __fmul_rn(dl, __fadd_rn((float)((int)((code >> (2 * j)) & 3u) - 1), delta));
+        }
+    } else if (FMT == T_IQ1_M) {           // src/quant/quant_ref.cpp:247-283
+        const uint32_t s0 = g_u16(b + 48), s1 = g_u16(b + 50), s2 = g_u16(b + 52), s3 = g_u16(b + 54);
+        const uint32_t su = (s0 >> 12) | ((s1 >> 8) & 0x00F0u) | ((s2 >> 4) & 0x0F00u) | (s3 & 0xF000u);
+        const float d = __half2float(__ushort_as_half((unsigned short)su));
+        const uint32_t scw = (s >> 1) == 0 ? s0 : (s >> 1) == 1 ? s1 : (s >> 1) == 2 ? s2 : s3;
+        const uint32_t t = scw >> (6 * (s & 1));
+        const float dl[2] = {__fmul_rn(d, (float)(2 * (int)(t & 7) + 1)), __fmul_rn(d, (float)(2 * (int)((t >> 3) & 7) + 1))};
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t hn = (b[32 + 2 * s + (l >> 1)] >> (4 * (l & 1))) & 0xFu;
+            const uint32_t code = q38b_iq1s_codes[b[4 * s + l] | ((hn & 7u) << 8)];
+            const float delta = (hn & 8u) ? -0.125f : 0.125f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) y[8 * l + j] = __fmul_rn(dl[l >> 1], __fadd_rn((float)((int)((code >> (2 * j)) & 3u) - 1), delta));
         }
     } else if (FMT == T_IQ4_XS) {
         const float d = g_f16(b);

@@ -45,6 +45,7 @@ int ensure_kernel_smem(q38b_ctx* ctx, const void* kern, int dyn_smem_bytes, bool
 bool known_format(uint32_t t) {
     switch (t) {
         case T_Q8_0: case T_Q4_K: case T_Q5_K: case T_Q6_K: case T_IQ3_XXS: case T_IQ3_S: case T_IQ4_XS: return true;
+        case T_Q2_K: case T_IQ2_XXS: case T_IQ2_XS: case T_IQ2_S: case T_IQ1_S: case T_IQ1_M: return true;   // one-column kernel, dequantizer, prefill
         default: return false;
     }
 }
@@ -54,6 +55,7 @@ int format_alignment(uint32_t t) {
     switch (t) {
         case T_Q4_K: case T_Q5_K: return 16;
         case T_IQ4_XS: return 8;
+        case T_Q2_K: return 4;
         default: return 2;
     }
 }
@@ -67,6 +69,7 @@ struct Plan {
 // Carves the 227 KB of shared memory of one CTA: barriers | activation scales | activations | codebook |
 // reduction buffers | NGROUPS rings of n_stages stages of 16 row slots.
 int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, int nb, Plan* p) {
+    if (one_column_only((int)type)) return Q38B_ERR_UNSUPPORTED;   // no fragment builders for these formats
     const int bb = block_bytes((int)type);
     const int nsb = K / 256;
     int cb_entries = type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;
@@ -136,7 +139,8 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     return Q38B_OK;
 }
 
-constexpr int G1_WARPS = 8;
+constexpr int G1_WARPS = 8;                  // consumer warps of a CTA when two CTAs share an SM
+constexpr int G1_WARPS_ONE = 16;             // ... when a CTA has the SM to itself
 constexpr int G1_SMEM_BUDGET = 113 * 1024;   // two CTAs per SM (228 KB of shared memory per SM, 1 KB reserved per CTA)
 
 
@@ -146,6 +150,7 @@ struct Plan1 {
     int smem;
     int rows;   // rows per tile: 8, 4 or 2
     int rg;     // 1: row-group mapping (tables in static shared memory, activations staged twice)
+    int occ;    // CTAs per SM: 2 (8 consumer warps) or 1 (16 consumer warps, the whole shared memory)
 };
 
 // The row-group decoders want every row to start 8 bytes aligned: W is 16-byte aligned, so the row stride decides.
@@ -153,12 +158,14 @@ bool rowgroup_eligible(uint32_t type, size_t row_bytes, int rows) { return type 
 
 // Shared-memory carve-up of the single-column kernel: barriers | activation scales | activations | codebook |
 // per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
-int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, Plan1* p) {
+int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, int occ, Plan1* p) {
     const int bb = block_bytes((int)type);
+    const int warps = occ == 1 ? G1_WARPS_ONE : G1_WARPS;
+    p->occ = occ;
     const int nsb = K / 256;
     const int rg = ctx->rowgroup && rowgroup_eligible(type, row_bytes, G1_ROWS) ? 1 : 0;
     const int cb_entries = rg ? 0 : type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;   // row groups keep their tables in static shared memory
-    const int budget = std::min(ctx->smem_optin, G1_SMEM_BUDGET) - 128 - (rg ? RG_STATIC_BYTES : 0);
+    const int budget = (occ == 1 ? ctx->smem_optin : std::min(ctx->smem_optin, G1_SMEM_BUDGET)) - 128 - (rg ? RG_STATIC_BYTES : 0);
     Gemv1Args& a = p->a;
     p->rows = G1_ROWS;
     p->rg = rg;
@@ -170,62 +177,43 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
         if (i < n_mats) a.n_tiles += (Ms[i] + G1_ROWS - 1) / G1_ROWS;
     }
     for (int i = n_mats; i < G1_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
-    a.off_actd = 2176;   // barriers (1536 bytes), flags, ring of tile numbers
+    a.off_actd = 1664;   // barriers (1536 bytes), flags
     a.off_actq = a.off_actd + a.n_slices * 4 * 32;
     a.off_cb = a.off_actq + a.n_slices * (rg ? 4 * ACTR_BLOCK_BYTES : 1024);
     const int packed = nsb * bb;
-    a.phase_mask = ctx->line_phase ? 127 : 15;
-    const int phase_slack = a.phase_mask - 15;
     // stage shape: 8 whole rows in one bulk copy when the rows are packed and small enough, else 8 per-row copies of a
     // K-chunk of `chunk_slices` slices (bulk copies are issue-rate limited: keep each above ~2 KB)
-    const int target = 28 * 1024;
+    const int target = occ == 1 ? 40 * 1024 : 28 * 1024;
     if ((long long)row_bytes == packed && G1_ROWS * packed <= target) {
         a.contiguous = 1;
         a.chunk_slices = a.n_slices;
         a.slot_stride = packed;
-        a.stage_bytes = align_up(G1_ROWS * packed + 64 + phase_slack, 128);
+        a.stage_bytes = align_up(G1_ROWS * packed + 64, 128);
     } else {
         a.contiguous = 0;
         int cs = std::max(1, std::min(a.n_slices, (target / G1_ROWS - 32) / (4 * bb)));
         const int nch = (a.n_slices + cs - 1) / cs;
         cs = (a.n_slices + nch - 1) / nch;          // even chunks
         a.chunk_slices = cs;
-        a.slot_stride = align_up(cs * 4 * bb + 32 + phase_slack, 16);
+        a.slot_stride = align_up(cs * 4 * bb + 32, 16);
         a.stage_bytes = align_up(G1_ROWS * a.slot_stride + 64, 128);
     }
     a.n_chunks = (a.n_slices + a.chunk_slices - 1) / a.chunk_slices;
-    const int min_stages = (G1_WARPS + a.chunk_slices - 1) / a.chunk_slices + 1;
+    const int min_stages = (warps + a.chunk_slices - 1) / a.chunk_slices + 1;
     for (int rep_log2 = cb_entries ? cb1_rep_log2((int)type) : 0; rep_log2 >= (cb_entries ? cb1_rep_log2((int)type) : 0); rep_log2--) {   // the replica count is part of the format's decoder
         a.cb_rep_log2 = rep_log2;
-        a.off_sgn = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
+        a.off_sgn = a.off_cb + align_up((cb_entries * 4 << rep_log2) + 2 * code16_entries((int)type), 128);
         a.off_red = a.off_sgn + (type == T_IQ3_XXS && !rg ? KSIGN_TABLE_BYTES : 0);
         for (int stages = G1_MAX_STAGES; stages >= min_stages; stages--) {
             // tile buffers: a warp can run at most (stages + warps) units ahead of a tile that is still being finished
-            const int tb = (G1_WARPS + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;
+            const int tb = (warps + stages * a.chunk_slices + 2 * a.n_slices - 1) / a.n_slices + 1;
             if (tb > G1_MAX_TILEBUF) continue;
             a.off_stage = align_up(a.off_red + tb * a.n_slices * G1_ROWS * 4, 128);
             if (a.off_stage + stages * a.stage_bytes + align_up(3 * bb, 128) > budget) continue;
             a.n_stages = stages;
             a.n_tilebuf = tb;
             p->smem = a.off_stage + stages * a.stage_bytes + 128 + align_up(3 * bb, 128);   // granules past a ragged row end are read (and discarded)
-            // the grid and the cut of the leftover tiles (see Gemv1Args::full_rounds)
-            const int grid_max = 2 * ctx->sm_count;
-            a.full_rounds = a.n_tiles / grid_max;
-            const int rem = a.n_tiles - a.full_rounds * grid_max;
-            const int rows_per_pass = rg ? 4 : (type == T_Q4_K || type == T_Q5_K) ? 2 : 1;
-            int best_log2 = 0;
-            double best_cost = 1e30;
-            for (int lg = 0; lg <= 2 && (G1_ROWS >> lg) >= rows_per_pass && (G1_ROWS >> lg) >= 2; lg++) {
-                // sub-rounds needed, times the cost of one: its share of a tile's bytes plus what a unit costs whatever its size
-                const long long sub_rounds = (((long long)rem << lg) + grid_max - 1) / grid_max;
-                const double cost = (double)sub_rounds * (1.0 / (1 << lg) + 0.1);
-                if (cost < best_cost - 1e-9) { best_cost = cost; best_log2 = lg; }
-            }
-            if (!ctx->split_tail) best_log2 = 0;
-            a.split_log2 = best_log2;
-            a.n_sub = rem << best_log2;
-            p->grid = a.full_rounds > 0 ? grid_max : std::max(1, std::min(grid_max, a.n_sub));
-            a.n_sched = a.full_rounds * p->grid + a.n_sub;
+            p->grid = std::max(1, std::min(occ * ctx->sm_count, a.n_tiles));
             return Q38B_OK;
         }
         if (!cb_entries) break;
@@ -236,28 +224,43 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
 // Rows per tile: the largest of 8, 4, 2 that can be planned.  Measured on B200 for every shape of the benchmark pass,
 // eight rows win even where fewer rows would balance the CTAs better or let a tile be fetched by one copy: the cost per
 // (tile, slice) unit (activation loads, waits, lane reduction) outweighs both.
+// One CTA per SM (ctx->one_cta: 0 never, 1 where it was measured faster, 2 always): row groups take 16-row tiles there.
 int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, Plan1* best) {
+    const bool long_rows = q38b_row_bytes(type, K) > 6000;
+    const bool table_heavy = ctx->rowgroup && rowgroup_eligible(type, row_bytes, 8);
+    const bool one = ctx->one_cta == 2 || (ctx->one_cta == 1 && (long_rows || table_heavy));
+    if (one) {
+        const int cands1[4] = {16, 8, 4, 2};
+        for (int rows : cands1) {
+            if (rows == 16 && !(ctx->rowgroup && rowgroup_eligible(type, row_bytes, 16))) continue;
+            memset(best, 0, sizeof(*best));
+            if (plan_gemv1_rows(ctx, type, K, Ms, n_mats, row_bytes, rows, 1, best) == Q38B_OK) return Q38B_OK;
+        }
+    }
     const int cands[3] = {8, 4, 2};
     for (int rows : cands) {
         memset(best, 0, sizeof(*best));
-        if (plan_gemv1_rows(ctx, type, K, Ms, n_mats, row_bytes, rows, best) == Q38B_OK) return Q38B_OK;
+        if (plan_gemv1_rows(ctx, type, K, Ms, n_mats, row_bytes, rows, 2, best) == Q38B_OK) return Q38B_OK;
     }
     return Q38B_ERR_NOMEM;
 }
 
-template <int FMT, int ROWS, bool RG, bool A32 = false>
+template <int FMT, int ROWS, bool RG, bool A32 = false, int OCC = 2>
 int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    auto kern = gemv1_kernel<FMT, G1_WARPS, ROWS, RG, A32>;
-    const int rc = ensure_kernel_smem(ctx, (const void*)kern, G1_SMEM_BUDGET - (RG ? RG_STATIC_BYTES : 0), true);
+    constexpr int WARPS = OCC == 1 ? G1_WARPS_ONE : G1_WARPS;
+    auto kern = gemv1_kernel<FMT, WARPS, ROWS, RG, A32, OCC>;
+    const int rc = ensure_kernel_smem(ctx, (const void*)kern, (OCC == 1 ? ctx->smem_optin : G1_SMEM_BUDGET) - (RG ? RG_STATIC_BYTES : 0), true);
     if (rc != Q38B_OK) return rc;
-    Gemv1Args args = p.a;
-    // Consecutive launches take the counter pairs in turn: a launch may start while the one before it is still running
-    // (programmatic dependent launch), and a pair is zero again when the kernel that used it has finished.
-    args.sched = ctx->dynamic_tiles && ctx->d_sched ? ctx->d_sched + 2 * (ctx->sched_seq++ % Q38B_SCHED_PAIRS) : nullptr;
+    if (ctx->check_occupancy) {   // test hook: count launches whose CTAs would not be resident as often as planned
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * (1 + WARPS), (size_t)p.smem) != cudaSuccess || per_sm < OCC)
+            ctx->occupancy_shortfalls++;
+    }
+    const Gemv1Args& args = p.a;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)p.grid);
-    cfg.blockDim = dim3(32 * (1 + G1_WARPS));
+    cfg.blockDim = dim3(32 * (1 + WARPS));
     cfg.dynamicSmemBytes = (size_t)p.smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -281,14 +284,57 @@ int launch_gemv1(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
         }
     }
     if constexpr (FMT == T_IQ3_XXS) {
+        if (p.rg && p.occ == 1 && p.rows == 16) return launch_gemv1_rows<FMT, 16, true, false, 1>(ctx, p, st);
+        if (p.rg && p.occ == 1 && p.rows == 8) return launch_gemv1_rows<FMT, 8, true, false, 1>(ctx, p, st);
+        if (p.rg && p.occ == 1 && p.rows == 4) return launch_gemv1_rows<FMT, 4, true, false, 1>(ctx, p, st);
         if (p.rg && p.rows == 8) return launch_gemv1_rows<FMT, 8, true>(ctx, p, st);
         if (p.rg && p.rows == 4) return launch_gemv1_rows<FMT, 4, true>(ctx, p, st);
+    }
+    if (p.occ == 1) {
+        switch (p.rows) {
+            case 8: return launch_gemv1_rows<FMT, 8, false, false, 1>(ctx, p, st);
+            case 4: return launch_gemv1_rows<FMT, 4, false, false, 1>(ctx, p, st);
+            case 2: return launch_gemv1_rows<FMT, 2, false, false, 1>(ctx, p, st);
+            default: return Q38B_ERR_ARG;
+        }
     }
     switch (p.rows) {
         case 8: return launch_gemv1_rows<FMT, 8, false>(ctx, p, st);
         case 4: return launch_gemv1_rows<FMT, 4, false>(ctx, p, st);
         case 2: return launch_gemv1_rows<FMT, 2, false>(ctx, p, st);
         default: return Q38B_ERR_ARG;
+    }
+}
+
+// device table a format's decoders stage into shared memory (32-bit codebook words or 16-bit grid codes), or nullptr
+const uint32_t* codebook_of(const q38b_ctx* ctx, uint32_t type) {
+    switch (type) {
+        case T_IQ3_XXS: return ctx->d_cb_iq3xxs;
+        case T_IQ3_S: return ctx->d_cb_iq3s;
+        case T_IQ2_XXS: return ctx->d_code16[0];
+        case T_IQ2_XS: return ctx->d_code16[1];
+        case T_IQ2_S: return ctx->d_code16[2];
+        case T_IQ1_S: case T_IQ1_M: return ctx->d_code16[3];
+        default: return nullptr;
+    }
+}
+
+int dispatch_gemv1(q38b_ctx* ctx, uint32_t type, const Plan1& p1, cudaStream_t st) {
+    switch (type) {
+        case T_Q8_0: return launch_gemv1<T_Q8_0>(ctx, p1, st);
+        case T_Q4_K: return launch_gemv1<T_Q4_K>(ctx, p1, st);
+        case T_Q5_K: return launch_gemv1<T_Q5_K>(ctx, p1, st);
+        case T_Q6_K: return launch_gemv1<T_Q6_K>(ctx, p1, st);
+        case T_IQ3_XXS: return launch_gemv1<T_IQ3_XXS>(ctx, p1, st);
+        case T_IQ3_S: return launch_gemv1<T_IQ3_S>(ctx, p1, st);
+        case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
+        case T_Q2_K: return launch_gemv1<T_Q2_K>(ctx, p1, st);
+        case T_IQ2_XXS: return launch_gemv1<T_IQ2_XXS>(ctx, p1, st);
+        case T_IQ2_XS: return launch_gemv1<T_IQ2_XS>(ctx, p1, st);
+        case T_IQ2_S: return launch_gemv1<T_IQ2_S>(ctx, p1, st);
+        case T_IQ1_S: return launch_gemv1<T_IQ1_S>(ctx, p1, st);
+        case T_IQ1_M: return launch_gemv1<T_IQ1_M>(ctx, p1, st);
+        default: return Q38B_ERR_UNSUPPORTED;
     }
 }
 
@@ -304,6 +350,12 @@ int launch_dequant(q38b_ctx* ctx, uint32_t type, const uint8_t* W, long long rb,
         case T_IQ3_XXS: dequant_rows_kernel<T_IQ3_XXS, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
         case T_IQ3_S: dequant_rows_kernel<T_IQ3_S, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
         case T_IQ4_XS: dequant_rows_kernel<T_IQ4_XS, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_Q2_K: dequant_rows_kernel<T_Q2_K, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_IQ2_XXS: dequant_rows_kernel<T_IQ2_XXS, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_IQ2_XS: dequant_rows_kernel<T_IQ2_XS, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_IQ2_S: dequant_rows_kernel<T_IQ2_S, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_IQ1_S: dequant_rows_kernel<T_IQ1_S, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
+        case T_IQ1_M: dequant_rows_kernel<T_IQ1_M, KIND><<<blocks, 128, 0, st>>>(W, rb, K, rows, out); break;
         default: return Q38B_ERR_UNSUPPORTED;
     }
     Q38B_CUDA(ctx, cudaGetLastError());
@@ -329,18 +381,19 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
         cudaDeviceGetAttribute(&c->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
         if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         cudaMemset(c->d_status, 0, sizeof(int));
-        if (cudaMalloc(&c->d_sched, 2 * Q38B_SCHED_PAIRS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
-        cudaMemset(c->d_sched, 0, 2 * Q38B_SCHED_PAIRS * sizeof(int));
         const void *xxs = nullptr, *s = nullptr;
         if (cudaGetSymbolAddress((void**)&xxs, q38b_iq3xxs_grid) != cudaSuccess ||
             cudaGetSymbolAddress((void**)&s, q38b_iq3s_grid) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         c->d_cb_iq3xxs = (uint32_t*)xxs;
         c->d_cb_iq3s = (uint32_t*)s;
+        const void* t16[4] = {nullptr, nullptr, nullptr, nullptr};
+        if (cudaGetSymbolAddress((void**)&t16[0], q38b_iq2xxs_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[1], q38b_iq2xs_codes) != cudaSuccess ||
+            cudaGetSymbolAddress((void**)&t16[2], q38b_iq2s_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[3], q38b_iq1s_codes) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
+        for (int i = 0; i < 4; i++) c->d_code16[i] = (const uint32_t*)t16[i];
     } while (0);
     if (rc != Q38B_OK) {
         c->last_cuda = (int)cudaGetLastError();
         if (c->d_status) cudaFree(c->d_status);
-        if (c->d_sched) cudaFree(c->d_sched);
         delete c;
         return rc;
     }
@@ -351,7 +404,6 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
 void q38b_ctx_destroy(q38b_ctx* ctx) {
     if (!ctx) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
-    if (ctx->d_sched) cudaFree(ctx->d_sched);
     if (ctx->d_flags) cudaFree(ctx->d_flags);
     delete ctx;
 }
@@ -389,24 +441,18 @@ int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
     ctx->rowgroup = enabled ? 1 : 0;
     return Q38B_OK;
 }
-// Test hook: 0 lands every copy at its source's phase inside 16 bytes instead of inside a 128-byte line.
-int q38b_debug_set_line_phase(q38b_ctx* ctx, int enabled) {
-    if (!ctx) return Q38B_ERR_ARG;
-    ctx->line_phase = enabled ? 1 : 0;
+// Test hook: one CTA per SM for the one-column kernel: 0 never, 1 for the shapes it was measured faster on, 2 always.
+int q38b_debug_set_one_cta(q38b_ctx* ctx, int mode) {
+    if (!ctx || mode < 0 || mode > 2) return Q38B_ERR_ARG;
+    ctx->one_cta = mode;
     return Q38B_OK;
 }
-int q38b_debug_set_trace(q38b_ctx* ctx, void* dev_buf) { ctx->dbg_trace = dev_buf; return 0; }   // TEMP
-// Test hook: 0 deals the tiles of the one-column kernel round-robin instead of by tickets.
-int q38b_debug_set_dynamic_tiles(q38b_ctx* ctx, int enabled) {
-    if (!ctx) return Q38B_ERR_ARG;
-    ctx->dynamic_tiles = enabled ? 1 : 0;
-    return Q38B_OK;
-}
-// Test hook: 0 deals whole tiles only (no sub-tiles after the last full round of the grid).
-int q38b_debug_set_split_tail(q38b_ctx* ctx, int enabled) {
-    if (!ctx) return Q38B_ERR_ARG;
-    ctx->split_tail = enabled ? 1 : 0;
-    return Q38B_OK;
+// Test hook: enabled = 1 starts counting one-column launches whose CTAs fit an SM less often than their plan assumes;
+// returns the count so far.
+int q38b_debug_occupancy_shortfalls(q38b_ctx* ctx, int enabled) {
+    if (!ctx) return -1;
+    ctx->check_occupancy = enabled ? 1 : 0;
+    return ctx->occupancy_shortfalls;
 }
 
 int q38b_ctx_set_wait_budget_cycles(q38b_ctx* ctx, long long cycles) {
@@ -511,6 +557,45 @@ int q38b_swiglu_q8k(q38b_ctx* ctx, const float* g, const float* u, long long ld,
     return Q38B_OK;
 }
 
+int q38b_add_rmsnorm_q8k(q38b_ctx* ctx, float* x, const float* a, const float* b, const float* w, int n, long long ld, int n_rows, float eps,
+                         float* xn, void* q8k, long long q8k_stride, void* stream) {
+    if (!ctx || !x || !w || n <= 0 || n % 256 || n > 32 * 256 || ld < n || ld % 4 || n_rows < 1 || (q8k && q8k_stride < n / 256)) return Q38B_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w | (uintptr_t)xn) & 15) return Q38B_ERR_ALIGN;
+    if ((uintptr_t)q8k & 3) return Q38B_ERR_ALIGN;
+    add_rmsnorm_q8k_kernel<<<(unsigned)n_rows, (unsigned)(n / 256) * 32, 0, (cudaStream_t)stream>>>(x, a, b, w, n, ld, eps, xn, (uint8_t*)q8k,
+                                                                                                  q8k_stride);
+    Q38B_CUDA(ctx, cudaGetLastError());
+    return Q38B_OK;
+}
+
+int q38b_gemv_bf16(q38b_ctx* ctx, const void* W_bf16, int K, int N, const float* x, float* y, void* stream) {
+    if (!ctx || !W_bf16 || !x || !y || K <= 0 || K % 8 || N < 1) return Q38B_ERR_ARG;
+    if (((uintptr_t)W_bf16 & 15) || ((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
+    gemv_bf16_kernel<<<(unsigned)N, BF16_THREADS, 0, (cudaStream_t)stream>>>((const uint16_t*)W_bf16, K, N, x, y);
+    Q38B_CUDA(ctx, cudaGetLastError());
+    return Q38B_OK;
+}
+
+int q38b_swiglu_rows_inplace(q38b_ctx* ctx, float* G, const float* U, int B, int n, long long ld, int out_kind, void* stream) {
+    if (!ctx || !G || !U || B < 1 || n <= 0 || n % 8 || ld < n || ld % 4) return Q38B_ERR_ARG;
+    if (out_kind != Q38B_OUT_F16 && out_kind != Q38B_OUT_BF16) return Q38B_ERR_ARG;
+    if (((uintptr_t)G & 15) || ((uintptr_t)U & 15)) return Q38B_ERR_ALIGN;
+    const int smem = 2 * n;
+    if (smem > ctx->smem_optin) return Q38B_ERR_NOMEM;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_kind == Q38B_OUT_BF16) {
+        const int rc = ensure_kernel_smem(ctx, (const void*)swiglu_rows_inplace_kernel<true>, ctx->smem_optin, false);
+        if (rc != Q38B_OK) return rc;
+        swiglu_rows_inplace_kernel<true><<<(unsigned)B, 256, smem, st>>>(G, U, n, ld);
+    } else {
+        const int rc = ensure_kernel_smem(ctx, (const void*)swiglu_rows_inplace_kernel<false>, ctx->smem_optin, false);
+        if (rc != Q38B_OK) return rc;
+        swiglu_rows_inplace_kernel<false><<<(unsigned)B, 256, smem, st>>>(G, U, n, ld);
+    }
+    Q38B_CUDA(ctx, cudaGetLastError());
+    return Q38B_OK;
+}
+
 int q38b_gemv_q8k(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_bytes, int K, int M, const void* q8k,
                   long long q8k_stride, int nb, float* y, long long y_ld, int accumulate, void* stream) {
     return q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, K, M, q8k, q8k_stride, nb, y, y_ld, accumulate, nullptr, 0, stream);
@@ -528,7 +613,18 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     const int al = format_alignment(type);
     if (((uintptr_t)W & 15) || (row_bytes % al) || ((uintptr_t)q8k & 3) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
-    if (nb == 1 && !ctx->uniform_columns) {
+    if (one_column_only((int)type) && nb > 1) {
+        // formats that only the one-column kernel decodes: one launch per column (every column is the nb = 1 result)
+        for (int c = 0; c < nb; c++) {
+            float* peers_c[7];
+            for (int i = 0; i < n_peers; i++) peers_c[i] = y_peers[i] + (size_t)c * y_ld;
+            const int rc = q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, K, M, (const uint8_t*)q8k + (size_t)c * q8k_stride * Q8K_BYTES, q8k_stride, 1,
+                                                 y + (size_t)c * y_ld, y_ld, accumulate, peers_c, n_peers, stream);
+            if (rc != Q38B_OK) return rc;
+        }
+        return Q38B_OK;
+    }
+    if (nb == 1 && (!ctx->uniform_columns || one_column_only((int)type))) {
         // single column: the dp4a kernel (one lane per 32- or 64-weight granule)
         Plan1 p1;
         memset(&p1, 0, sizeof(p1));
@@ -544,20 +640,11 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
             g.static_weights = ctx->static_weights;
             for (int i = 0; i < n_peers; i++) g.y_peer[i] = y_peers[i];
             g.status = ctx->d_status;
-            g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+            g.codebook = codebook_of(ctx, type);
             g.K = K;
             g.M = M;
             g.accumulate = accumulate ? 1 : 0;
-            switch (type) {
-                case T_Q8_0: return launch_gemv1<T_Q8_0>(ctx, p1, st);
-                case T_Q4_K: return launch_gemv1<T_Q4_K>(ctx, p1, st);
-                case T_Q5_K: return launch_gemv1<T_Q5_K>(ctx, p1, st);
-                case T_Q6_K: return launch_gemv1<T_Q6_K>(ctx, p1, st);
-                case T_IQ3_XXS: return launch_gemv1<T_IQ3_XXS>(ctx, p1, st);
-                case T_IQ3_S: return launch_gemv1<T_IQ3_S>(ctx, p1, st);
-                case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
-                default: return Q38B_ERR_UNSUPPORTED;
-            }
+            return dispatch_gemv1(ctx, type, p1, st);
         }
     }
     // Long rows on the multi-column kernel: the staged activations (nb x K bytes) would leave almost no shared memory
@@ -586,7 +673,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     a.static_weights = ctx->static_weights;
     for (int i = 0; i < n_peers; i++) a.y_peer[i] = y_peers[i];
     a.status = ctx->d_status;
-    a.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+    a.codebook = codebook_of(ctx, type);
     a.K = K;
     a.M = M;
     a.nb = nb;
@@ -613,10 +700,19 @@ int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, s
 
 int q38b_gemvn_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                      const void* q8k, long long q8k_stride, int nb, float* const* y, const long long* y_ld, void* stream) {
-    if (!ctx || !W || !M || !y || !y_ld || !q8k || n_mats < 1 || n_mats > GEMV_MAX_MATS) return Q38B_ERR_ARG;
+    return q38b_gemvn_group_x(ctx, type, n_mats, W, row_bytes, K, M, q8k, q8k_stride, nullptr, 0, nb, y, y_ld, nullptr, 0, stream);
+}
+
+int q38b_gemvn_group_x(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                       const void* q8k, long long q8k_stride, const float* x_f32, long long x_f32_ld, int nb, float* const* y,
+                       const long long* y_ld, float* const* y_peers, int n_peers, void* stream) {
+    if (!ctx || !W || !M || !y || !y_ld || (!q8k == !x_f32) || n_mats < 1 || n_mats > GEMV_MAX_MATS) return Q38B_ERR_ARG;
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && (!y_peers || n_mats != 1))) return Q38B_ERR_ARG;
     if (!q38b_gemvn_group_plannable(ctx, type, n_mats, row_bytes, K, M, nb)) return Q38B_ERR_UNSUPPORTED;
     const int al = format_alignment(type);
-    if ((row_bytes % al) || ((uintptr_t)q8k & 3) || q8k_stride < K / 256) return Q38B_ERR_ALIGN;
+    if (row_bytes % al) return Q38B_ERR_ALIGN;
+    if (q8k && (((uintptr_t)q8k & 3) || q8k_stride < K / 256)) return Q38B_ERR_ALIGN;
+    if (x_f32 && (((uintptr_t)x_f32 & 15) || x_f32_ld < K || x_f32_ld % 4)) return Q38B_ERR_ALIGN;
     for (int i = 0; i < n_mats; i++) {
         if (!W[i] || !y[i] || M[i] < 1 || y_ld[i] < M[i]) return Q38B_ERR_ARG;
         if (((uintptr_t)W[i] & 15) || ((uintptr_t)y[i] & 3)) return Q38B_ERR_ALIGN;
@@ -639,10 +735,13 @@ int q38b_gemvn_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const
     a.row_bytes = (long long)row_bytes;
     a.xq = (const uint8_t*)q8k;
     a.x_stride = q8k_stride;
-    a.n_peers = 0;
+    a.x_f32 = x_f32;
+    a.x_f32_ld = x_f32_ld;
+    a.n_peers = n_peers;
+    for (int i = 0; i < n_peers; i++) a.y_peer[i] = y_peers[i];
     a.static_weights = ctx->static_weights;
     a.status = ctx->d_status;
-    a.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+    a.codebook = codebook_of(ctx, type);
     a.K = K;
     a.nb = nb;
     a.accumulate = 0;
@@ -665,15 +764,17 @@ int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, si
     return plan_gemv1(ctx, type, K, M, n_mats, row_bytes, &p1) == Q38B_OK;
 }
 
-// Test hook: rows per tile the one-column kernel would use on a 148-SM device (0: the shape does not fit it).
-int q38b_debug_gemv1_rows(uint32_t type, int K, int M, size_t row_bytes, int rowgroup) {
+// Test hook: the one-column kernel's plan on a 148-SM device as CTAs per SM * 100000 + one-copy tiles * 10000 + rows per
+// tile * 100 + stages (0: the shape does not fit it).
+int q38b_debug_gemv1_rows(uint32_t type, int K, int M, size_t row_bytes, int rowgroup, int one_cta) {
     q38b_ctx ctx;
     ctx.sm_count = 148;
     ctx.smem_optin = 232448;
     ctx.rowgroup = rowgroup;
+    ctx.one_cta = one_cta;
     Plan1 p1;
     if (!known_format(type) || K <= 0 || K % 256 || plan_gemv1(&ctx, type, K, &M, 1, row_bytes, &p1) != Q38B_OK) return 0;
-    return p1.rows * 100 + p1.a.n_stages;
+    return p1.occ * 100000 + p1.a.contiguous * 10000 + p1.rows * 100 + p1.a.n_stages;
 }
 
 int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
@@ -683,6 +784,13 @@ int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const*
 
 int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                           const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream) {
+    return q38b_gemv_group_swiglu(ctx, type, n_mats, W, row_bytes, K, M, q8k, x_f32, y, y_peers, n_peers, nullptr, nullptr, stream);
+}
+
+int q38b_gemv_group_swiglu(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                           const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers,
+                           unsigned* sw_counters, void* sw_q8k, void* stream) {
+    if (sw_counters && (!sw_q8k || n_mats != 2 || n_peers != 0 || M[0] != M[1] || M[0] % 256 || ((uintptr_t)sw_q8k & 3))) return Q38B_ERR_ARG;
     if (!ctx || !W || !M || !y || n_mats < 1 || n_mats > G1_MAX_MATS || (!q8k == !x_f32)) return Q38B_ERR_ARG;
     if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return Q38B_ERR_ARG;
     for (int i = 0; i < n_mats * n_peers; i++) if (!y_peers[i] || ((uintptr_t)y_peers[i] & 3)) return Q38B_ERR_ARG;
@@ -711,26 +819,18 @@ int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* 
     g.xq = (const uint8_t*)q8k;
     g.x_f32 = x_f32;
     g.sync = take_pending_sync(ctx);
-    g.trace = (unsigned long long*)ctx->dbg_trace;
+    g.sw_counters = sw_counters;
+    g.sw_q8k = (uint8_t*)sw_q8k;
     g.n_peers = n_peers;
     for (int i = 0; i < n_mats; i++)
         for (int pr = 0; pr < n_peers; pr++) (i == 0 ? g.y_peer[pr] : g.y_peer_more[i - 1][pr]) = y_peers[i * n_peers + pr];
     g.static_weights = ctx->static_weights;
     g.status = ctx->d_status;
-    g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+    g.codebook = codebook_of(ctx, type);
     g.K = K;
     g.accumulate = 0;
     cudaStream_t st = (cudaStream_t)stream;
-    switch (type) {
-        case T_Q8_0: return launch_gemv1<T_Q8_0>(ctx, p1, st);
-        case T_Q4_K: return launch_gemv1<T_Q4_K>(ctx, p1, st);
-        case T_Q5_K: return launch_gemv1<T_Q5_K>(ctx, p1, st);
-        case T_Q6_K: return launch_gemv1<T_Q6_K>(ctx, p1, st);
-        case T_IQ3_XXS: return launch_gemv1<T_IQ3_XXS>(ctx, p1, st);
-        case T_IQ3_S: return launch_gemv1<T_IQ3_S>(ctx, p1, st);
-        case T_IQ4_XS: return launch_gemv1<T_IQ4_XS>(ctx, p1, st);
-        default: return Q38B_ERR_UNSUPPORTED;
-    }
+    return dispatch_gemv1(ctx, type, p1, st);
 }
 
 int q38b_quantize_act_q8(q38b_ctx* ctx, const float* x, int K, int n_rows, int8_t* q, float* d, float* s, void* stream) {
@@ -752,8 +852,9 @@ int q38b_gemv_act_q8(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_byt
     if (((uintptr_t)W & 15) || (row_bytes % al) || ((uintptr_t)q & 3) || (act_ld & 3) || ((uintptr_t)d & 3) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
     // One launch of the one-column kernel per column: every column is the single-column result by construction (the
     // promise of src/cuda/gemv.cuh:31-34 of the reference), at nb times the cost of one column.
-    const int saved_rg = ctx->rowgroup;
+    const int saved_rg = ctx->rowgroup, saved_one = ctx->one_cta;
     ctx->rowgroup = 0;
+    ctx->one_cta = 0;
     int rc = Q38B_OK;
     for (int c = 0; c < nb && rc == Q38B_OK; c++) {
         Plan1 p1;
@@ -769,23 +870,15 @@ int q38b_gemv_act_q8(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_byt
         g.n_peers = 0;
         g.static_weights = ctx->static_weights;
         g.status = ctx->d_status;
-        g.codebook = type == T_IQ3_XXS ? ctx->d_cb_iq3xxs : type == T_IQ3_S ? ctx->d_cb_iq3s : nullptr;
+        g.codebook = codebook_of(ctx, type);
         g.K = K;
         g.M = M;
         g.accumulate = accumulate ? 1 : 0;
         cudaStream_t st = (cudaStream_t)stream;
-        switch (type) {
-            case T_Q8_0: rc = launch_gemv1<T_Q8_0>(ctx, p1, st); break;
-            case T_Q4_K: rc = launch_gemv1<T_Q4_K>(ctx, p1, st); break;
-            case T_Q5_K: rc = launch_gemv1<T_Q5_K>(ctx, p1, st); break;
-            case T_Q6_K: rc = launch_gemv1<T_Q6_K>(ctx, p1, st); break;
-            case T_IQ3_XXS: rc = launch_gemv1<T_IQ3_XXS>(ctx, p1, st); break;
-            case T_IQ3_S: rc = launch_gemv1<T_IQ3_S>(ctx, p1, st); break;
-            case T_IQ4_XS: rc = launch_gemv1<T_IQ4_XS>(ctx, p1, st); break;
-            default: rc = Q38B_ERR_UNSUPPORTED;
-        }
+        rc = dispatch_gemv1(ctx, type, p1, st);
     }
     ctx->rowgroup = saved_rg;
+    ctx->one_cta = saved_one;
     return rc;
 }
 

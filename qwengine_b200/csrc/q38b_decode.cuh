@@ -34,7 +34,9 @@
 namespace q38b {
 
 // ggml type ids (the reference keeps them verbatim: include/q38rt/q38rt_types.h:36-67)
-enum : int { T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ3_XXS = 18, T_IQ3_S = 21, T_IQ4_XS = 23 };
+enum : int { T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ3_XXS = 18, T_IQ3_S = 21, T_IQ4_XS = 23,
+              // one-column kernel, dequantizer and prefill GEMM only (several columns run one after the other):
+              T_Q2_K = 10, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ1_S = 19, T_IQ2_S = 22, T_IQ1_M = 29 };
 
 #if !defined(__CUDA_ARCH__)
 // Host emulation hooks (defined by the CPU unit test): current lane, warp-wide mma and shuffle.
@@ -479,11 +481,32 @@ template <> struct Unit<T_Q8_0> {
     }
 };
 
+// The reference's other six formats (block layouts: src/quant/quant_formats.h:92,97-99,102-103): sizes only here; their
+// decoders are the granule decoders of q38b_decode1.cuh and the exact dequantizer of q38b_act.cuh.  Their grids hold eight
+// values out of three levels per entry and are kept as eight 2-bit level indices (codebooks.inc): CODE16_ENTRIES.
+template <> struct Unit<T_Q2_K> { static constexpr int BLOCK_BYTES = 84, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 0; };
+template <> struct Unit<T_IQ2_XXS> { static constexpr int BLOCK_BYTES = 66, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 256; };
+template <> struct Unit<T_IQ2_XS> { static constexpr int BLOCK_BYTES = 74, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 512; };
+template <> struct Unit<T_IQ2_S> { static constexpr int BLOCK_BYTES = 82, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 1024; };
+template <> struct Unit<T_IQ1_S> { static constexpr int BLOCK_BYTES = 50, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 2048; };
+template <> struct Unit<T_IQ1_M> { static constexpr int BLOCK_BYTES = 56, CODEBOOK_ENTRIES = 0, CODE16_ENTRIES = 2048; };
+
+// 16-bit grid codes a format keeps in shared memory (0 for the formats without such a table)
+Q38B_HD constexpr int code16_entries(int fmt) {
+    return fmt == T_IQ2_XXS ? 256 : fmt == T_IQ2_XS ? 512 : fmt == T_IQ2_S ? 1024 : (fmt == T_IQ1_S || fmt == T_IQ1_M) ? 2048 : 0;
+}
+// formats that only the one-column kernel decodes
+Q38B_HD constexpr bool one_column_only(int fmt) {
+    return fmt == T_Q2_K || fmt == T_IQ2_XXS || fmt == T_IQ2_XS || fmt == T_IQ2_S || fmt == T_IQ1_S || fmt == T_IQ1_M;
+}
+
 // bytes of one 256-weight super-block
 Q38B_HD int block_bytes(int fmt) {
     switch (fmt) {
         case T_Q8_0: return 272; case T_Q4_K: return 144; case T_Q5_K: return 176; case T_Q6_K: return 210;
-        case T_IQ3_XXS: return 98; case T_IQ3_S: return 110; case T_IQ4_XS: return 136; default: return 0;
+        case T_IQ3_XXS: return 98; case T_IQ3_S: return 110; case T_IQ4_XS: return 136;
+        case T_Q2_K: return 84; case T_IQ2_XXS: return 66; case T_IQ2_XS: return 74; case T_IQ2_S: return 82;
+        case T_IQ1_S: return 50; case T_IQ1_M: return 56; default: return 0;
     }
 }
 

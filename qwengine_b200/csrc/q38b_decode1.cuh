@@ -114,7 +114,7 @@ Q38B_HD uint32_t byte_x128(uint32_t w, int k) { return (k == 0 ? (w << 7) : (w >
 Q38B_HD uint32_t byte_x64(uint32_t w, int k) { return (k == 0 ? (w << 6) : (w >> (8 * k - 6))) & 0x3FC0u; }
 // replicas of the single-column kernels' shared-memory codebooks: IQ3_XXS (256 entries) 32, every lane its own bank;
 // IQ3_S (512 entries) 16, lanes l and l + 16 share a replica (32 KB instead of 64)
-Q38B_HD constexpr int cb1_rep_log2(int fmt) { return fmt == T_IQ3_S ? 4 : 5; }
+Q38B_HD constexpr int cb1_rep_log2(int fmt) { return fmt == T_IQ3_S ? 4 : fmt == T_IQ3_XXS ? 5 : 0; }
 
 // what a lane needs from the activations for one slice
 template <int NWORDS> struct ActRegs {
@@ -410,6 +410,180 @@ template <> struct Gran<T_Q8_0> {
             prev = next;
         }
         return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * (float)dot;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// IQ2_XXS, IQ2_XS, IQ2_S, IQ1_S, IQ1_M, Q2_K (integer sums of src/cpu/cpu_kernels.cpp:191-349, 435-477).  The grids of
+// the i-quants hold eight values out of three levels per entry; shared memory keeps them as 16-bit codes (eight 2-bit
+// level indices, one copy: cb.lane_base points at it) and PRMT expands four indices into four bytes from a register.
+// ---------------------------------------------------------------------------------------------------------------
+// 8 bits = four 2-bit indices -> PRMT selector with index i in nibble i
+Q38B_HD uint32_t sel_from_codes(uint32_t x) {
+    const uint32_t t = (x | (x << 4)) & 0x0F0Fu;
+    return (t | (t << 2)) & 0x3333u;
+}
+Q38B_HD uint32_t iq2_bytes(uint32_t code8) { return prmt(0x002B1908u, 0u, sel_from_codes(code8)); }      // levels 8, 25, 43
+// 8 * {-1, 0, 1} + 1 = -7, 1, 9 and 8 * {-1, 0, 1} - 1 = -9, -1, 7 as int8
+Q38B_HD uint32_t iq1_bytes(uint32_t code8, bool minus) { return prmt(minus ? 0x0007FFF7u : 0x000901F9u, 0u, sel_from_codes(code8)); }
+Q38B_HD uint32_t ksign_byte(uint32_t s7) { return s7 | ((uint32_t)(popc(s7) & 1) << 7); }
+Q38B_HD uint32_t code16(const Codebook1& cb, uint32_t idx) { return sp_ld16(cb.lane_base + (int)(2u * idx)); }
+
+// 8 signed weights of one grid entry against two activation words: P += |g| . q, N += (negative |g|) . q
+Q38B_HD void iq2_group(uint32_t code, uint32_t sign8, uint32_t q0, uint32_t q1, int& P, int& N) {
+    const uint32_t g0 = iq2_bytes(code & 0xFFu), g1 = iq2_bytes(code >> 8);
+    P = dp4a_us(g0, q0, P);
+    P = dp4a_us(g1, q1, P);
+    N = dp4a_us(g0 & sign_mask4(sign8 & 0xFu), q0, N);
+    N = dp4a_us(g1 & sign_mask4(sign8 >> 4), q1, N);
+}
+
+template <int FMT> struct GranPlain {   // the common activation side: one 32-weight sub-block per lane
+    static constexpr int WORDS = 8, LANES_PER_ROW = 32;
+    using Acts = ActRegs<WORDS>;
+    template <bool A32>
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
+    }
+};
+
+template <> struct Gran<T_IQ2_XXS> : GranPlain<T_IQ2_XXS> {
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 66 * (lane >> 3);
+        const int ib = lane & 7;
+        uint32_t a0, a1;
+        sp_ld8b_a2(p + (2 + 8 * ib), sp_low2(p) ^ 2u, a0, a1);
+        int P = 0, N = 0;
+#pragma unroll
+        for (int l = 0; l < 4; l++)
+            iq2_group(code16(cb, (a0 >> (8 * l)) & 0xFFu), ksign_byte((a1 >> (7 * l)) & 127u), a.q[2 * l], a.q[2 * l + 1], P, N);
+        const int sumi = (int)(2u * (a1 >> 28) + 1u) * (P - 2 * N);
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * 0.125f * (float)sumi;
+    }
+};
+
+template <> struct Gran<T_IQ2_XS> : GranPlain<T_IQ2_XS> {
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 74 * (lane >> 3);
+        const int ib = lane & 7;
+        uint32_t w[2];
+        sp_ld8b_a2(p + (2 + 8 * ib), sp_low2(p) ^ 2u, w[0], w[1]);
+        const uint32_t sc = sp_ld8(p, 66 + ib);
+        int P[2] = {0, 0}, N[2] = {0, 0};
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t qv = (w[l >> 1] >> (16 * (l & 1))) & 0xFFFFu;
+            iq2_group(code16(cb, qv & 511u), ksign_byte(qv >> 9), a.q[2 * l], a.q[2 * l + 1], P[l >> 1], N[l >> 1]);
+        }
+        const int sumi = (int)(2u * (sc & 0xFu) + 1u) * (P[0] - 2 * N[0]) + (int)(2u * (sc >> 4) + 1u) * (P[1] - 2 * N[1]);
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * 0.125f * (float)sumi;
+    }
+};
+
+template <> struct Gran<T_IQ2_S> : GranPlain<T_IQ2_S> {
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 82 * (lane >> 3);
+        const int ib = lane & 7;
+        const uint32_t qs = sp_ld16(p, 2 + 4 * ib) | (sp_ld16(p, 4 + 4 * ib) << 16);
+        const uint32_t sg = sp_ld16(p, 34 + 4 * ib) | (sp_ld16(p, 36 + 4 * ib) << 16);
+        const uint32_t qh = sp_ld8(p, 66 + ib), sc = sp_ld8(p, 74 + ib);
+        int P[2] = {0, 0}, N[2] = {0, 0};
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | ((qh << (8 - 2 * l)) & 0x300u);
+            iq2_group(code16(cb, idx), (sg >> (8 * l)) & 0xFFu, a.q[2 * l], a.q[2 * l + 1], P[l >> 1], N[l >> 1]);
+        }
+        const int sumi = (int)(2u * (sc & 0xFu) + 1u) * (P[0] - 2 * N[0]) + (int)(2u * (sc >> 4) + 1u) * (P[1] - 2 * N[1]);
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * 0.125f * (float)sumi;
+    }
+};
+
+template <> struct Gran<T_IQ1_S> : GranPlain<T_IQ1_S> {
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 50 * (lane >> 3);
+        const int ib = lane & 7;
+        const uint32_t qs = sp_ld16(p, 2 + 4 * ib) | (sp_ld16(p, 4 + 4 * ib) << 16);
+        const uint32_t qh = sp_ld16(p, 34 + 2 * ib);
+        const bool minus = (qh & 0x8000u) != 0;
+        int S = 0;
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t code = code16(cb, ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8));
+            S = dp4a_ss(iq1_bytes(code & 0xFFu, minus), a.q[2 * l], S);
+            S = dp4a_ss(iq1_bytes(code >> 8, minus), a.q[2 * l + 1], S);
+        }
+        const int sumi = (int)(2u * ((qh >> 12) & 7u) + 1u) * S;
+        return fp16_bits_to_float(sp_ld16(p, 0)) * a.dx * 0.125f * (float)sumi;
+    }
+};
+
+template <> struct Gran<T_IQ1_M> : GranPlain<T_IQ1_M> {
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1& cb, int lane) {
+        const SP p = row + 56 * (lane >> 3);
+        const int ib = lane & 7;
+        const uint32_t qs = sp_ld16(p, 4 * ib) | (sp_ld16(p, 4 * ib + 2) << 16);
+        const uint32_t qh = sp_ld16(p, 32 + 2 * ib);                 // nibble l: 3 index bits and the delta sign of group l
+        const uint32_t s0 = sp_ld16(p, 48), s1 = sp_ld16(p, 50), s2 = sp_ld16(p, 52), s3 = sp_ld16(p, 54);
+        const uint32_t su = (s0 >> 12) | ((s1 >> 8) & 0x00F0u) | ((s2 >> 4) & 0x0F00u) | (s3 & 0xF000u);   // the scattered fp16 super-scale
+        const uint32_t scw = (ib >> 1) == 0 ? s0 : (ib >> 1) == 1 ? s1 : (ib >> 1) == 2 ? s2 : s3;
+        const uint32_t t = scw >> (6 * (ib & 1));
+        int S[2] = {0, 0};
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t hn = (qh >> (4 * l)) & 0xFu;
+            const uint32_t code = code16(cb, ((qs >> (8 * l)) & 0xFFu) | ((hn & 7u) << 8));
+            const bool minus = (hn & 8u) != 0;
+            S[l >> 1] = dp4a_ss(iq1_bytes(code & 0xFFu, minus), a.q[2 * l], S[l >> 1]);
+            S[l >> 1] = dp4a_ss(iq1_bytes(code >> 8, minus), a.q[2 * l + 1], S[l >> 1]);
+        }
+        const int sumi = (int)(2u * (t & 7u) + 1u) * S[0] + (int)(2u * ((t >> 3) & 7u) + 1u) * S[1];
+        return fp16_bits_to_float(su) * a.dx * 0.125f * (float)sumi;
+    }
+};
+
+// Q2_K: 84 bytes = scales[16] (low nibble scale, high nibble min, per 16 weights) | qs[64] | fp16 d | fp16 dmin; sub-block
+// 4n + j of a super-block = bits 2j, 2j+1 of the 32 bytes qs[32n ..]; w = d * sc * q - dmin * m.  Rows must be 4-byte
+// aligned.  bs0 / bs1: sums of the activations of the sub-block's two halves (the Q8_K bsums), from the int8 values.
+template <> struct Gran<T_Q2_K> {
+    static constexpr int WORDS = 8, LANES_PER_ROW = 32;
+    struct Acts { uint32_t q[8]; float dx; int bs0, bs1; };
+    template <bool A32>
+    static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
+        uint32_t v[4];
+        sp_ld128(aq, 32 * lane, v);
+        a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
+        sp_ld128(aq, 32 * lane + 16, v);
+        a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
+        a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
+        a.bs0 = 0; a.bs1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) { a.bs0 = dp4a_ss(0x01010101u, a.q[i], a.bs0); a.bs1 = dp4a_ss(0x01010101u, a.q[4 + i], a.bs1); }
+    }
+    template <bool A32>
+    static Q38B_HD float dot(SP row, const Acts& a, const Codebook1&, int lane) {
+        const SP p = row + 84 * (lane >> 3);
+        const int ib = lane & 7, n = ib >> 2, j = ib & 3;
+        int S0 = 0, S1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            S0 = dp4a_us((sp_ld32(p, 16 + 32 * n + 4 * i) >> (2 * j)) & 0x03030303u, a.q[i], S0);
+            S1 = dp4a_us((sp_ld32(p, 32 + 32 * n + 4 * i) >> (2 * j)) & 0x03030303u, a.q[4 + i], S1);
+        }
+        const uint32_t sc = sp_ld16(p, 2 * ib);                      // scale bytes of the two 16-weight groups
+        const int sumi = (int)(sc & 0xFu) * S0 + (int)((sc >> 8) & 0xFu) * S1;
+        const int msum = (int)((sc >> 4) & 0xFu) * a.bs0 + (int)(sc >> 12) * a.bs1;
+        const uint32_t dd = sp_ld32(p, 80);
+        return fp16_bits_to_float(dd & 0xFFFFu) * a.dx * (float)sumi - fp16_bits_to_float(dd >> 16) * a.dx * (float)msum;
     }
 };
 

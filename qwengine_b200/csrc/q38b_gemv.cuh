@@ -14,6 +14,7 @@
 // Every column is computed by the same instructions whatever nb is, so column c of an nb-column call is
 // bit-identical to a 1-column call on that column (the reference promises the same: src/cuda/gemv.cuh:31-34).
 #pragma once
+#include "q38b_act.cuh"
 #include "q38b_decode.cuh"
 #include "q38b_pipe.cuh"
 
@@ -37,8 +38,10 @@ struct GemvArgs {
     int tile_start[GEMV_MAX_MATS];   // first tile of each matrix (unused ones = n_tiles)
     const uint8_t* W;        // [M] rows, row_bytes apart, GGUF blocks
     long long row_bytes;
-    const uint8_t* xq;       // Q8_K blocks; column c starts at xq + c * x_stride * 292
+    const uint8_t* xq;       // Q8_K blocks; column c starts at xq + c * x_stride * 292; or nullptr:
     long long x_stride;      // blocks between columns
+    const float* x_f32;      // then the columns as floats (column c at x_f32 + c * x_f32_ld), quantized to Q8_K by every CTA in its prologue
+    long long x_f32_ld;
     float* y;                // y[c * y_ld + r]
     long long y_ld;
     float* y_peer[7];        // the same output position in the other GPUs' buffers (peer stores), n_peers used
@@ -154,6 +157,52 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         for (int i = ctid; i < CBN * rep; i += NGROUPS * GROUP_THREADS) cbw[i] = a.codebook[i >> a.cb_rep_log2];
     }
     pdl_wait_prior();   // activations come from the previous kernel of the stream
+    if (a.x_f32) {
+        // quantize the columns here (every CTA, the arithmetic of quantize_q8k_kernel): one warp per 256 values, the
+        // loads of three blocks going out together
+        constexpr int QB = 3, NW = NGROUPS * GROUP_WARPS;
+        const int cwarp = ctid >> 5;
+        const int n_blocks = a.nb * a.nsb;
+        for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS)
+            if ((i & 7) >= a.nb) actd[i] = 0.0f;
+        for (int b0 = cwarp; b0 < n_blocks; b0 += QB * NW) {
+            float4 lo4[QB], hi4[QB];
+#pragma unroll
+            for (int j = 0; j < QB; j++) {
+                const int b = b0 + j * NW;
+                lo4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                hi4[j] = lo4[j];
+                if (b < n_blocks) {
+                    const int c = b / a.nsb, sb = b - c * a.nsb;
+                    const float* src = a.x_f32 + (size_t)c * a.x_f32_ld + (size_t)sb * 256 + 8 * lane;
+                    lo4[j] = *(const float4*)src;
+                    hi4[j] = *(const float4*)(src + 4);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < QB; j++) {
+                const int b = b0 + j * NW;
+                if (b >= n_blocks) continue;
+                const int c = b / a.nsb, sb = b - c * a.nsb;
+                const float v[8] = {lo4[j].x, lo4[j].y, lo4[j].z, lo4[j].w, hi4[j].x, hi4[j].y, hi4[j].z, hi4[j].w};
+                uint32_t w0, w1;
+                int s8;
+                float d;
+                q8k_block_core(v, w0, w1, s8, d);
+                if (lane == 0) actd[sb * 8 + c] = d;
+                uint8_t* dst = actq + (size_t)c * a.K + sb * 256;
+                if (FMT == T_IQ4_XS) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int k = 8 * lane + e;
+                        dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
+                    }
+                } else {
+                    *(uint2*)(dst + 8 * lane) = make_uint2(w0, w1);
+                }
+            }
+        }
+    } else {
     for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS) {
         const int sb = i >> 3, c = i & 7;
         actd[i] = c < a.nb ? *(const float*)(a.xq + ((size_t)c * a.x_stride + sb) * Q8K_BYTES) : 0.0f;
@@ -172,6 +221,7 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         } else {
             *(uint32_t*)(dst + 4 * wi) = v;
         }
+    }
     }
     named_bar_sync(15, NGROUPS * GROUP_THREADS);
 

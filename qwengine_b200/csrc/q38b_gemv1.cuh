@@ -35,6 +35,12 @@ struct Gemv1Args {
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     float* y_peer_more[G1_MAX_MATS - 1][7];   // the same for matrices 1 and 2
     PeerSync sync;          // cross-GPU barrier before the column is read (the peers pushed parts of it), n = 0: none
+    // SwiGLU in the epilogue (sw_counters != nullptr): matrices 0 and 1 are the gate and up projections, M rows each
+    // (a multiple of 256).  The warp that completes a tile adds its rows to the counter of their 256-row block; the one
+    // that brings a block to 512 rows (gate and up complete) computes h = silu(g) * u for it and writes its Q8_K block
+    // to sw_q8k, then zeroes the counter: no SwiGLU kernel between this launch and the down projection.
+    unsigned* sw_counters;
+    uint8_t* sw_q8k;
     int n_peers;
     int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;
@@ -43,19 +49,6 @@ struct Gemv1Args {
     int nsb;                // super-blocks per row
     int n_slices;           // ceil(nsb / 4)
     int n_tiles;            // tiles of all matrices
-    // The tiles are dealt to the CTAs round-robin; the ones left over after the last full round of the grid are cut into
-    // `1 << split_log2` sub-tiles of fewer rows, dealt round-robin again, so that the last round costs every CTA a
-    // fraction of a tile instead of a whole tile for some and nothing for the others.
-    int full_rounds;        // rounds in which every CTA takes a whole tile
-    int n_sub;              // sub-tiles after them: (n_tiles - full_rounds * grid) << split_log2
-    int split_log2;
-    // Dynamic tile scheduling: sched[0] = tickets handed out beyond each CTA's first tile, sched[1] = CTAs that have
-    // fetched their last ticket (the last one of them zeroes both for the next launch that uses this pair).  nullptr:
-    // tiles are dealt round-robin (CTA b takes b, b + grid, ...).
-    int* sched;
-    int n_sched;            // tiles and sub-tiles in all: full_rounds * grid + n_sub
-    unsigned long long* trace;   // TEMP timing probe: 8 words per CTA
-    int phase_mask;         // 127: a copy lands at the phase of its source inside a 128-byte line (one shared-memory line per line read); 15: inside 16 bytes
     int n_stages;
     int chunk_slices;       // slices per stage (K-chunk); n_chunks = ceil(n_slices / chunk_slices)
     int n_chunks;
@@ -70,47 +63,21 @@ struct Gemv1Args {
 // One block of the slice for every row pass of a row-group tile (B is a template argument: the alignment of the block's
 // fields follows from it).
 template <int FMT, int B, int NPASS>
-__device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int npass, int s, SP act_block, SP actd_block, const TablesR& tabs, float (&acc)[NPASS]) {
+__device__ __forceinline__ void rowgroup_block(const SP (&rowp)[NPASS], int s, SP act_block, SP actd_block, const TablesR& tabs, float (&acc)[NPASS]) {
     ActsR ar;
     GranR<FMT>::load_acts(ar, act_block, actd_block, s);
 #pragma unroll
-    for (int ps = 0; ps < NPASS; ps++)
-        if (ps < npass) acc[ps] += GranR<FMT>::template dot<B>(rowp[ps], s, ar, tabs);
+    for (int ps = 0; ps < NPASS; ps++) acc[ps] += GranR<FMT>::template dot<B>(rowp[ps], s, ar, tabs);
 }
 
-// Tile number `ti` of this CTA: the matrix, the first row inside it and the number of rows (fewer for a sub-tile).
-struct TileRef { int mi, row0, nrows; };
+// Tile `gtile` of the launch's sequence (matrix 0's tiles, then matrix 1's, ...): the matrix and the first row inside it.
+struct TileRef { int mi, row0; };
 template <int ROWS>
-__device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int u) {   // u: number of the tile or sub-tile in the launch's sequence
-    const int n_whole = a.full_rounds * (int)gridDim.x;
-    int gtile = u, sub = 0, nrows = ROWS;
-    if (u >= n_whole) {
-        const int v = u - n_whole;
-        gtile = n_whole + (v >> a.split_log2);
-        sub = v & ((1 << a.split_log2) - 1);
-        nrows = ROWS >> a.split_log2;
-    }
+__device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int gtile) {
     TileRef t;
     t.mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
-    t.row0 = (gtile - a.tile_start[t.mi]) * ROWS + sub * nrows;
-    t.nrows = nrows;
+    t.row0 = (gtile - a.tile_start[t.mi]) * ROWS;
     return t;
-}
-
-constexpr int G1_TILE_RING = 128;   // sequence numbers of this CTA's latest tiles (more than stages can be in flight)
-
-// Consumers wait until stage fill `item` has been issued, or learn that the CTA's last fill came before it.
-__device__ __forceinline__ bool wait_item_or_end(uint32_t issued_addr, uint32_t end_addr, int item, volatile int* abort_flag, int* status) {
-    const long long t0 = clock64();
-    for (;;) {
-        if (ld_acquire_shared(issued_addr) > item) return true;
-        if (ld_acquire_shared(end_addr) <= item) return false;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
-    }
-    *abort_flag = 1;
-    if (status) atomicOr(status, ST_WAIT_FULL_TIMEOUT);
-    return false;
 }
 
 // shared-memory tables of the row-group decoders (static, so that their addresses are immediates of the loads)
@@ -122,13 +89,24 @@ constexpr int RG_STATIC_BYTES = 4 * (RG_CB_WORDS + RG_SGN_WORDS);
 // RG: the row-group mapping of q38b_decode1.cuh (IQ3_XXS, rows 8 bytes aligned): lane = (row of a group of four,
 // sub-block), tables in static shared memory, activations staged in the layout of actr_pos.
 // A32: the column is given in the reference GPU path's per-32 format (ActQ8: xq = int8 values, xd32 = one scale per 32).
-template <int FMT, int NWARPS, int ROWS, bool RG, bool A32>
-__global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1Args a) {
+// OCC: CTAs per SM the kernel is built for: 2 (eight consumer warps each, half the shared memory each) or 1 (sixteen
+// consumer warps, all of it: one set of tables, deeper rings and larger tiles for long rows).
+template <int FMT, int NWARPS, int ROWS, bool RG, bool A32, int OCC>
+__global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gemv1Args a) {
     constexpr int G1_ROWS = ROWS;
-    static_assert(!RG || (FMT == T_IQ3_XXS && ROWS % 4 == 0), "row-group mapping: IQ3_XXS, tiles of 4 or 8 rows");
+    static_assert(!RG || (FMT == T_IQ3_XXS && ROWS % 4 == 0), "row-group mapping: IQ3_XXS, tiles of 4, 8 or 16 rows");
+    static_assert(RG || ROWS <= 8, "the lane-per-granule mapping reduces at most eight rows per unit");
     static_assert(!(RG && A32), "per-32 activations run on the lane-per-granule mapping");
-    __shared__ __align__(128) uint32_t rg_cb[RG ? RG_CB_WORDS : 1];
-    __shared__ __align__(128) uint32_t rg_sgn[RG ? RG_SGN_WORDS : 1];
+    // tables of the row-group decoders: static shared memory (their addresses become immediates of the loads); kernels
+    // without them have no static shared memory at all, so that two CTAs of 113 KB still fit an SM
+    uint32_t* rg_cb = nullptr;
+    uint32_t* rg_sgn = nullptr;
+    if constexpr (RG) {
+        __shared__ __align__(128) uint32_t rg_cb_store[RG_CB_WORDS];
+        __shared__ __align__(128) uint32_t rg_sgn_store[RG_SGN_WORDS];
+        rg_cb = rg_cb_store;
+        rg_sgn = rg_sgn_store;
+    }
     extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
     uint8_t* smem = smem_raw;
     uint64_t* full = (uint64_t*)smem;                        // [G1_MAX_STAGES]
@@ -136,8 +114,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     uint64_t* tbar = empty + G1_MAX_STAGES;                  // [G1_MAX_TILEBUF]
     volatile int* abort_flag = (volatile int*)(tbar + G1_MAX_TILEBUF);
     int* issued = (int*)abort_flag + 1;                      // stage fills the producer has issued so far
-    int* end_item = issued + 1;                              // fills this CTA issues in all (known once the producer ran out of tiles)
-    int* tile_seq = end_item + 1;                            // [G1_TILE_RING] sequence number of tile ti of this CTA at [ti % ring]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int BB = Unit<FMT>::BLOCK_BYTES;
     constexpr int SLICE_BYTES = 4 * BB;
@@ -145,39 +121,32 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     if (tid == 0) {
         *abort_flag = 0;
         *issued = 0;
-        *end_item = 0x7fffffff;
         for (int s = 0; s < a.n_stages; s++) { mbar_init(smem_u32(&full[s]), G1_ROWS); mbar_init(smem_u32(&empty[s]), a.chunk_slices); }
         for (int t = 0; t < a.n_tilebuf; t++) mbar_init(smem_u32(&tbar[t]), a.n_slices);
         mbar_fence_init();
     }
     __syncthreads();
     pdl_launch_dependents();
-    unsigned long long gt0 = 0;
-    if (a.trace && tid == 32) { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0)); a.trace[blockIdx.x * 8 + 0] = gt0; }
 
+    // tiles are dealt round-robin: CTA b takes tiles b, b + grid, b + 2 grid, ...
+    const int my_tiles = a.n_tiles > (int)blockIdx.x ? (a.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int n_items = my_tiles * a.n_chunks;       // stages this CTA streams
     const int packed_row = a.nsb * BB;
 
     if (warp == 0) {
         // ---------------- producer ----------------
         if (!a.static_weights) pdl_wait_prior();   // W may be the output of the kernel before this one
         if (lane < G1_ROWS) {
-            constexpr uint32_t PMASK = (1u << G1_ROWS) - 1u;     // the producing lanes
-            int ti = 0, chunk = 0, stage = 0, item = 0;
+            int ti = 0, chunk = 0, stage = 0;
             uint32_t use = 0;                      // parity of the number of earlier fills of this stage
-            // This CTA's first tile is its own number; the following ones are tickets from the launch's counter (fetched one
-            // tile ahead, so that the round trip of the atomic is off the critical path), or every grid-th tile without one.
-            int u = (int)blockIdx.x < a.n_sched ? (int)blockIdx.x : -1;
-            int ticket = 0;
-            if (a.sched && lane == 0) ticket = atomicAdd(a.sched, 1);
-            while (u >= 0) {
-                if (chunk == 0 && lane == 0) tile_seq[ti & (G1_TILE_RING - 1)] = u;
+            for (int item = 0; item < n_items; item++) {
                 const uint32_t fb = smem_u32(&full[stage]);
                 mbar_wait_bounded(smem_u32(&empty[stage]), use ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
-                const TileRef tr = tile_ref<G1_ROWS>(a, u);
+                const TileRef tr = tile_ref<G1_ROWS>(a, (int)blockIdx.x + (int)gridDim.x * ti);
                 const int mi = tr.mi, row0 = tr.row0;
                 const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
                 const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
-                const int rows_here = min(tr.nrows, Mm - row0);
+                const int rows_here = min(G1_ROWS, Mm - row0);
                 const uintptr_t safe_end = ((uintptr_t)Wm + (uintptr_t)(Mm - 1) * a.row_bytes + packed_row) & ~(uintptr_t)15;
                 uint8_t* sbase = smem + a.off_stage + (size_t)stage * a.stage_bytes;
                 // what this lane copies: the whole tile (lane 0, contiguous rows) or its own row's chunk
@@ -199,7 +168,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                     mbar_arrive(fb);
                 } else {
                     const uintptr_t lo = src & ~(uintptr_t)15;
-                    slot += lo & (uintptr_t)(a.phase_mask & ~15);
                     uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
                     if (hi > safe_end) {   // the tensor's last bytes do not fill a 16-byte unit: plain loads
                         hi = safe_end > lo ? safe_end : lo;
@@ -214,36 +182,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
                         mbar_arrive(fb);
                     }
                 }
+                if (++chunk == a.n_chunks) { chunk = 0; ti++; }
                 if (++stage == a.n_stages) { stage = 0; use ^= 1u; }
-                __syncwarp(PMASK);
-                item++;
-                if (lane == 0) st_release_shared(smem_u32(issued), item);
-                if (++chunk == a.n_chunks) {   // next tile
-                    chunk = 0;
-                    ti++;
-                    if (a.sched) {
-                        int nu = 0;
-                        if (lane == 0) {
-                            nu = ticket + (int)gridDim.x;
-                            if (nu < a.n_sched) ticket = atomicAdd(a.sched, 1);
-                        }
-                        u = __shfl_sync(PMASK, nu, 0);
-                    } else {
-                        u += (int)gridDim.x;
-                    }
-                    if (u >= a.n_sched) u = -1;
-                }
-            }
-            if (lane == 0) {
-                st_release_shared(smem_u32(end_item), item);
-                if (a.sched) {   // the last CTA to get here leaves the pair of counters at zero for its next user
-                    __threadfence();
-                    if (atomicAdd(a.sched + 1, 1) == (int)gridDim.x - 1) {
-                        a.sched[0] = 0;
-                        a.sched[1] = 0;
-                        __threadfence();
-                    }
-                }
+                __syncwarp((1u << G1_ROWS) - 1u);
+                if (lane == 0) st_release_shared(smem_u32(issued), item + 1);
             }
         }
         return;
@@ -273,6 +215,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     } else if (CBN > 0) {
         const int rep = 1 << a.cb_rep_log2;
         for (int i = ctid; i < CBN * rep; i += NWARPS * 32) cbw[i] = a.codebook[i >> a.cb_rep_log2];
+    } else if (code16_entries(FMT) > 0) {   // the grid as 16-bit codes, one copy (two entries per word)
+        for (int i = ctid; i < code16_entries(FMT) / 2; i += NWARPS * 32) cbw[i] = a.codebook[i];
     }
     if (FMT == T_IQ3_XXS && !RG) {
         uint32_t* sg = (uint32_t*)(smem + a.off_sgn);
@@ -283,9 +227,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             sg[2 * i + 1] = hi;
         }
     }
-    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 1] = t; }
     pdl_wait_prior();
-    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 2] = t; }
     if (a.sync.n > 0) {
         peer_sync_wait(a.sync, blockIdx.x == 0, ctid, a.status);
         named_bar_sync(14, NWARPS * 32);
@@ -361,7 +303,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     }
     }
     named_bar_sync(15, NWARPS * 32);
-    if (a.trace && tid == 32) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 3] = t; }
 
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
     cb.lane_base = sp_from(cbw) + 4 * (lane & ((1 << cb1_rep_log2(FMT)) - 1));
@@ -375,7 +316,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     constexpr int PASSES = G1_ROWS * LPR / 32;       // row passes per stage
     const int sub = LPR == 32 ? 0 : LPR == 16 ? (lane >> 4) : (lane >> 3);   // which of the rows of a pass this lane works on
 
-    // (tile, slice) units are dealt round-robin to the warps until the producer runs out of tiles
+    const int n_units = my_tiles * a.n_slices;       // (tile, slice) units, dealt round-robin to the warps
     // The unit's (tile, slice, chunk) and the ring positions of its stage and tile buffer are stepped, never divided.
     int ti = 0, slice = cw;
     while (slice >= a.n_slices) { slice -= a.n_slices; ti++; }
@@ -386,7 +327,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
     int seen_item = -1;                              // last stage fill this warp has waited for
     const uint32_t rb32 = (uint32_t)a.row_bytes;
     const uint32_t rb_step = a.contiguous ? 0u : rb32;   // rows of a contiguous stage share the copy's low address bits
-    for (;;) {
+    for (int unit = cw; unit < n_units; unit += NWARPS) {
         const int item = ti * a.n_chunks + chunk;
         while (cur_item < item) { cur_item++; if (++stage == a.n_stages) { stage = 0; stage_par ^= 1u; } }
         while (cur_ti < ti) { cur_ti++; if (++tslot == a.n_tilebuf) { tslot = 0; tile_par ^= 1u; } }
@@ -395,12 +336,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         // phase for this one.  The producer issues a fill only after the readers of the previous use of the barrier have
         // released it, i.e. after that phase completed: once `issued` has passed `item` the parity is unambiguous.
         if (item > seen_item) {
-            if (!wait_item_or_end(smem_u32(issued), smem_u32(end_item), item, abort_flag, a.status)) break;
+            wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             mbar_wait_bounded(smem_u32(&full[stage]), stage_par, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
         }
-        if (a.trace && tid == 32 && seen_item < 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[blockIdx.x * 8 + 4] = t; }
         seen_item = item;
-        const TileRef tr = tile_ref<G1_ROWS>(a, tile_seq[ti & (G1_TILE_RING - 1)]);
+        const TileRef tr = tile_ref<G1_ROWS>(a, (int)blockIdx.x + (int)gridDim.x * ti);
         const int mi = tr.mi;
         const uint32_t w_lo = (uint32_t)(uintptr_t)(mi == 0 ? a.W : a.W_more[mi - 1]);
         const SP st = stage0_sp + (stage * a.stage_bytes + cslice * SLICE_BYTES);
@@ -418,15 +358,14 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
 #pragma unroll
             for (int ps = 0; ps < PASSES; ps++) {
                 const int r = 4 * ps + sub;
-                rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & (uint32_t)a.phase_mask));
+                rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
                 acc[ps] = 0.0f;
             }
             const int sb0 = slice * 4;
-            const int npass = (tr.nrows + 3) >> 2;   // a sub-tile has fewer rows: passes past them are skipped
-            if (sb0 + 0 < a.nsb) rowgroup_block<FMT, 0, PASSES>(rowp, npass, s, actq_sp + (sb0 + 0) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 0) * 32, tabs, acc);
-            if (sb0 + 1 < a.nsb) rowgroup_block<FMT, 1, PASSES>(rowp, npass, s, actq_sp + (sb0 + 1) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 1) * 32, tabs, acc);
-            if (sb0 + 2 < a.nsb) rowgroup_block<FMT, 2, PASSES>(rowp, npass, s, actq_sp + (sb0 + 2) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 2) * 32, tabs, acc);
-            if (sb0 + 3 < a.nsb) rowgroup_block<FMT, 3, PASSES>(rowp, npass, s, actq_sp + (sb0 + 3) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 3) * 32, tabs, acc);
+            if (sb0 + 0 < a.nsb) rowgroup_block<FMT, 0, PASSES>(rowp, s, actq_sp + (sb0 + 0) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 0) * 32, tabs, acc);
+            if (sb0 + 1 < a.nsb) rowgroup_block<FMT, 1, PASSES>(rowp, s, actq_sp + (sb0 + 1) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 1) * 32, tabs, acc);
+            if (sb0 + 2 < a.nsb) rowgroup_block<FMT, 2, PASSES>(rowp, s, actq_sp + (sb0 + 2) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 2) * 32, tabs, acc);
+            if (sb0 + 3 < a.nsb) rowgroup_block<FMT, 3, PASSES>(rowp, s, actq_sp + (sb0 + 3) * ACTR_BLOCK_BYTES, actd_sp + (sb0 + 3) * 32, tabs, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
 #pragma unroll
@@ -444,16 +383,12 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         const int gran_sb = slice * 4 + (LPR == 32 ? (lane >> 3) : ((lane & 15) >> 2));
         const bool live = gran_sb < a.nsb;
         float acc[PASSES];
-        const int npass = LPR == 32 ? tr.nrows : (tr.nrows + 1) >> 1;   // a sub-tile has fewer rows: passes past them are skipped
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
-            acc[ps] = 0.0f;
-            if (ps < npass) {
-                const int r = LPR == 32 ? ps : 2 * ps + sub;
-                const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & (uint32_t)a.phase_mask));
-                const float v = Gran<FMT>::template dot<A32>(rowp, acts, cb, lane);
-                acc[ps] = live ? v : 0.0f;
-            }
+            const int r = LPR == 32 ? ps : 2 * ps + sub;
+            const SP rowp = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
+            const float v = Gran<FMT>::template dot<A32>(rowp, acts, cb, lane);
+            acc[ps] = live ? v : 0.0f;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive_n(smem_u32(&empty[stage]), n_arr);
@@ -501,15 +436,28 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
             const int row = tr.row0 + lane;
             float* ym = mi == 0 ? a.y : a.y_more[mi - 1];
             const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
-            if (lane < tr.nrows && row < Mm) {
+            if (lane < G1_ROWS && row < Mm) {
                 const float* rs = red + (size_t)tslot * a.n_slices * G1_ROWS + lane;
                 float v = 0.0f;
                 for (int s = 0; s < a.n_slices; s++) v += rs[s * G1_ROWS];
                 const float out = a.accumulate ? ym[row] + v : v;
                 ym[row] = out;
                 for (int pr = 0; pr < a.n_peers; pr++) (mi == 0 ? a.y_peer[pr] : a.y_peer_more[mi - 1][pr])[row] = out;   // fused all-gather: push to every peer
+                if (a.sw_counters) __threadfence();   // the row is visible to whoever completes the block
             }
             __syncwarp();
+            if (a.sw_counters) {
+                const int blk = tr.row0 >> 8;
+                const int stored = max(0, min(G1_ROWS, Mm - tr.row0));
+                unsigned before = 0;
+                if (lane == 0) before = atomicAdd(a.sw_counters + blk, (unsigned)stored);
+                before = __shfl_sync(0xffffffffu, before, 0);
+                if (before + (unsigned)stored == 512u) {
+                    __threadfence();
+                    swiglu_block<true>(a.y + (size_t)blk * 256, a.y_more[0] + (size_t)blk * 256, nullptr, a.sw_q8k + (size_t)blk * 292);
+                    if (lane == 0) a.sw_counters[blk] = 0u;
+                }
+            }
         }
         slice += NWARPS;
         while (slice >= a.n_slices) { slice -= a.n_slices; ti++; }
@@ -517,7 +465,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), 2) gemv1_kernel(const Gemv1
         cslice = slice;
         while (cslice >= a.chunk_slices) { cslice -= a.chunk_slices; chunk++; }
     }
-    if (a.trace && lane == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); atomicMax(&a.trace[blockIdx.x * 8 + 5], t); }
 }
 
 }  // namespace q38b

@@ -3,8 +3,6 @@
 #include <cstddef>
 #include <cstdint>
 
-constexpr int Q38B_SCHED_PAIRS = 8;
-
 struct q38b_ctx {
     int device = 0;
     int sm_count = 0;
@@ -14,17 +12,14 @@ struct q38b_ctx {
     int pass_pdl = 1;          // programmatic dependent launch between the kernels of a recorded pass
     int static_weights = 0;    // 1: matvec producers start streaming W before the previous kernel of the stream has finished
     int rowgroup = 1;          // 0: the row-group mapping of the one-column kernel is not used (test hook q38b_debug_set_rowgroup)
-    void* dbg_trace = nullptr;   // TEMP
-    int line_phase = 1;        // one-column kernel: copies keep their source's phase inside a 128-byte line (test hook q38b_debug_set_line_phase)
-    int split_tail = 1;        // 0: the one-column kernel deals whole tiles only (test hook q38b_debug_set_split_tail)
+    int one_cta = 1;           // one-column kernel with one CTA per SM: 0 never, 1 chosen shapes, 2 always (test hook q38b_debug_set_one_cta)
+    int check_occupancy = 0, occupancy_shortfalls = 0;   // test hook q38b_debug_occupancy_shortfalls
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     long long wait_budget_cycles = 4000000000LL;   // bounded waits on other GPUs (q38b_ctx_set_wait_budget_cycles)
     int* d_status = nullptr;
-    int* d_sched = nullptr;    // Q38B_SCHED_PAIRS pairs of tile-scheduling counters (see Gemv1Args::sched), all zero between launches
-    unsigned sched_seq = 0;
-    int dynamic_tiles = 1;     // 0: tiles are dealt round-robin (test hook q38b_debug_set_dynamic_tiles)
     uint32_t* d_cb_iq3xxs = nullptr;
     uint32_t* d_cb_iq3s = nullptr;
+    const uint32_t* d_code16[4] = {};   // 16-bit grid codes of IQ2_XXS, IQ2_XS, IQ2_S, IQ1_S / IQ1_M (two per word)
     void* comm = nullptr;   // ncclComm_t when q38b_comm_init was called
     int n_ranks = 1, rank = 0;
     // peer-store gather: flags[0..7] written by the peers, [8] = this rank's barrier count
@@ -44,7 +39,17 @@ extern "C" int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int
 // q38b_gemv_group with peer stores: y_peers[i * n_peers + r] is where peer r keeps the output of matrix i
 extern "C" int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                                      const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream);
+// the same with SwiGLU in the epilogue (see Gemv1Args::sw_counters): two matrices (gate, up) of M rows, one column, one GPU;
+// sw_counters: M / 256 zeroed words that the kernel leaves zeroed; sw_q8k: M / 256 Q8_K blocks of silu(gate) * up
+extern "C" int q38b_gemv_group_swiglu(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                                      const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers,
+                                      unsigned* sw_counters, void* sw_q8k, void* stream);
 // the same for the multi-column kernel (nb columns of Q8_K blocks, q8k_stride blocks apart; y[i][c * y_ld[i] + r]); no peers
 extern "C" int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb);
+// the same with the columns given as floats (x_f32, x_f32_ld floats apart; quantized inside the kernel) instead of Q8_K
+// blocks, and, for a single matrix, with peer stores
+extern "C" int q38b_gemvn_group_x(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
+                                  const void* q8k, long long q8k_stride, const float* x_f32, long long x_f32_ld, int nb, float* const* y,
+                                  const long long* y_ld, float* const* y_peers, int n_peers, void* stream);
 extern "C" int q38b_gemvn_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                                 const void* q8k, long long q8k_stride, int nb, float* const* y, const long long* y_ld, void* stream);

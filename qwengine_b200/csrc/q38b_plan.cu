@@ -88,14 +88,17 @@ struct q38b_pass {
     float* pin_in = nullptr;
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
+    int fuse_swiglu = 1;         // single-column replays on one GPU: a SwiGLU step right behind a merged gate + up launch runs in its epilogue
+    unsigned* d_sw_counters = nullptr;   // one word per 256-row block of the widest SwiGLU step, zero between launches
+    int sw_counter_words = 0;
     int merge_steps = 1;         // replays: one launch for matvecs that share a column, quantize steps folded into single-column launches
     // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
     // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
     struct Captured {
-        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, split_tail, line_phase, dynamic_tiles;
+        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, one_cta, fuse_swiglu;
         bool operator==(const Captured& o) const {
             return n_ops == o.n_ops && peer_store == o.peer_store && merge_steps == o.merge_steps && uniform_columns == o.uniform_columns &&
-                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && split_tail == o.split_tail && line_phase == o.line_phase && dynamic_tiles == o.dynamic_tiles;
+                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && one_cta == o.one_cta && fuse_swiglu == o.fuse_swiglu;
         }
     };
     Captured captured[9] = {};
@@ -147,7 +150,7 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
 
 // One launch of the merged single-column replay: `n` matvec ops (indices into p->ops) that read one column, which comes
 // as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source of that quantize op (folded into the launch).
-struct Merged { int first_op; int n; int ops[3]; int quant; };
+struct Merged { int first_op; int n; int ops[3]; int quant; int swiglu; };   // swiglu >= 0: that SwiGLU step runs in the launch's epilogue
 
 // Which steps of a single-column replay on one GPU can share launches.  A quantize step is folded into the matvecs that
 // read its output when they follow it directly, nothing else reads that output before it is rewritten, and all of them
@@ -181,10 +184,6 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
     while (i < n) {
         int quant = -1;
         size_t g0 = i;
-        if (ops[i].kind == OP_QUANT && nb > 1) {   // several columns: the quantize step stays a kernel (each CTA would redo nb x K values)
-            i = next_real(i + 1);
-            continue;
-        }
         if (ops[i].kind == OP_QUANT) {
             const int col = ops[i].b;
             const size_t j = ranks ? i + 1 : next_real(i + 1);   // several ranks: only a matvec right after the quantize step
@@ -200,7 +199,9 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
             for (size_t k : run) {
                 if (!ok) break;
                 const Mat& m = p->mats[ops[k].a];
-                if (m.K != ops[i].n || !q38b_gemv_group_plannable(ctx, m.type, 1, m.row_bytes, m.K, &m.M)) ok = false;
+                if (m.K != ops[i].n) ok = false;
+                else if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m.type, 1, m.row_bytes, m.K, &m.M)
+                                 : !q38b_gemvn_group_plannable(ctx, m.type, 1, m.row_bytes, m.K, &m.M, nb)) ok = false;
             }
             if (!ok) { i = next_real(i + 1); continue; }   // the quantize step runs as a kernel of its own
             quant = (int)i;
@@ -214,7 +215,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
         const int col = ops[g0].b;
         size_t k = g0, resume = g0 + 1;   // resume: the step after the last matvec this run has taken
         while (on_column(k, col)) {
-            Merged mg = {(int)k, 0, {0, 0, 0}, quant};
+            Merged mg = {(int)k, 0, {0, 0, 0}, quant, -1};
             const Mat& m0 = p->mats[ops[k].a];
             int Ms[3];
             while (on_column(k, col) && mg.n < 3) {
@@ -233,6 +234,18 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 resume = k + 1;
                 k = next_in_run(k);
                 continue;
+            }
+            // gate and up in one single-column launch, SwiGLU right behind them on exactly their outputs: the launch's epilogue
+            // forms h and its Q8_K blocks (one GPU: a rank's row shard does not cover whole 256-row blocks)
+            if (mg.n == 2 && nb == 1 && !ranks && p->fuse_swiglu) {
+                const Op &g = ops[mg.ops[0]], &u = ops[mg.ops[1]];
+                const size_t j = next_real((size_t)mg.ops[1] + 1);
+                const int Mg = p->mats[g.a].M;
+                if (j < n && ops[j].kind == OP_SWIGLU && ops[j].a == g.c && ops[j].off == g.off && ops[j].b == u.c && ops[j].d == u.off &&
+                    ops[j].n == Mg && p->mats[u.a].M == Mg && Mg % 256 == 0 && Mg / 256 <= p->sw_counter_words) {
+                    mg.swiglu = (int)j;
+                    skip[j] = 1;
+                }
             }
             if (mg.n > 1 || quant >= 0) {
                 for (int t = 0; t < mg.n; t++) skip[mg.ops[t]] = 1;
@@ -280,7 +293,21 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                 long long ylds[3];
                 for (int t = 0; t < mg.n; t++) ylds[t] = p->bufs[p->ops[mg.ops[t]].c].n;
                 const Buf& sb = p->bufs[g0.b];
-                const int rc = q38b_gemvn_group(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, sb.ptr, sb.n / 256, nb, y, ylds, st);
+                const float* xf = nullptr;
+                long long xf_ld = 0;
+                if (mg.quant >= 0) {   // the quantize step is folded: the kernel reads the fp32 columns
+                    const Buf& src = p->bufs[p->ops[mg.quant].a];
+                    xf = (const float*)src.ptr + p->ops[mg.quant].off;
+                    xf_ld = src.n;
+                }
+                float* peers[7];
+                int np = 0;
+                const Buf& d0 = p->bufs[g0.c];
+                if (p->peer_store && ctx->n_ranks > 1 && mg.n == 1)
+                    for (int r = 0; r < d0.n_peer_ranks; r++)
+                        if (r != ctx->rank && d0.peer[r]) peers[np++] = (float*)d0.peer[r] + g0.off;
+                const int rc = q38b_gemvn_group_x(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, xf ? nullptr : sb.ptr, sb.n / 256, xf, xf_ld, nb, y,
+                                                  ylds, peers, np, st);
                 if (rc != Q38B_OK) return rc;
                 continue;
             }
@@ -300,7 +327,10 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                     if (k != np) return Q38B_ERR_ARG;   // all outputs of one launch live in peer-visible buffers, or none
                 }
             }
-            const int rc = q38b_gemv_group_peers(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, st);
+            const int rc = mg.swiglu >= 0
+                               ? q38b_gemv_group_swiglu(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, p->d_sw_counters,
+                                                        p->bufs[p->ops[mg.swiglu].c].ptr, st)
+                               : q38b_gemv_group_peers(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, st);
             if (rc != Q38B_OK) return rc;
         }
         if (skip[oi]) continue;
@@ -347,7 +377,8 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                 for (const Merged& mg : merged) next_is_merged |= (mg.quant >= 0 ? mg.quant : mg.first_op) == (int)j;
                 const bool next_is_swiglu = j < p->ops.size() && !skip[j] && p->ops[j].kind == OP_SWIGLU;
                 const bool adjacent = j == oi + 1;   // nothing (not even a gather) between the barrier and that launch
-                if (adjacent && (next_is_merged || next_is_swiglu)) ctx->pending_sync_seq = barrier_seq++;
+                // (the multi-column kernel has no barrier in its prologue: in front of it the barrier is a kernel of its own)
+                if (adjacent && ((next_is_merged && nb == 1) || next_is_swiglu)) ctx->pending_sync_seq = barrier_seq++;
                 else rc = launch_barrier(ctx, 0, 1, barrier_seq++, st);
                 break;
             }
@@ -484,6 +515,7 @@ void q38b_pass_destroy(q38b_pass* p) {
     if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
     if (p->pin_in) cudaFreeHost(p->pin_in);
     if (p->pin_out) cudaFreeHost(p->pin_out);
+    if (p->d_sw_counters) cudaFree(p->d_sw_counters);
     delete p;
 }
 
@@ -562,6 +594,14 @@ int q38b_pass_op_gemv(q38b_pass* p, int mat, int src, int dst, int off) {
 int q38b_pass_op_swiglu(q38b_pass* p, int g, int g_off, int u, int u_off, int n, int dst) {
     if (!p || !is_f32(p, g) || !is_f32(p, u) || !is_q8k(p, dst) || n % 256 || g_off < 0 || u_off < 0) return Q38B_ERR_ARG;
     if (g_off + n > p->bufs[g].n || u_off + n > p->bufs[u].n || p->bufs[dst].n < n || p->bufs[g].n != p->bufs[u].n) return Q38B_ERR_ARG;
+    if (n / 256 > p->sw_counter_words) {   // counters of the fused epilogue (never allocated while a graph is being captured)
+        if (p->d_sw_counters) cudaFree(p->d_sw_counters);
+        p->d_sw_counters = nullptr;
+        p->sw_counter_words = 0;
+        PASS_CUDA(p, cudaMalloc(&p->d_sw_counters, (size_t)(n / 256) * sizeof(unsigned)));
+        PASS_CUDA(p, cudaMemset(p->d_sw_counters, 0, (size_t)(n / 256) * sizeof(unsigned)));
+        p->sw_counter_words = n / 256;
+    }
     p->ops.push_back({OP_SWIGLU, g, u, dst, u_off, n, g_off});
     return Q38B_OK;
 }
@@ -578,7 +618,7 @@ int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const q38b_pass::Captured now = {p->ops.size(), p->peer_store, p->merge_steps, p->ctx->uniform_columns, p->ctx->pass_pdl,
-                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->split_tail, p->ctx->line_phase, p->ctx->dynamic_tiles};
+                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->one_cta, p->fuse_swiglu};
     if (p->graphs[nb] && !(now == p->captured[nb])) {
         cudaGraphExecDestroy(p->graphs[nb]);
         p->graphs[nb] = nullptr;
@@ -613,6 +653,7 @@ int q38b_pass_run_host(q38b_pass* p, int nb, int in_buf, const float* x_host, in
     }
     if (p->pin_out_n < need_out) {
         if (p->pin_out) cudaFreeHost(p->pin_out);
+    if (p->d_sw_counters) cudaFree(p->d_sw_counters);
         PASS_CUDA(p, cudaMallocHost(&p->pin_out, need_out * sizeof(float)));
         p->pin_out_n = need_out;
     }
@@ -674,9 +715,17 @@ int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, in
     for (int i = 0; i < n_steps; i++) launch_of[i] = i;
     for (const Merged& mg : merged) {
         if (mg.quant >= 0) launch_of[mg.quant] = -1;
+        if (mg.swiglu >= 0) launch_of[mg.swiglu] = mg.first_op;
         for (int t = 0; t < mg.n; t++) launch_of[mg.ops[t]] = mg.first_op;
     }
     return (int)merged.size();
+}
+
+// Test hook: 0 keeps SwiGLU steps as kernels of their own.
+int q38b_debug_pass_set_fuse_swiglu(q38b_pass* p, int enabled) {
+    if (!p) return Q38B_ERR_ARG;
+    p->fuse_swiglu = enabled ? 1 : 0;
+    return Q38B_OK;
 }
 
 int q38b_pass_kernel_count(const q38b_pass* p) {

@@ -403,6 +403,12 @@ int gemm_prefill_any(q38b_ctx* ctx, uint32_t type, const void* W, size_t row_byt
         case T_IQ3_XXS: return launch_prefill<T_IQ3_XXS>(ctx, a, map, grid, st, f16);
         case T_IQ3_S: return launch_prefill<T_IQ3_S>(ctx, a, map, grid, st, f16);
         case T_IQ4_XS: return launch_prefill<T_IQ4_XS>(ctx, a, map, grid, st, f16);
+        case T_Q2_K: return launch_prefill<T_Q2_K>(ctx, a, map, grid, st, f16);
+        case T_IQ2_XXS: return launch_prefill<T_IQ2_XXS>(ctx, a, map, grid, st, f16);
+        case T_IQ2_XS: return launch_prefill<T_IQ2_XS>(ctx, a, map, grid, st, f16);
+        case T_IQ2_S: return launch_prefill<T_IQ2_S>(ctx, a, map, grid, st, f16);
+        case T_IQ1_S: return launch_prefill<T_IQ1_S>(ctx, a, map, grid, st, f16);
+        case T_IQ1_M: return launch_prefill<T_IQ1_M>(ctx, a, map, grid, st, f16);
         default: return Q38B_ERR_UNSUPPORTED;
     }
 }

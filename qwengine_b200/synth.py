@@ -13,6 +13,7 @@ from . import formats as F
 _FP16_FIELDS = {
     "Q8_0": (0,), "Q4_K": (0, 2), "Q5_K": (0, 2), "Q6_K": (208,),
     "IQ3_XXS": (0,), "IQ3_S": (0,), "IQ4_XS": (0,),
+    "Q2_K": (80, 82), "IQ2_XXS": (0,), "IQ2_XS": (0,), "IQ2_S": (0,), "IQ1_S": (0,), "IQ1_M": (),
 }
 
 
@@ -33,6 +34,12 @@ def make_weights(fmt, M: int, K: int, seed: int, scale: float = 1e-3, zero_mean:
             d0 = w[:, :, 0:2].copy().view(np.float16).reshape(M, nblk).astype(np.float32)
             d = (d0 * np.float32(ZERO_MEAN_DMIN[f.name])).astype(np.float16)
         w[:, :, off:off + 2] = d.view(np.uint8).reshape(M, nblk, 2)
+    if f.name == "IQ1_M":
+        # the fp16 super-scale is scattered over the top nibbles of the four 16-bit scale words (bytes 48..55)
+        bits = (np.abs(rng.standard_normal((M, nblk), dtype=np.float32)) * np.float32(scale)).astype(np.float16).view(np.uint16)
+        for k in range(4):
+            hi = w[:, :, 49 + 2 * k]
+            w[:, :, 49 + 2 * k] = (hi & 0x0F) | ((((bits >> (4 * k)) & 0xF) << 4).astype(np.uint8))
     return w.reshape(M, nblk * f.block_bytes)
 
 

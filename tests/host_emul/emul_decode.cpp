@@ -216,6 +216,11 @@ static int emul_gemv1_any(int fmt, int K, const uint8_t* W, int n_rows, const ui
     for (int i = 0; i < 128 * 16; i++) ksign_entry((uint32_t)i >> 4, sgn[2 * i], sgn[2 * i + 1]);
     Codebook1 cbs[32];
     for (int l = 0; l < 32; l++) cbs[l] = Codebook1{sp_from(cb.data()) + 4 * (l & (reps - 1)), sp_from(sgn.data()) + 8 * (l & 15)};
+    // the formats whose grids are 16-bit codes read one shared copy of the table
+    const unsigned short* codes = fmt == T_IQ2_XXS ? q38b_iq2xxs_codes : fmt == T_IQ2_XS ? q38b_iq2xs_codes : fmt == T_IQ2_S ? q38b_iq2s_codes
+                                  : (fmt == T_IQ1_S || fmt == T_IQ1_M) ? q38b_iq1s_codes : nullptr;
+    if (codes)
+        for (int l = 0; l < 32; l++) cbs[l].lane_base = sp_from(codes);
     switch (fmt) {
         case T_Q8_0: if (d32) run_slices<T_Q8_0, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q8_0, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         case T_Q4_K: if (d32) run_slices<T_Q4_K, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q4_K, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
@@ -224,6 +229,12 @@ static int emul_gemv1_any(int fmt, int K, const uint8_t* W, int n_rows, const ui
         case T_IQ3_XXS: if (d32) run_slices<T_IQ3_XXS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ3_XXS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         case T_IQ3_S: if (d32) run_slices<T_IQ3_S, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ3_S, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         case T_IQ4_XS: if (d32) run_slices<T_IQ4_XS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ4_XS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_Q2_K: if (d32) run_slices<T_Q2_K, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_Q2_K, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ2_XXS: if (d32) run_slices<T_IQ2_XXS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ2_XXS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ2_XS: if (d32) run_slices<T_IQ2_XS, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ2_XS, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ2_S: if (d32) run_slices<T_IQ2_S, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ2_S, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ1_S: if (d32) run_slices<T_IQ1_S, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ1_S, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
+        case T_IQ1_M: if (d32) run_slices<T_IQ1_M, true>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); else run_slices<T_IQ1_M, false>(K, rowp.data(), n_rows, aq, actd.data(), cbs, y); break;
         default: return -1;
     }
     return 0;

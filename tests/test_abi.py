@@ -34,7 +34,10 @@ def test_format_table(lib):
         assert lib.q38b_format_supported(f.type_id) == 1
         for K in (256, 5120, 6144, 17408):
             assert lib.q38b_row_bytes(f.type_id, K) == f.row_bytes(K)
-    for unsupported in (0, 1, 2, 10, 16, 19, 29, 30):   # F32, F16, Q4_0, Q2_K, IQ2_XXS, IQ1_S, IQ1_M, BF16
+    for f in F.ONE_COLUMN.values():
+        assert lib.q38b_format_supported(f.type_id) == 1
+        assert lib.q38b_row_bytes(f.type_id, 5120) == f.row_bytes(5120)
+    for unsupported in (0, 1, 2, 3, 11, 20, 30):   # F32, F16, Q4_0, Q4_1, Q3_K, IQ4_NL, BF16
         assert lib.q38b_format_supported(unsupported) == 0
         assert lib.q38b_row_bytes(unsupported, 5120) == 0
     assert lib.q38b_row_bytes(18, 5000) == 0

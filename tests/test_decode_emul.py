@@ -44,12 +44,12 @@ def test_tile_matches_oracle(emul, name, nb, addr_lo, rep_log2):
     assert not y[:, nb:].any()
 
 
-@pytest.mark.parametrize("name", list(F.FORMATS))
+@pytest.mark.parametrize("name", list(F.FORMATS) + list(F.ONE_COLUMN))
 @pytest.mark.parametrize("K,addr_lo,rep_log2", [(1024, 0, 5), (1280, 8, 3), (2048, 2, 0)])
 def test_single_column_granules_match_oracle(emul, name, K, addr_lo, rep_log2):
     """The dp4a granule decoders of the nb = 1 kernel (q38b_decode1.cuh), lane by lane on the host."""
     f = F.get(name)
-    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8}.get(name, 2):
+    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8, "Q2_K": 4}.get(name, 2):
         addr_lo = 0
     u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
     f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
@@ -84,13 +84,13 @@ def test_row_group_decoder_matches_oracle(emul, K, row_pad, addr_lo):
     assert np.max(np.abs(y - ref) / mag) < 1e-6
 
 
-@pytest.mark.parametrize("name", list(F.FORMATS))
+@pytest.mark.parametrize("name", list(F.FORMATS) + list(F.ONE_COLUMN))
 @pytest.mark.parametrize("K,addr_lo", [(1024, 0), (1280, 8)])
 def test_single_column_granules_with_per32_activations(emul, name, K, addr_lo):
     """The same decoders fed with the reference GPU path's activation format (int8 values, one scale per 32): the
     result is the exact dot of the dequantized weights with d[k / 32] * q[k]."""
     f = F.get(name)
-    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8}.get(name, 2):
+    if addr_lo % {"Q4_K": 16, "Q5_K": 16, "IQ4_XS": 8, "Q2_K": 4}.get(name, 2):
         addr_lo = 0
     u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
     i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")

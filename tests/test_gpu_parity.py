@@ -136,30 +136,22 @@ def test_row_group_mapping_against_lane_per_granule(ctx, M, K, pad):
 
 @pytest.mark.parametrize("name", ALL)
 @pytest.mark.parametrize("M,K", [(5120, 1024), (2999, 1024), (8 * 296 + 8 * 40 + 3, 512), (700, 5120), (5120, 17408)])
-def test_sub_tiles_of_the_last_round_change_no_bits(ctx, name, M, K):
-    """The one-column kernel cuts the tiles left over after the last full round of the grid into sub-tiles of fewer
-    rows; a row's arithmetic does not depend on the tile it sits in, so the outputs are the bits of the whole-tile
-    schedule."""
+def test_one_and_two_ctas_per_sm_give_the_same_bits(ctx, name, M, K):
+    """The one-column kernel exists for two CTAs per SM (eight consumer warps each) and for one (sixteen warps, larger
+    tiles for the row-group mapping); a row's arithmetic does not depend on the tile it sits in or the warp that takes
+    it, so both give the same bits."""
     f = F.get(name)
     w = dev(synth.make_weights(f, M, K, seed=800 + M % 97, scale=scale_for(name)))
     xq = dev(oracle.port.quantize_q8k(synth.make_activations(1, K, seed=801)))
-    y_split = ctx.gemv(f, w, xq, K)
-    ctx.debug_set_split_tail(False)
     try:
-        y_whole = ctx.gemv(f, w, xq, K)
+        ctx.debug_set_one_cta(0)
+        y_two = ctx.gemv(f, w, xq, K)
+        ctx.debug_set_one_cta(2)
+        y_one = ctx.gemv(f, w, xq, K)
     finally:
-        ctx.debug_set_split_tail(True)
+        ctx.debug_set_one_cta(1)
     ctx.check()
-    assert torch.equal(y_split.view(torch.int32), y_whole.view(torch.int32))
-    # the same holds for who computes a tile: tickets from a counter (default) or every grid-th tile
-    ctx.debug_set_dynamic_tiles(False)
-    try:
-        y_static = ctx.gemv(f, w, xq, K)
-    finally:
-        ctx.debug_set_dynamic_tiles(True)
-    for _ in range(3):   # the counters are back at zero after every launch
-        assert torch.equal(ctx.gemv(f, w, xq, K).view(torch.int32), y_static.view(torch.int32))
-    ctx.check()
+    assert torch.equal(y_two.view(torch.int32), y_one.view(torch.int32))
 
 
 @pytest.mark.parametrize("name", ALL)
@@ -267,7 +259,7 @@ def test_argument_errors(ctx):
     call = lambda **kw: ctx.gemv_raw(**{**dict(type_id=18, W_ptr=w.data_ptr(), row_bytes=rb, K=K, M=M, xq_ptr=xq.data_ptr(),
                                                x_stride=K // 256, nb=1, y_ptr=y.data_ptr(), y_ld=M), **kw})
     assert call() == 0
-    assert call(type_id=10) == -2          # Q2_K: no kernel here
+    assert call(type_id=11) == -2          # Q3_K: no kernel here
     assert call(nb=9) == -1 and call(nb=0) == -1
     assert call(K=500) == -1
     assert call(W_ptr=w.data_ptr() + 2) == -3
@@ -343,3 +335,24 @@ def test_ffn_block_full_size(ctx):
     y_o = oracle.port.gemv(F.Q6_K.type_id, down, hq_o, FF)[0]
     _, mag = oracle.port.row_ref_mag(F.Q6_K.type_id, down, hq_o[0], FF)
     assert np.max(np.abs(y - y_o) / mag) < HARD_BAR
+
+
+def test_one_column_kernels_are_resident_as_planned(ctx):
+    """Every one-column launch plans its shared memory for two CTAs per SM (or one, for the 16-warp variant); a launch
+    whose CTA turned out too large (for instance by static shared memory the plan did not count) would silently run at
+    half the occupancy."""
+    ctx.lib.q38b_debug_occupancy_shortfalls(ctx.h, 1)
+    try:
+        for name in ALL:
+            f = F.get(name)
+            for M, K in [(64, 256), (128, 1024), (512, 5120), (64, 6144), (40, 17408)]:
+                w = dev(synth.make_weights(f, M, K, seed=1))
+                xq = dev(oracle.port.quantize_q8k(synth.make_activations(1, K, seed=2)))
+                for mode in (0, 2):
+                    ctx.debug_set_one_cta(mode)
+                    ctx.gemv(f, w, xq, K)
+        ctx.check()
+    finally:
+        ctx.debug_set_one_cta(1)
+        n = ctx.lib.q38b_debug_occupancy_shortfalls(ctx.h, 0)
+    assert n == 0

@@ -56,7 +56,7 @@ def test_decode_call_sites(probe, name, nb):
 
 def test_unsupported_format_returns_false(probe):
     t = torch.zeros(64, dtype=torch.uint8, device="cuda")
-    assert probe.probe_decode(10, t.data_ptr(), 84, 256, 1, t.data_ptr(), 1, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr()) == 1   # Q2_K
+    assert probe.probe_decode(11, t.data_ptr(), 110, 256, 1, t.data_ptr(), 1, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr()) == 1   # Q3_K: no kernel
 
 
 @pytest.mark.parametrize("name", ["IQ3_XXS", "Q4_K"])

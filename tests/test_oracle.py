@@ -8,6 +8,7 @@ from qwengine_b200 import formats as F, synth
 
 ALL = list(F.FORMATS)
 WITH_REF_DOT = ["IQ3_XXS", "IQ3_S", "IQ4_XS", "Q4_K", "Q6_K"]   # get_vec_dot returns nullptr for Q5_K and Q8_0
+EXTRA = list(F.ONE_COLUMN)                                      # the reference's other six matvec formats
 
 
 def bits(a):
@@ -59,7 +60,23 @@ def test_port_equals_compiled_reference(name):
         assert not oracle.ref.has_vec_dot(f.type_id)
 
 
-@pytest.mark.parametrize("name", ALL)
+@pytest.mark.skipif(oracle.ref is None, reason="oracle/_ref not built (no reference checkout)")
+@pytest.mark.parametrize("name", EXTRA)
+def test_port_equals_compiled_reference_other_formats(name):
+    """IQ2_XXS, IQ2_XS, IQ2_S, IQ1_S, IQ1_M and Q2_K: dequantized values and dot products of the restatement are the bits of
+    the reference's own quant_ref.cpp / cpu_kernels.cpp."""
+    f = F.get(name)
+    K = 1024
+    w = synth.make_weights(f, 40, K, seed=5 + f.type_id, scale=1e-3)
+    assert np.array_equal(bits(oracle.port.dequantize(f.type_id, w)), bits(oracle.ref.dequantize(f.type_id, w, K)))
+    xq = oracle.port.quantize_q8k(synth.make_activations(8, K, seed=9) * (np.arange(8, dtype=np.float32)[:, None] + 1))
+    assert oracle.ref.has_vec_dot(f.type_id)
+    for nb in (1, 4, 7, 8):
+        y_ref, _ = oracle.ref.gemv(f.type_id, w, xq[:nb], K, threads=2)
+        assert np.array_equal(bits(oracle.port.gemv(f.type_id, w, xq[:nb], K)), bits(y_ref))
+
+
+@pytest.mark.parametrize("name", ALL + EXTRA)
 def test_dequant_matches_gguf_py(name):
     gguf = pytest.importorskip("gguf")
     from gguf import quants
