@@ -87,7 +87,10 @@ __device__ __forceinline__ void quantize_block(const float* src, uint8_t* blk) {
     q8k_block_from_regs(v, blk);
 }
 
-// h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u; one warp, 256 values.
+// h = silu(g) * u, the CPU formula of the reference (src/runtime/engine.cpp:177-182): g / (1 + expf(-g)) * u
+__device__ __forceinline__ float swiglu_value(float gv, float uv) { return __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv); }
+
+// one warp, 256 values
 template <bool COHERENT>
 __device__ __forceinline__ void swiglu_block(const float* g, const float* u, float* h, uint8_t* blk) {
     const int lane = threadIdx.x & 31;
@@ -96,7 +99,7 @@ __device__ __forceinline__ void swiglu_block(const float* g, const float* u, flo
     for (int e = 0; e < 8; e++) {
         const float gv = COHERENT ? __ldcg(g + 8 * lane + e) : g[8 * lane + e];
         const float uv = COHERENT ? __ldcg(u + 8 * lane + e) : u[8 * lane + e];
-        v[e] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
+        v[e] = swiglu_value(gv, uv);
     }
     if (h) {
 #pragma unroll

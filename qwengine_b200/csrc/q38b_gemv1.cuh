@@ -31,16 +31,11 @@ struct Gemv1Args {
     const float* xd32;      // per-32 activations (kernels instantiated with A32): xq = K int8 values, xd32 = K / 32 scales
     const uint8_t* xq;      // Q8_K blocks of the single column, or nullptr:
     const float* x_f32;     // then the K floats of the column, quantized to Q8_K blocks by every CTA in its prologue
+    const float* x_up;      // with x_f32: the column is silu(x_f32) * x_up (SwiGLU of gate and up outputs), formed in the prologue too
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     float* y_peer_more[G1_MAX_MATS - 1][7];   // the same for matrices 1 and 2
     PeerSync sync;          // cross-GPU barrier before the column is read (the peers pushed parts of it), n = 0: none
-    // SwiGLU in the epilogue (sw_counters != nullptr): matrices 0 and 1 are the gate and up projections, M rows each
-    // (a multiple of 256).  The warp that completes a tile adds its rows to the counter of their 256-row block; the one
-    // that brings a block to 512 rows (gate and up complete) computes h = silu(g) * u for it and writes its Q8_K block
-    // to sw_q8k, then zeroes the counter: no SwiGLU kernel between this launch and the down projection.
-    unsigned* sw_counters;
-    uint8_t* sw_q8k;
     int n_peers;
     int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;
@@ -248,6 +243,19 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                     hi4[j] = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane + 4);
                 }
             }
+            if (a.x_up) {   // the arithmetic of swiglu_block, value by value
+#pragma unroll
+                for (int j = 0; j < QB; j++) {
+                    const int sb = sb0 + j * NWARPS;
+                    if (sb >= a.nsb) continue;
+                    const float4 ul = *(const float4*)(a.x_up + (size_t)sb * 256 + 8 * lane);
+                    const float4 uh = *(const float4*)(a.x_up + (size_t)sb * 256 + 8 * lane + 4);
+                    lo4[j].x = swiglu_value(lo4[j].x, ul.x); lo4[j].y = swiglu_value(lo4[j].y, ul.y);
+                    lo4[j].z = swiglu_value(lo4[j].z, ul.z); lo4[j].w = swiglu_value(lo4[j].w, ul.w);
+                    hi4[j].x = swiglu_value(hi4[j].x, uh.x); hi4[j].y = swiglu_value(hi4[j].y, uh.y);
+                    hi4[j].z = swiglu_value(hi4[j].z, uh.z); hi4[j].w = swiglu_value(hi4[j].w, uh.w);
+                }
+            }
 #pragma unroll
             for (int j = 0; j < QB; j++) {
                 const int sb = sb0 + j * NWARPS;
@@ -443,20 +451,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                 const float out = a.accumulate ? ym[row] + v : v;
                 ym[row] = out;
                 for (int pr = 0; pr < a.n_peers; pr++) (mi == 0 ? a.y_peer[pr] : a.y_peer_more[mi - 1][pr])[row] = out;   // fused all-gather: push to every peer
-                if (a.sw_counters) __threadfence();   // the row is visible to whoever completes the block
-            }
-            __syncwarp();
-            if (a.sw_counters) {
-                const int blk = tr.row0 >> 8;
-                const int stored = max(0, min(G1_ROWS, Mm - tr.row0));
-                unsigned before = 0;
-                if (lane == 0) before = atomicAdd(a.sw_counters + blk, (unsigned)stored);
-                before = __shfl_sync(0xffffffffu, before, 0);
-                if (before + (unsigned)stored == 512u) {
-                    __threadfence();
-                    swiglu_block<true>(a.y + (size_t)blk * 256, a.y_more[0] + (size_t)blk * 256, nullptr, a.sw_q8k + (size_t)blk * 292);
-                    if (lane == 0) a.sw_counters[blk] = 0u;
-                }
             }
         }
         slice += NWARPS;

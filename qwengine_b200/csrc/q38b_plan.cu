@@ -88,9 +88,11 @@ struct q38b_pass {
     float* pin_in = nullptr;
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
-    int fuse_swiglu = 1;         // single-column replays on one GPU: a SwiGLU step right behind a merged gate + up launch runs in its epilogue
-    unsigned* d_sw_counters = nullptr;   // one word per 256-row block of the widest SwiGLU step, zero between launches
-    int sw_counter_words = 0;
+    // 1: single-column replays fold a SwiGLU step into the matvecs that read its output, like a quantize step (one kernel
+    // fewer per FFN block).  Off by default: every CTA of the down projection then evaluates all of silu(g) * u in its
+    // prologue, which measured slower on B200 than the separate SwiGLU kernel (26.4 us against 15.7 + about 5 us for
+    // K = 17408).  q38b_debug_pass_set_fuse_swiglu switches it on.
+    int fuse_swiglu = 0;
     int merge_steps = 1;         // replays: one launch for matvecs that share a column, quantize steps folded into single-column launches
     // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
     // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
@@ -149,12 +151,13 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
 }
 
 // One launch of the merged single-column replay: `n` matvec ops (indices into p->ops) that read one column, which comes
-// as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source of that quantize op (folded into the launch).
-struct Merged { int first_op; int n; int ops[3]; int quant; int swiglu; };   // swiglu >= 0: that SwiGLU step runs in the launch's epilogue
+// as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source(s) of that quantize or SwiGLU op (folded into
+// the launch: the kernel forms the Q8_K blocks in its prologue).
+struct Merged { int first_op; int n; int ops[3]; int quant; };
 
-// Which steps of a single-column replay on one GPU can share launches.  A quantize step is folded into the matvecs that
-// read its output when they follow it directly, nothing else reads that output before it is rewritten, and all of them
-// run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
+// Which steps of a replay can share launches.  A quantize step (for one column also a SwiGLU step) is folded into the
+// matvecs that read its output when they follow it directly, nothing else reads that output before it is rewritten, and
+// all of them run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
 void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vector<char>& skip) {
     const q38b_ctx* ctx = p->ctx;
     const std::vector<Op>& ops = p->ops;
@@ -184,13 +187,14 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
     while (i < n) {
         int quant = -1;
         size_t g0 = i;
-        if (ops[i].kind == OP_QUANT) {
-            const int col = ops[i].b;
+        const bool gated = ops[i].kind == OP_SWIGLU && nb == 1 && p->fuse_swiglu;
+        if (ops[i].kind == OP_QUANT || gated) {
+            const int col = gated ? ops[i].c : ops[i].b;
             const size_t j = ranks ? i + 1 : next_real(i + 1);   // several ranks: only a matvec right after the quantize step
             std::vector<size_t> run;                              // the matvecs the quantize step would be folded into
             for (size_t k = j; on_column(k, col); k = next_in_run(k)) run.push_back(k);
             const size_t run_end = run.empty() ? j : next_real(run.back() + 1);
-            bool ok = !run.empty() && ops[i].off % 4 == 0;
+            bool ok = !run.empty() && ops[i].off % 4 == 0 && (!gated || ops[i].d % 4 == 0);
             for (size_t k = run_end; ok && k < n; k++) {   // nobody else reads the Q8_K buffer before it is written again
                 const Op& o = ops[k];
                 if ((o.kind == OP_QUANT && o.b == col) || (o.kind == OP_SWIGLU && o.c == col)) break;
@@ -215,7 +219,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
         const int col = ops[g0].b;
         size_t k = g0, resume = g0 + 1;   // resume: the step after the last matvec this run has taken
         while (on_column(k, col)) {
-            Merged mg = {(int)k, 0, {0, 0, 0}, quant, -1};
+            Merged mg = {(int)k, 0, {0, 0, 0}, quant};
             const Mat& m0 = p->mats[ops[k].a];
             int Ms[3];
             while (on_column(k, col) && mg.n < 3) {
@@ -234,18 +238,6 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 resume = k + 1;
                 k = next_in_run(k);
                 continue;
-            }
-            // gate and up in one single-column launch, SwiGLU right behind them on exactly their outputs: the launch's epilogue
-            // forms h and its Q8_K blocks (one GPU: a rank's row shard does not cover whole 256-row blocks)
-            if (mg.n == 2 && nb == 1 && !ranks && p->fuse_swiglu) {
-                const Op &g = ops[mg.ops[0]], &u = ops[mg.ops[1]];
-                const size_t j = next_real((size_t)mg.ops[1] + 1);
-                const int Mg = p->mats[g.a].M;
-                if (j < n && ops[j].kind == OP_SWIGLU && ops[j].a == g.c && ops[j].off == g.off && ops[j].b == u.c && ops[j].d == u.off &&
-                    ops[j].n == Mg && p->mats[u.a].M == Mg && Mg % 256 == 0 && Mg / 256 <= p->sw_counter_words) {
-                    mg.swiglu = (int)j;
-                    skip[j] = 1;
-                }
             }
             if (mg.n > 1 || quant >= 0) {
                 for (int t = 0; t < mg.n; t++) skip[mg.ops[t]] = 1;
@@ -313,6 +305,8 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
             }
             const void* q8k = mg.quant >= 0 ? nullptr : p->bufs[g0.b].ptr;
             const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
+            const float* xu = nullptr;   // a folded SwiGLU step: the column is silu(xf) * xu
+            if (mg.quant >= 0 && p->ops[mg.quant].kind == OP_SWIGLU) xu = (const float*)p->bufs[p->ops[mg.quant].b].ptr + p->ops[mg.quant].d;
             float* peers[3 * 7];
             int np = 0;
             if (p->peer_store && ctx->n_ranks > 1) {
@@ -327,10 +321,7 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                     if (k != np) return Q38B_ERR_ARG;   // all outputs of one launch live in peer-visible buffers, or none
                 }
             }
-            const int rc = mg.swiglu >= 0
-                               ? q38b_gemv_group_swiglu(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, p->d_sw_counters,
-                                                        p->bufs[p->ops[mg.swiglu].c].ptr, st)
-                               : q38b_gemv_group_peers(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, st);
+            const int rc = q38b_gemv_group_gated(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, xu, y, peers, np, st);
             if (rc != Q38B_OK) return rc;
         }
         if (skip[oi]) continue;
@@ -515,7 +506,6 @@ void q38b_pass_destroy(q38b_pass* p) {
     if (p->cap_stream) cudaStreamDestroy(p->cap_stream);
     if (p->pin_in) cudaFreeHost(p->pin_in);
     if (p->pin_out) cudaFreeHost(p->pin_out);
-    if (p->d_sw_counters) cudaFree(p->d_sw_counters);
     delete p;
 }
 
@@ -594,14 +584,6 @@ int q38b_pass_op_gemv(q38b_pass* p, int mat, int src, int dst, int off) {
 int q38b_pass_op_swiglu(q38b_pass* p, int g, int g_off, int u, int u_off, int n, int dst) {
     if (!p || !is_f32(p, g) || !is_f32(p, u) || !is_q8k(p, dst) || n % 256 || g_off < 0 || u_off < 0) return Q38B_ERR_ARG;
     if (g_off + n > p->bufs[g].n || u_off + n > p->bufs[u].n || p->bufs[dst].n < n || p->bufs[g].n != p->bufs[u].n) return Q38B_ERR_ARG;
-    if (n / 256 > p->sw_counter_words) {   // counters of the fused epilogue (never allocated while a graph is being captured)
-        if (p->d_sw_counters) cudaFree(p->d_sw_counters);
-        p->d_sw_counters = nullptr;
-        p->sw_counter_words = 0;
-        PASS_CUDA(p, cudaMalloc(&p->d_sw_counters, (size_t)(n / 256) * sizeof(unsigned)));
-        PASS_CUDA(p, cudaMemset(p->d_sw_counters, 0, (size_t)(n / 256) * sizeof(unsigned)));
-        p->sw_counter_words = n / 256;
-    }
     p->ops.push_back({OP_SWIGLU, g, u, dst, u_off, n, g_off});
     return Q38B_OK;
 }
@@ -653,7 +635,6 @@ int q38b_pass_run_host(q38b_pass* p, int nb, int in_buf, const float* x_host, in
     }
     if (p->pin_out_n < need_out) {
         if (p->pin_out) cudaFreeHost(p->pin_out);
-    if (p->d_sw_counters) cudaFree(p->d_sw_counters);
         PASS_CUDA(p, cudaMallocHost(&p->pin_out, need_out * sizeof(float)));
         p->pin_out_n = need_out;
     }
@@ -688,7 +669,7 @@ int q38b_pass_set_merge(q38b_pass* p, int enabled) {
 // steps[3 i ..] = {kind (0 quantize, 1 matvec, 2 SwiGLU, 3 all-gather, 4 barrier), column buffer, output offset}; every
 // matvec is a 512 x 1024 Q4_K matrix writing 512 floats at its offset.  launch_of[i] receives the position in the step
 // list at which step i is launched (its own index unless it joined an earlier launch), -1 for folded quantize steps.
-int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, int* launch_of) {
+int q38b_debug_merge_plan(int n_ranks, int nb, int fuse_swiglu, int n_steps, const int* steps, int* launch_of) {
     if (n_ranks < 1 || nb < 1 || n_steps < 0 || !steps || !launch_of) return Q38B_ERR_ARG;
     q38b_ctx ctx;
     ctx.sm_count = 148;
@@ -696,6 +677,7 @@ int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, in
     ctx.n_ranks = n_ranks;
     q38b_pass p;
     p.ctx = &ctx;
+    p.fuse_swiglu = fuse_swiglu;
     p.mats.push_back({(uint32_t)T_Q4_K, nullptr, 576, 1024, 512, false});
     for (int b = 0; b < 8; b++) p.bufs.push_back({nullptr, 1 << 20, b >= 4, {}, 0, false});   // 0..3 fp32, 4..7 Q8_K columns
     for (int i = 0; i < n_steps; i++) {
@@ -715,7 +697,6 @@ int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, in
     for (int i = 0; i < n_steps; i++) launch_of[i] = i;
     for (const Merged& mg : merged) {
         if (mg.quant >= 0) launch_of[mg.quant] = -1;
-        if (mg.swiglu >= 0) launch_of[mg.swiglu] = mg.first_op;
         for (int t = 0; t < mg.n; t++) launch_of[mg.ops[t]] = mg.first_op;
     }
     return (int)merged.size();

@@ -70,7 +70,9 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
     is created); gather = "nccl" records an NCCL all-gather after every matvec.
     Returns dict(in_buf, out_buf, out_len).
     """
-    x = ps.buffer_f32(HIDDEN)              # residual-stream stand-in: input of every layer
+    x_in = ps.buffer_f32(HIDDEN)           # the token's hidden state: read by layer 0 only, never written, so that
+                                           # every replay computes the same thing from the same input
+    x = ps.buffer_f32(HIDDEN)              # residual-stream stand-in: output of every layer, input of the next
     xq = ps.buffer_q8k(HIDDEN)
     big = ps.buffer_f32(16384)             # projection outputs (in_proj / q+gate)
     kv = ps.buffer_f32(2048)
@@ -95,7 +97,7 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
 
     for il in range(n_layers):
         attn, mats = layer_specs(il)
-        ps.quantize(x, 0, HIDDEN, xq)
+        ps.quantize(x_in if il == 0 else x, 0, HIDDEN, xq)
         if attn:
             matvec(mats[0], xq, big, 0)
             matvec(mats[1], xq, kv, 0)
@@ -120,7 +122,7 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
         ps.quantize(x, 0, HIDDEN, xq)
         matvec(MatSpec("lm_head", "Q6_K", VOCAB, HIDDEN), xq, logits, 0)
         sync()
-    return dict(in_buf=x, out_buf=logits if head else x, out_len=VOCAB if head else HIDDEN)
+    return dict(in_buf=x_in, out_buf=logits if head else x, out_len=VOCAB if head else HIDDEN)
 
 
 def oracle_forward(port, weights, x, n_layers, head=True):

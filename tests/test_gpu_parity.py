@@ -139,19 +139,26 @@ def test_row_group_mapping_against_lane_per_granule(ctx, M, K, pad):
 def test_one_and_two_ctas_per_sm_give_the_same_bits(ctx, name, M, K):
     """The one-column kernel exists for two CTAs per SM (eight consumer warps each) and for one (sixteen warps, larger
     tiles for the row-group mapping); a row's arithmetic does not depend on the tile it sits in or the warp that takes
-    it, so both give the same bits."""
+    it, so both give the same bits.  (Compared with the row-group mapping off: which shapes it takes differs between the
+    two variants, and it sums a row in another order than the lane-per-granule mapping.)"""
     f = F.get(name)
     w = dev(synth.make_weights(f, M, K, seed=800 + M % 97, scale=scale_for(name)))
     xq = dev(oracle.port.quantize_q8k(synth.make_activations(1, K, seed=801)))
+    ys = {}
     try:
-        ctx.debug_set_one_cta(0)
-        y_two = ctx.gemv(f, w, xq, K)
-        ctx.debug_set_one_cta(2)
-        y_one = ctx.gemv(f, w, xq, K)
+        for rg in (False, True):
+            ctx.debug_set_rowgroup(rg)
+            for mode in (0, 2):
+                ctx.debug_set_one_cta(mode)
+                ys[rg, mode] = ctx.gemv(f, w, xq, K)
     finally:
         ctx.debug_set_one_cta(1)
+        ctx.debug_set_rowgroup(True)
     ctx.check()
-    assert torch.equal(y_two.view(torch.int32), y_one.view(torch.int32))
+    assert torch.equal(ys[False, 0].view(torch.int32), ys[False, 2].view(torch.int32))
+    scale = float(ys[False, 0].abs().max())
+    for mode in (0, 2):
+        assert float((ys[True, mode] - ys[False, 0]).abs().max()) <= 1e-5 * scale
 
 
 @pytest.mark.parametrize("name", ALL)

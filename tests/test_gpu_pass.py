@@ -277,9 +277,9 @@ def test_pass_from_gguf_file(ctx, tmp_path):
             g2.close()
 
 
-def test_swiglu_in_the_gate_up_epilogue(ctx):
-    """On one GPU the SwiGLU step behind a merged gate + up launch runs in that launch's epilogue (the warp that completes
-    a 256-row block of both matrices forms h and its Q8_K block): one kernel fewer per layer, the same bits."""
+def test_swiglu_folded_into_the_down_projection(ctx):
+    """A SwiGLU step whose output only the next matvec reads is folded into that launch (every CTA forms silu(g) * u and
+    its Q8_K blocks in its prologue, the arithmetic of the SwiGLU kernel): one kernel fewer per layer, the same bits."""
     K, FFN = 1024, 1536
     wg = synth.make_weights("IQ3_XXS", FFN, K, seed=31, scale=2e-4)
     wu = synth.make_weights("IQ3_XXS", FFN, K, seed=32, scale=2e-4)
@@ -290,7 +290,7 @@ def test_swiglu_in_the_gate_up_epilogue(ctx):
         ps = q.Pass(ctx, max_nb=1)
         ps.debug_set_fuse_swiglu(fuse)
         xin, xq, gu, hq, y = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(2 * FFN), ps.buffer_q8k(FFN), ps.buffer_f32(300)
-        for _ in range(2):   # two layers: the block counters are back at zero for the second one
+        for _ in range(2):   # two layers
             ps.quantize(xin, 0, K, xq)
             ps.gemv(ps.matrix_upload("IQ3_XXS", wg, K), xq, gu, 0)
             ps.gemv(ps.matrix_upload("IQ3_XXS", wu, K), xq, gu, FFN)
