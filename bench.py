@@ -427,16 +427,20 @@ def run_ours(args):
     finite = bool(torch.isfinite(logits[:7]).all().item())
 
     # end to end through the host-buffer entry point: pinned staging, H2D of the token's hidden state, the pass,
-    # D2H of the logits, synchronise -- every step
+    # D2H of the step's result (the head's top-k values and positions, what the sampler reads), synchronise -- every step
     xh = np.ascontiguousarray(x0[:1].cpu().numpy())
-    yh = np.empty((1, io["out_len"]), np.float32)
+    yh = np.empty((1, 2 * io["topk_k"]), np.float32)
     for _ in range(3):
-        ps.run_host(1, io["in_buf"], xh, io["out_buf"], 0, yh)
+        ps.run_host(1, io["in_buf"], xh, io["topk_buf"], 0, yh)
     sync_all()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        ps.run_host(1, io["in_buf"], xh, io["out_buf"], 0, yh)
+        ps.run_host(1, io["in_buf"], xh, io["topk_buf"], 0, yh)
     sync_all()
+    # the returned candidates are the logits' largest (checked once, outside the timed region)
+    k_ = io["topk_k"]
+    top_v, top_i = torch.topk(logits[0], k_)
+    topk_ok = bool(np.array_equal(np.sort(yh[0, k_:].view(np.int32)), np.sort(top_i.cpu().numpy().astype(np.int32)))) if finite else None
     e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device="cuda")
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
@@ -500,7 +504,7 @@ def run_ours(args):
             "ms_per_step": round(ms1, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8", "data": "synthetic",
             "config": run_config(n_layers, world, args.gather),
-            "checks": {"outputs_finite": finite, "sharded_bits_equal_single": shard_ok},
+            "checks": {"outputs_finite": finite, "topk_matches_logits": topk_ok, "sharded_bits_equal_single": shard_ok},
             "tokens_per_s": round(1e3 / ms1, 1),
             "frac_of_nominal_8TBps": round(value / world / HBM_NOMINAL_GBS, 4),
             "nb7": {"ms_per_step": round(ms7, 4), "value": round(total_bytes / ms7 / 1e6, 1), "tokens_per_s": round(7e3 / ms7, 1),

@@ -159,6 +159,14 @@ int q38b_add_rmsnorm_q8k(q38b_ctx* ctx, float* x_dev, const float* a_dev, const 
  * W [N][K] (row-major, 16-byte aligned, K a multiple of 8), fp32 x and y, fp32 accumulation. */
 int q38b_gemv_bf16(q38b_ctx* ctx, const void* W_bf16_dev, int K, int N, const float* x_dev, float* y_dev, void* stream);
 
+/* Replaces topk (src/cuda/ops.cuh:142-144, src/cuda/ops.cu:823-903,1037-1044; called on the head's logits,
+ * src/runtime/engine.cpp:1680,1910): for each of n_rows vectors of n logits (ld floats apart) the k largest values,
+ * descending, equal values by ascending position, and their positions + index_offset; NaN ranks below everything; slots
+ * past n get position -1.  vals_dev / idx_dev: [n_rows][out_ld].  1 <= k <= 64, n <= 393216, n_rows <= 8; no work buffer
+ * argument (the context owns it), nothing allocated by the call. */
+int q38b_topk(q38b_ctx* ctx, const float* logits_dev, long long ld, int n, int n_rows, int k, int index_offset, float* vals_dev,
+              int* idx_dev, int out_ld, void* stream);
+
 /* Replaces swiglu_rows_inplace (src/cuda/prefill.cuh:33-35, src/cuda/prefill.cu:132-151): for B rows of n values (row
  * stride ld floats) silu(G) * U is written IN PLACE over the first 2 n bytes of each row of G, as fp16
  * (out_kind = Q38B_OUT_F16, the reference's choice) or bf16 (Q38B_OUT_BF16, for q38b_gemm_prefill): the next GEMM reads
@@ -232,6 +240,9 @@ int q38b_pass_matrix_device(q38b_pass* pass, uint32_t type, const void* W_dev, s
 int q38b_pass_op_quantize(q38b_pass* pass, int src_f32, int src_off, int K, int dst_q8k);
 int q38b_pass_op_gemv(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
 int q38b_pass_op_swiglu(q38b_pass* pass, int g_f32, int g_off, int u_f32, int u_off, int n, int dst_q8k);
+/* The k best of n logits of buffer src_f32 (from float offset off) per column: dst_f32 gets k values followed by k
+ * positions (int32 bit patterns), so that a run can return 8 k bytes per column instead of all logits. */
+int q38b_pass_op_topk(q38b_pass* pass, int src_f32, int off, int n, int k, int dst_f32);
 /* After q38b_peer_connect the fp32 buffers of a pass live in the arena and matvec steps push their outputs to every
  * peer; q38b_pass_op_barrier then makes them usable on all ranks.  One barrier may cover several matvecs. */
 int q38b_pass_op_barrier(q38b_pass* pass);

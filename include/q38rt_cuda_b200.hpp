@@ -173,6 +173,17 @@ void gemm_f16(void* cublas, const __half* W, int N, int K, const __half* X, int 
     if (rc != Q38B_OK) b200::fatal("gemm_f16", rc);
 }
 
+#if defined(Q38RT_B200_WITH_TOPK)
+// topk of the sampling step (src/cuda/ops.cuh:142-144 of the reference project), for builds that also drop it from
+// src/cuda/ops.cu: the same result (values descending, equal values by ascending position); `work` is not used.
+void topk(const float* logits, int n, int k, int index_offset, float* vals, int* idx, void* work, cudaStream_t st) {
+    (void)work;
+    const int rc = q38b_topk(b200::context(), logits, n, n, 1, k, index_offset, vals, idx, k, (void*)st);
+    if (rc != Q38B_OK) b200::fatal("topk", rc);
+}
+size_t topk_work_bytes(int) { return 16; }
+#endif
+
 // The GEMM needs no library handle or workspace here; the runtime still gets a non-null token to pass around.
 void* cublas_create() { return b200::context(); }
 bool cublas_bind(void* cublas, cudaStream_t, void*, size_t) { return cublas != nullptr; }

@@ -187,3 +187,22 @@ def act_q8_dequant(q, d):
     """The activations an ActQ8 row stands for: d[k / 32] * q[k], float32 [n_rows, K]."""
     n, K = q.shape
     return (q.reshape(n, K // 32, 32).astype(np.float32) * d[:, :, None]).reshape(n, K)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# top-k of the output head's logits (src/cuda/ops.cuh:142-144 of the reference project; its test orders by value
+# descending, tests/kernels/test_ops.cu:425-447): values descending, equal values by ascending position, NaN last.
+# ---------------------------------------------------------------------------------------------------------------
+def topk(logits, k, index_offset=0):
+    """logits float32 [rows, n] -> (values float32 [rows, k], positions int32 [rows, k]); slots past n: (NaN, -1)."""
+    x = np.ascontiguousarray(logits, np.float32)
+    rows, n = x.shape
+    vals = np.full((rows, k), np.nan, np.float32)
+    idx = np.full((rows, k), -1, np.int32)
+    for r in range(rows):
+        key = np.where(np.isnan(x[r]), -np.inf, x[r].astype(np.float64))
+        nan_last = np.isnan(x[r]).astype(np.int8)
+        order = np.lexsort((np.arange(n), -key, nan_last))[:k]   # last key is the primary one
+        vals[r, :len(order)] = x[r, order]
+        idx[r, :len(order)] = order + index_offset
+    return vals, idx

@@ -92,6 +92,8 @@ def load_library():
     lib.q38b_add_rmsnorm_q8k.argtypes = [vp, vp, vp, vp, vp, i32, ll, i32, C.c_float, vp, vp, ll, vp]
     lib.q38b_gemv_bf16.argtypes = [vp, vp, i32, i32, vp, vp, vp]
     lib.q38b_swiglu_rows_inplace.argtypes = [vp, vp, vp, i32, i32, ll, i32, vp]
+    lib.q38b_topk.argtypes = [vp, vp, ll, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.q38b_pass_op_topk.argtypes = [vp, i32, i32, i32, i32, i32]
     lib.q38b_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
     lib.q38b_gguf_close.argtypes = [vp]
     lib.q38b_gguf_find.argtypes = [vp, C.c_char_p]
@@ -260,6 +262,15 @@ class Context:
         self._rc(self.lib.q38b_gemv_bf16(self.h, W.data_ptr(), K, N, x.data_ptr(), y.data_ptr(), _stream()), "q38b_gemv_bf16")
         return y
 
+    def topk(self, logits, k, index_offset=0):
+        """The k largest of each row of `logits` [rows, n] (fp32, device): (values [rows, k], positions [rows, k] int32)."""
+        rows, n = logits.shape
+        vals = torch.empty((rows, k), dtype=torch.float32, device=logits.device)
+        idx = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+        self._rc(self.lib.q38b_topk(self.h, logits.data_ptr(), logits.stride(0), n, rows, k, index_offset, vals.data_ptr(),
+                                    idx.data_ptr(), k, _stream()), "q38b_topk")
+        return vals, idx
+
     def swiglu_rows_inplace(self, G, U, n, kind):
         """G, U float32 [B, ld]; writes silu(G[:, :n]) * U[:, :n] over the start of every row of G as 16-bit floats."""
         self._rc(self.lib.q38b_swiglu_rows_inplace(self.h, G.data_ptr(), U.data_ptr(), G.shape[0], n, G.stride(0), kind, _stream()),
@@ -399,6 +410,9 @@ class Pass:
     def set_merge(self, enabled):
         """enabled=False: single-column runs launch one kernel per recorded step (no shared launches, no folded quantize)."""
         self.ctx._rc(self.lib.q38b_pass_set_merge(self.h, int(bool(enabled))), "q38b_pass_set_merge")
+
+    def topk(self, src, off, n, k, dst):
+        self.ctx._rc(self.lib.q38b_pass_op_topk(self.h, src, off, n, k, dst), "q38b_pass_op_topk")
 
     def debug_set_fuse_swiglu(self, enabled):
         """Test hook: enabled=False keeps SwiGLU steps as kernels of their own."""

@@ -11,6 +11,7 @@
 #include "q38b_act.cuh"
 #include "q38b_internal.h"
 #include "q38b_gemv.cuh"
+#include "q38b_topk.cuh"
 #include "q38b_gemv1.cuh"
 
 using namespace q38b;
@@ -390,10 +391,13 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
         if (cudaGetSymbolAddress((void**)&t16[0], q38b_iq2xxs_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[1], q38b_iq2xs_codes) != cudaSuccess ||
             cudaGetSymbolAddress((void**)&t16[2], q38b_iq2s_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[3], q38b_iq1s_codes) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         for (int i = 0; i < 4; i++) c->d_code16[i] = (const uint32_t*)t16[i];
+        // candidate lists of q38b_topk: 8 columns x TOPK_MAX_CHUNKS lists x TOPK_MAX_K pairs (1.5 MB), so that the decode path never allocates
+        if (cudaMalloc(&c->d_topk, (size_t)8 * TOPK_MAX_CHUNKS * TOPK_MAX_K * sizeof(TopkPair)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
     } while (0);
     if (rc != Q38B_OK) {
         c->last_cuda = (int)cudaGetLastError();
         if (c->d_status) cudaFree(c->d_status);
+        if (c->d_topk) cudaFree(c->d_topk);
         delete c;
         return rc;
     }
@@ -404,6 +408,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
 void q38b_ctx_destroy(q38b_ctx* ctx) {
     if (!ctx) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_topk) cudaFree(ctx->d_topk);
     if (ctx->d_flags) cudaFree(ctx->d_flags);
     delete ctx;
 }
@@ -572,6 +577,25 @@ int q38b_gemv_bf16(q38b_ctx* ctx, const void* W_bf16, int K, int N, const float*
     if (!ctx || !W_bf16 || !x || !y || K <= 0 || K % 8 || N < 1) return Q38B_ERR_ARG;
     if (((uintptr_t)W_bf16 & 15) || ((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return Q38B_ERR_ALIGN;
     gemv_bf16_kernel<<<(unsigned)N, BF16_THREADS, 0, (cudaStream_t)stream>>>((const uint16_t*)W_bf16, K, N, x, y);
+    Q38B_CUDA(ctx, cudaGetLastError());
+    return Q38B_OK;
+}
+
+int q38b_topk(q38b_ctx* ctx, const float* logits, long long ld, int n, int n_rows, int k, int index_offset, float* vals, int* idx, int out_ld,
+              void* stream) {
+    if (!ctx || !logits || !vals || !idx || n < 1 || n_rows < 1 || n_rows > 8 || k < 1 || k > TOPK_MAX_K || out_ld < k) return Q38B_ERR_ARG;
+    if (n_rows > 1 && ld < n) return Q38B_ERR_ARG;
+    const int n_chunks = (n + TOPK_CHUNK - 1) / TOPK_CHUNK;
+    if (n_chunks > TOPK_MAX_CHUNKS) return Q38B_ERR_UNSUPPORTED;
+    if (((uintptr_t)logits & 3) || ((uintptr_t)vals & 3) || ((uintptr_t)idx & 3)) return Q38B_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)n_chunks * k * sizeof(TopkPair);
+    const int rc = ensure_kernel_smem(ctx, (const void*)topk_merge_kernel, ctx->smem_optin, false);
+    if (rc != Q38B_OK) return rc;
+    TopkPair* lists = (TopkPair*)ctx->d_topk;
+    topk_lists_kernel<<<dim3((unsigned)((n_chunks + TOPK_STAGE1_WARPS - 1) / TOPK_STAGE1_WARPS), (unsigned)n_rows), TOPK_STAGE1_WARPS * 32, 0, st>>>(
+        logits, ld, n, k, lists, n_chunks);
+    topk_merge_kernel<<<(unsigned)n_rows, 32 * TOPK_LISTS_PER_LANE, smem, st>>>(lists, n_chunks, k, logits, ld, index_offset, vals, idx, (long long)out_ld);
     Q38B_CUDA(ctx, cudaGetLastError());
     return Q38B_OK;
 }

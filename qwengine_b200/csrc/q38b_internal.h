@@ -17,6 +17,7 @@ struct q38b_ctx {
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     long long wait_budget_cycles = 4000000000LL;   // bounded waits on other GPUs (q38b_ctx_set_wait_budget_cycles)
     int* d_status = nullptr;
+    void* d_topk = nullptr;    // work area of q38b_topk (candidate lists)
     uint32_t* d_cb_iq3xxs = nullptr;
     uint32_t* d_cb_iq3s = nullptr;
     const uint32_t* d_code16[4] = {};   // 16-bit grid codes of IQ2_XXS, IQ2_XS, IQ2_S, IQ1_S / IQ1_M (two per word)

@@ -51,7 +51,7 @@ Nccl& nccl() {
 }
 constexpr int NCCL_FLOAT = 7;
 
-enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER, OP_BARRIER };
+enum OpKind { OP_QUANT, OP_GEMV, OP_SWIGLU, OP_GATHER, OP_BARRIER, OP_TOPK };
 struct Op { int kind, a, b, c, d, n, off; };
 struct Buf { void* ptr; int n; bool q8k; void* peer[8]; int n_peer_ranks; bool in_arena; };
 struct Mat { uint32_t type; const void* W; size_t row_bytes; int K, M; bool owned; };
@@ -355,6 +355,12 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                                      d.n / 256, st);
                 break;
             }
+            case OP_TOPK: {   // a: logits buffer, off: first logit, n: how many, d: k, b: destination (k values, then k positions as int bits)
+                const Buf& s = p->bufs[o.a];
+                const Buf& d = p->bufs[o.b];
+                rc = q38b_topk(ctx, (const float*)s.ptr + o.off, s.n, o.n, nb, o.d, 0, (float*)d.ptr, (int*)d.ptr + o.d, d.n, st);
+                break;
+            }
             case OP_BARRIER: {
                 if (n_barriers == 0) break;
                 if (ctx->pending_sync_seq >= 0) {   // two barriers in a row: the earlier one runs by itself
@@ -581,6 +587,15 @@ int q38b_pass_op_gemv(q38b_pass* p, int mat, int src, int dst, int off) {
     return Q38B_OK;
 }
 
+int q38b_pass_op_topk(q38b_pass* p, int src, int off, int n, int k, int dst) {
+    if (!p || !is_f32(p, src) || !is_f32(p, dst) || src == dst || off < 0 || n < 1 || off + n > p->bufs[src].n || k < 1 || k > 64 ||
+        p->bufs[dst].n < 2 * k)
+        return Q38B_ERR_ARG;
+    if ((n + 1023) / 1024 > 384) return Q38B_ERR_UNSUPPORTED;
+    p->ops.push_back({OP_TOPK, src, dst, 0, k, n, off});
+    return Q38B_OK;
+}
+
 int q38b_pass_op_swiglu(q38b_pass* p, int g, int g_off, int u, int u_off, int n, int dst) {
     if (!p || !is_f32(p, g) || !is_f32(p, u) || !is_q8k(p, dst) || n % 256 || g_off < 0 || u_off < 0) return Q38B_ERR_ARG;
     if (g_off + n > p->bufs[g].n || u_off + n > p->bufs[u].n || p->bufs[dst].n < n || p->bufs[g].n != p->bufs[u].n) return Q38B_ERR_ARG;
@@ -718,6 +733,7 @@ int q38b_pass_kernel_count(const q38b_pass* p) {
     for (size_t i = 0; i < p->ops.size(); i++) {
         const Op& o = p->ops[i];
         n += !skip[i] && (o.kind != OP_GATHER) && (o.kind != OP_BARRIER || p->ctx->n_ranks > 1);
+        n += o.kind == OP_TOPK;   // two kernels
     }
     return n + (int)merged.size();
 }

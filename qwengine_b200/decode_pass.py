@@ -6,7 +6,8 @@ Gated-DeltaNet layer (in_proj 16384 x 5120, out 5120 x 6144), every fourth a gat
 12288 x 5120, k and v 1024 x 5120, o 5120 x 6144), each followed by the FFN (gate, up 17408 x 5120, SwiGLU, down
 5120 x 17408), then the 248320 x 5120 output head.  The recurrence / attention between the projections is not
 part of this path: the first 6144 outputs of the input projection stand in for its result, so that every matvec
-still consumes data produced by the step before it.
+still consumes data produced by the step before it.  The FFN output of the last layer feeds the head; the other
+layers' FFN outputs end in a buffer of their own (see build).
 
 Sharding (one process per GPU): rank g of G owns rows [g*M/G, (g+1)*M/G) of every matrix and the fp32 output
 slices are all-gathered so that each rank holds the full vector for the next matvec.
@@ -19,6 +20,7 @@ from . import formats as F
 
 HIDDEN, FF, INNER, VOCAB = 5120, 17408, 6144, 248320
 N_LAYERS = 64
+TOPK = 32          # candidates the sampler takes from the head (TK of the reference, src/cuda/ops.cu:821)
 # fp16 super-scale magnitudes at which a matvec of uniformly random (zero-mean, see synth.ZERO_MEAN_DMIN) blocks has
 # a gain near 1, so that the 64 chained layers of the synthetic pass stay inside the fp32 range
 UNIT_GAIN_SCALE = {"Q4_K": 5.0e-5, "IQ3_XXS": 1.4e-4, "IQ4_XS": 5.5e-6, "Q6_K": 1.0e-5}
@@ -79,6 +81,7 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
     iq = ps.buffer_q8k(INNER)
     gu = ps.buffer_f32(2 * FF)             # gate | up
     hq = ps.buffer_q8k(FF)
+    ffn = ps.buffer_f32(HIDDEN)            # FFN block outputs (see below)
     logits = ps.buffer_f32(VOCAB) if head else None
     peer = world > 1 and gather == "peer"   # needs Context.peer_connect before the pass is created
     if hasattr(ps, "set_peer_store"):
@@ -116,13 +119,23 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
         matvec(up, xq, gu, FF)
         sync()
         ps.swiglu(gu, 0, gu, FF, FF, hq)
-        matvec(down, hq, x, 0)
+        # The FFN block's output goes to a buffer of its own, not back into x (except in the last layer, so that the
+        # pass's result depends on it): without the model's RMSNorm in front of it, silu(g) * u squares the scale of
+        # the stream at every layer and 64 chained layers leave the fp32 range whatever the weight scales are.  The
+        # chain x -> projections -> x stays linear (gain near 1 per layer).
+        matvec(down, hq, x if il == n_layers - 1 else ffn, 0)
         sync()
+    best = None
     if head:
         ps.quantize(x, 0, HIDDEN, xq)
         matvec(MatSpec("lm_head", "Q6_K", VOCAB, HIDDEN), xq, logits, 0)
         sync()
-    return dict(in_buf=x_in, out_buf=logits if head else x, out_len=VOCAB if head else HIDDEN)
+        if hasattr(ps, "topk"):
+            # what the sampler needs from the head (Engine::decode_batch's top-k, src/runtime/engine.cpp:1680 of the
+            # reference project): TOPK values and positions per column instead of 248320 logits
+            best = ps.buffer_f32(2 * TOPK)
+            ps.topk(logits, 0, VOCAB, TOPK, best)
+    return dict(in_buf=x_in, out_buf=logits if head else x, out_len=VOCAB if head else HIDDEN, topk_buf=best, topk_k=TOPK)
 
 
 def oracle_forward(port, weights, x, n_layers, head=True):
@@ -141,7 +154,9 @@ def oracle_forward(port, weights, x, n_layers, head=True):
         g = port.gemv(F.get(gate.fmt).type_id, weights[gate.name], xq, HIDDEN)
         u = port.gemv(F.get(up.fmt).type_id, weights[up.name], xq, HIDDEN)
         h = port.swiglu(g, u).reshape(nb, FF)
-        x = port.gemv(F.get(down.fmt).type_id, weights[down.name], port.quantize_q8k(h), FF)
+        y = port.gemv(F.get(down.fmt).type_id, weights[down.name], port.quantize_q8k(h), FF)
+        if il == n_layers - 1:
+            x = y
     if head:
         return port.gemv(F.Q6_K.type_id, weights["lm_head"], port.quantize_q8k(x), HIDDEN)
     return x

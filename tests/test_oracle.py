@@ -119,3 +119,11 @@ def test_fp16_conversion_exhaustive():
     finite = np.isfinite(theirs)
     back = np.array([lib.q38o_fp32_to_fp16(float(v)) for v in theirs[finite]], np.uint16)
     assert np.array_equal(back, h[finite])
+
+
+def test_topk_order():
+    """oracle.topk: values descending, equal values by ascending position, NaN last, (NaN, -1) past the end."""
+    x = np.array([[1.0, 5.0, 5.0, np.nan, -np.inf, 0.0, -0.0, 7.0]], np.float32)
+    v, i = oracle.topk(x, 10, index_offset=100)
+    assert i[0].tolist() == [107, 101, 102, 100, 105, 106, 104, 103, -1, -1]
+    assert v[0, 0] == 7.0 and np.isnan(v[0, 7]) and np.isnan(v[0, 9])
