@@ -141,7 +141,9 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
 }
 
 constexpr int G1_WARPS = 8;                  // consumer warps of a CTA when two CTAs share an SM
-constexpr int G1_WARPS_ONE = 16;             // ... when a CTA has the SM to itself
+// ... when a CTA has the SM to itself (measured on B200: the row-group decoder wants its 80 registers, which 20 warps
+// leave it; the others gain from more warps in flight, 5120 x 17408 IQ4_XS 15.7 -> 12.5 us)
+constexpr int G1_WARPS_ONE = 24, G1_WARPS_ONE_RG = 20;
 constexpr int G1_SMEM_BUDGET = 113 * 1024;   // two CTAs per SM (228 KB of shared memory per SM, 1 KB reserved per CTA)
 
 
@@ -161,10 +163,10 @@ bool rowgroup_eligible(uint32_t type, size_t row_bytes, int rows) { return type 
 // per-tile slice sums | ring of stages (8 row slots of one 1024-weight slice each).
 int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, int G1_ROWS, int occ, Plan1* p) {
     const int bb = block_bytes((int)type);
-    const int warps = occ == 1 ? G1_WARPS_ONE : G1_WARPS;
     p->occ = occ;
     const int nsb = K / 256;
     const int rg = ctx->rowgroup && rowgroup_eligible(type, row_bytes, G1_ROWS) ? 1 : 0;
+    const int warps = occ == 1 ? (rg ? G1_WARPS_ONE_RG : G1_WARPS_ONE) : G1_WARPS;
     const int cb_entries = rg ? 0 : type == T_IQ3_XXS ? 256 : type == T_IQ3_S ? 512 : 0;   // row groups keep their tables in static shared memory
     const int budget = (occ == 1 ? ctx->smem_optin : std::min(ctx->smem_optin, G1_SMEM_BUDGET)) - 128 - (rg ? RG_STATIC_BYTES : 0);
     Gemv1Args& a = p->a;
@@ -248,7 +250,7 @@ int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_m
 
 template <int FMT, int ROWS, bool RG, bool A32 = false, int OCC = 2>
 int launch_gemv1_rows(q38b_ctx* ctx, const Plan1& p, cudaStream_t st) {
-    constexpr int WARPS = OCC == 1 ? G1_WARPS_ONE : G1_WARPS;
+    constexpr int WARPS = OCC == 1 ? (RG ? G1_WARPS_ONE_RG : G1_WARPS_ONE) : G1_WARPS;
     auto kern = gemv1_kernel<FMT, WARPS, ROWS, RG, A32, OCC>;
     const int rc = ensure_kernel_smem(ctx, (const void*)kern, (OCC == 1 ? ctx->smem_optin : G1_SMEM_BUDGET) - (RG ? RG_STATIC_BYTES : 0), true);
     if (rc != Q38B_OK) return rc;
