@@ -173,7 +173,7 @@ class Context:
         self._rc(self.lib.q38b_debug_set_rowgroup(self.h, int(bool(enabled))), "q38b_debug_set_rowgroup")
 
     def debug_set_one_cta(self, mode):
-        """Test hook: one CTA per SM for the one-column kernel: 0 never, 1 chosen shapes, 2 always."""
+        """Test hook: one CTA per SM for the one-column kernel: 0 never, otherwise wherever such a plan fits (default)."""
         self._rc(self.lib.q38b_debug_set_one_cta(self.h, int(mode)), "q38b_debug_set_one_cta")
 
     def set_wait_budget_cycles(self, cycles):

@@ -227,12 +227,12 @@ int plan_gemv1_rows(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, in
 // Rows per tile: the largest of 8, 4, 2 that can be planned.  Measured on B200 for every shape of the benchmark pass,
 // eight rows win even where fewer rows would balance the CTAs better or let a tile be fetched by one copy: the cost per
 // (tile, slice) unit (activation loads, waits, lane reduction) outweighs both.
-// One CTA per SM (ctx->one_cta: 0 never, 1 where it was measured faster, 2 always): row groups take 16-row tiles there.
+// One CTA per SM with three times the consumer warps (ctx->one_cta, on by default) is tried first: one set of tables and
+// one quantized column per SM, deeper rings, 16-row tiles for the row groups.  Measured on B200 it is faster than two
+// CTAs per SM for every shape of the benchmark pass (4.23 ms against 4.30 ms with only long rows and row groups on it,
+// 5.2 ms with none); the two-CTA plans remain for shapes whose one-CTA plan does not fit.
 int plan_gemv1(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_mats, size_t row_bytes, Plan1* best) {
-    const bool long_rows = q38b_row_bytes(type, K) > 6000;
-    const bool table_heavy = ctx->rowgroup && rowgroup_eligible(type, row_bytes, 8);
-    const bool one = ctx->one_cta == 2 || (ctx->one_cta == 1 && (long_rows || table_heavy));
-    if (one) {
+    if (ctx->one_cta) {
         const int cands1[4] = {16, 8, 4, 2};
         for (int rows : cands1) {
             if (rows == 16 && !(ctx->rowgroup && rowgroup_eligible(type, row_bytes, 16))) continue;
@@ -448,10 +448,10 @@ int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
     ctx->rowgroup = enabled ? 1 : 0;
     return Q38B_OK;
 }
-// Test hook: one CTA per SM for the one-column kernel: 0 never, 1 for the shapes it was measured faster on, 2 always.
+// Test hook: one CTA per SM for the one-column kernel: 0 never, otherwise wherever such a plan fits (the default).
 int q38b_debug_set_one_cta(q38b_ctx* ctx, int mode) {
     if (!ctx || mode < 0 || mode > 2) return Q38B_ERR_ARG;
-    ctx->one_cta = mode;
+    ctx->one_cta = mode ? 1 : 0;
     return Q38B_OK;
 }
 // Test hook: enabled = 1 starts counting one-column launches whose CTAs fit an SM less often than their plan assumes;

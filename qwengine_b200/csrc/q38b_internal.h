@@ -12,7 +12,7 @@ struct q38b_ctx {
     int pass_pdl = 1;          // programmatic dependent launch between the kernels of a recorded pass
     int static_weights = 0;    // 1: matvec producers start streaming W before the previous kernel of the stream has finished
     int rowgroup = 1;          // 0: the row-group mapping of the one-column kernel is not used (test hook q38b_debug_set_rowgroup)
-    int one_cta = 1;           // one-column kernel with one CTA per SM: 0 never, 1 chosen shapes, 2 always (test hook q38b_debug_set_one_cta)
+    int one_cta = 1;           // one-column kernel with one CTA per SM where such a plan fits; 0: never (test hook q38b_debug_set_one_cta)
     int check_occupancy = 0, occupancy_shortfalls = 0;   // test hook q38b_debug_occupancy_shortfalls
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     long long wait_budget_cycles = 4000000000LL;   // bounded waits on other GPUs (q38b_ctx_set_wait_budget_cycles)
