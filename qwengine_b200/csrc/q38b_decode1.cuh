@@ -622,8 +622,21 @@ Q38B_HD int actr_pos(int j, int negated) { return (2 * negated + ((j >> 4) & 1))
 constexpr int ACTR_BLOCK_BYTES = 512;
 
 // tables of the row-group decoders in shared memory: codebook entry e, replica l at cb + e * 128 + l * 4; sign
-// selectors of code c, replica l at sgn + c * 128 + l * 4
-struct TablesR { SP cb_lane; SP sgn_lane; };   // bases with 4 * lane already added
+// selectors of code c, replica l at sgn + c * 128 + l * 4.  The lane's offset (bits 2..6) is OR-ed into the entry's
+// offset (bits 7 and up) by the same LOP3 that masks the entry number out of its word, and the table bases are the
+// addresses of static arrays, i.e. immediates of the loads: a look-up costs a shift, a LOP3 and the load.
+struct TablesR { SP cb; SP sgn; uint32_t lane4; };   // bases of the tables; 4 * lane
+// offset of this lane's replica of the entry whose number starts at bit `bit` of w: the number moved to bit 7, masked, | lane4
+Q38B_HD uint32_t entry_offset(uint32_t w, int bit, uint32_t mask, uint32_t lane4) {
+    const uint32_t moved = bit < 7 ? (w << (7 - bit)) : (w >> (bit - 7));
+#if defined(__CUDA_ARCH__)
+    uint32_t r;   // written as the instruction: the compiler would turn the OR of disjoint bits back into an add and hoist lane4 into the base
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(moved), "r"(mask), "r"(lane4));
+    return r;
+#else
+    return (moved & mask) | lane4;
+#endif
+}
 
 struct ActsR { uint32_t q[8], nq[8]; float dx; };
 
@@ -670,11 +683,10 @@ template <> struct GranR<T_IQ3_XXS> {
         int sum = 0;
 #pragma unroll
         for (int l = 0; l < 4; l++) {
-            const uint32_t c128 = (l == 0 ? (aux << 7) : (aux >> (7 * l - 7))) & 0x3F80u;
-            const uint32_t sel = sp_ld32(t.sgn_lane + (int)c128);
+            const uint32_t sel = sp_ld32(t.sgn + (int)entry_offset(aux, 7 * l, 0x3F80u, t.lane4));
             const uint32_t w = l < 2 ? i0 : i1;
-            const uint32_t g0 = sp_ld32(t.cb_lane + (int)byte_x128(w, 2 * (l & 1)));
-            const uint32_t g1 = sp_ld32(t.cb_lane + (int)byte_x128(w, 2 * (l & 1) + 1));
+            const uint32_t g0 = sp_ld32(t.cb + (int)entry_offset(w, 16 * (l & 1), 0x7F80u, t.lane4));
+            const uint32_t g1 = sp_ld32(t.cb + (int)entry_offset(w, 16 * (l & 1) + 8, 0x7F80u, t.lane4));
             sum = dp4a_us(g0, prmt(a.q[2 * l], a.nq[2 * l], sel), sum);
             sum = dp4a_us(g1, prmt(a.q[2 * l + 1], a.nq[2 * l + 1], sel >> 16), sum);
         }

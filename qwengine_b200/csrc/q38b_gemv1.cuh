@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
     Codebook1 cb;                                    // 32 replicas: lane l reads bank l
     cb.lane_base = sp_from(cbw) + 4 * (lane & ((1 << cb1_rep_log2(FMT)) - 1));
     cb.sign_base = sp_from(smem + a.off_sgn) + 8 * (lane & 15);
-    const TablesR tabs{sp_from(rg_cb) + 4 * lane, sp_from(rg_sgn) + 4 * lane};
+    const TablesR tabs{sp_from(rg_cb), sp_from(rg_sgn), 4u * (uint32_t)lane};
     const SP actq_sp = sp_from(actq), actd_sp = sp_from(actd);
     const SP stage0_sp = sp_from(smem + a.off_stage);
     float* red = (float*)(smem + a.off_red);         // [n_tilebuf][n_slices][8]

@@ -261,7 +261,7 @@ void run_rowgroup(int K, const uint8_t* const* rowp, int n_rows, const uint8_t* 
                     tl_lane = lane;
                     ActsR a;
                     GranR<FMT>::load_acts(a, sp_from(act + (size_t)sb * ACTR_BLOCK_BYTES), sp_from(actd + sb * 8), s);
-                    const TablesR t{sp_from(cb) + 4 * lane, sp_from(sgn) + 4 * lane};
+                    const TablesR t{sp_from(cb), sp_from(sgn), 4u * (uint32_t)lane};
                     const uint8_t* row = rowp[r] + (size_t)sl * 4 * GranR<FMT>::BB;
                     float v = 0;
                     switch (b) {
