@@ -194,18 +194,18 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
     uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
     constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
     if (RG) {
-        // thread e writes the 32 replicas of codebook entry e (and of sign code e): eight 16-byte stores each
-        for (int e = ctid; e < 256; e += NWARPS * 32) {
-            const uint32_t v = a.codebook[e];
-            uint4* dst = (uint4*)(rg_cb + 32 * e);
+        // the 32 replicas of an entry are 128 bytes: thread t writes 16 of them, so that a warp's store covers 512
+        // consecutive bytes (entries by the thread would put all 32 lanes on the same four banks)
+        constexpr int NT = NWARPS * 32, CB_ROUNDS = (256 * 8 + NT - 1) / NT;
+        uint32_t cbv[CB_ROUNDS];
 #pragma unroll
-            for (int i = 0; i < 8; i++) dst[i] = make_uint4(v, v, v, v);
-        }
-        for (int c = ctid; c < 128; c += NWARPS * 32) {
-            const uint32_t v = ksign_selectors((uint32_t)c);
-            uint4* dst = (uint4*)(rg_sgn + 32 * c);
+        for (int i = 0; i < CB_ROUNDS; i++) cbv[i] = a.codebook[min(ctid + i * NT, 256 * 8 - 1) >> 3];   // the loads go out together
 #pragma unroll
-            for (int i = 0; i < 8; i++) dst[i] = make_uint4(v, v, v, v);
+        for (int i = 0; i < CB_ROUNDS; i++)
+            if (ctid + i * NT < 256 * 8) ((uint4*)rg_cb)[ctid + i * NT] = make_uint4(cbv[i], cbv[i], cbv[i], cbv[i]);
+        for (int t = ctid; t < 128 * 8; t += NWARPS * 32) {
+            const uint32_t v = ksign_selectors((uint32_t)t >> 3);
+            ((uint4*)rg_sgn)[t] = make_uint4(v, v, v, v);
         }
     } else if (CBN > 0) {
         const int rep = 1 << a.cb_rep_log2;
