@@ -116,6 +116,16 @@ Q38B_HD uint32_t byte_x64(uint32_t w, int k) { return (k == 0 ? (w << 6) : (w >>
 // IQ3_S (512 entries) 16, lanes l and l + 16 share a replica (32 KB instead of 64)
 Q38B_HD constexpr int cb1_rep_log2(int fmt) { return fmt == T_IQ3_S ? 4 : fmt == T_IQ3_XXS ? 5 : 0; }
 
+// Staged int8 activations of a 1024-weight slice: the chunks that the lanes of a warp fetch with ONE load instruction
+// are consecutive (16 bytes per lane, 8 for Q6_K), so that the load is served in the fewest wavefronts; in the natural
+// order a lane's 32 (or 64) bytes are consecutive and eight lanes meet on the same banks.  k: byte of the slice in the
+// format's own order (after act_stage_pos); result: its place in the staged slice.
+Q38B_HD constexpr int act_slice_pos(int fmt, int k) {
+    if (fmt == T_Q4_K || fmt == T_Q5_K) return ((k >> 4) & 3) * 256 + (k >> 6) * 16 + (k & 15);   // lane pair pr = k / 64, chunk i
+    if (fmt == T_Q6_K) return ((k >> 5) & 3) * 256 + ((k >> 8) * 8 + ((k >> 7) & 1) * 4 + ((k >> 3) & 3)) * 8 + (k & 7);   // (sb, n, i) = lane, j
+    return ((k >> 4) & 1) * 512 + (k >> 5) * 16 + (k & 15);   // lane = k / 32, half
+}
+
 // what a lane needs from the activations for one slice
 template <int NWORDS> struct ActRegs {
     uint32_t q[NWORDS];   // int8 activations of the granule, in the format's staged order
@@ -137,9 +147,9 @@ template <> struct Gran<T_IQ3_XXS> {
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32) * 0.25f;
     }
@@ -178,9 +188,9 @@ template <> struct Gran<T_IQ3_S> {
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
@@ -221,9 +231,9 @@ template <> struct Gran<T_IQ4_XS> {
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
@@ -265,7 +275,7 @@ template <int NBITS> struct GranQ45K {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             uint32_t v[4];
-            sp_ld128(aq, 64 * pr + 16 * i, v);
+            sp_ld128(aq, 256 * i + 16 * pr, v);
             a.q[4 * i] = v[0]; a.q[4 * i + 1] = v[1]; a.q[4 * i + 2] = v[2]; a.q[4 * i + 3] = v[3];
         }
         a.dx = sp_ldf(ad, A32 ? 8 * pr : (pr >> 2) * 32);
@@ -342,7 +352,7 @@ template <> struct Gran<T_Q6_K> {
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         const int sb = lane >> 3, n = (lane >> 2) & 1, i = lane & 3;
 #pragma unroll
-        for (int j = 0; j < 4; j++) sp_ld64(aq, 256 * sb + 128 * n + 32 * j + 8 * i, a.q[2 * j], a.q[2 * j + 1]);
+        for (int j = 0; j < 4; j++) sp_ld64(aq, 256 * j + 8 * lane, a.q[2 * j], a.q[2 * j + 1]);
         a.dx = sp_ldf(ad, sb * 32);
 #pragma unroll
         for (int j = 0; j < 4; j++) a.dxs[j] = A32 ? sp_ldf(ad, sb * 32 + 16 * n + 4 * j) : a.dx;
@@ -387,9 +397,9 @@ template <> struct Gran<T_Q8_0> {
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
@@ -444,9 +454,9 @@ template <int FMT> struct GranPlain {   // the common activation side: one 32-we
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
     }
@@ -560,9 +570,9 @@ template <> struct Gran<T_Q2_K> {
     template <bool A32>
     static Q38B_HD void load_acts(Acts& a, SP aq, SP ad, int lane) {
         uint32_t v[4];
-        sp_ld128(aq, 32 * lane, v);
+        sp_ld128(aq, 16 * lane, v);
         a.q[0] = v[0]; a.q[1] = v[1]; a.q[2] = v[2]; a.q[3] = v[3];
-        sp_ld128(aq, 32 * lane + 16, v);
+        sp_ld128(aq, 512 + 16 * lane, v);
         a.q[4] = v[0]; a.q[5] = v[1]; a.q[6] = v[2]; a.q[7] = v[3];
         a.dx = sp_ldf(ad, A32 ? 4 * lane : (lane >> 3) * 32);
         a.bs0 = 0; a.bs1 = 0;

@@ -268,7 +268,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                     q8k_block_core(v, w0, w1, s8, d);
                 }
                 if (lane == 0) actd[sb * 8] = d;
-                uint8_t* dst = actq + sb * 256;
+                uint8_t* dst = actq + (sb >> 2) * 1024;   // the block's slice
+                const int k0 = (sb & 3) * 256 + 8 * lane;    // this lane's eight values in the slice
                 if (RG) {
                     uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
                     *(uint2*)(blk + actr_pos(8 * lane, 0)) = make_uint2(w0, w1);
@@ -276,11 +277,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                 } else if (FMT == T_IQ4_XS) {
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        const int k = 8 * lane + e;
-                        dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
+                        const int k = k0 + e;
+                        dst[act_slice_pos(FMT, (k & ~31) + act_stage_pos(FMT, k & 31))] = (uint8_t)((e < 4 ? w0 : w1) >> (8 * (e & 3)));
                     }
                 } else {
-                    *(uint2*)(dst + 8 * lane) = make_uint2(w0, w1);
+                    *(uint2*)(dst + act_slice_pos(FMT, k0)) = make_uint2(w0, w1);
                 }
             }
         }
@@ -294,7 +295,8 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
     for (int i = ctid; i < a.n_slices * 256; i += NWARPS * 32) {   // word i of the (zero padded) activation vector
         const int sb = i >> 6, wi = i & 63;
         const uint32_t v = sb >= a.nsb ? 0u : A32 ? *(const uint32_t*)(a.xq + 4 * (size_t)i) : *(const uint32_t*)(a.xq + (size_t)sb * Q8K_BYTES + 4 + 4 * wi);
-        uint8_t* dst = actq + sb * 256;
+        uint8_t* dst = actq + (sb >> 2) * 1024;   // the block's slice
+        const int k0 = (sb & 3) * 256 + 4 * wi;      // this word's four values in the slice
         if (RG) {
             uint8_t* blk = actq + sb * ACTR_BLOCK_BYTES;
             *(uint32_t*)(blk + actr_pos(4 * wi, 0)) = v;
@@ -302,11 +304,11 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
         } else if (FMT == T_IQ4_XS) {
 #pragma unroll
             for (int b = 0; b < 4; b++) {
-                const int k = 4 * wi + b;
-                dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)(v >> (8 * b));
+                const int k = k0 + b;
+                dst[act_slice_pos(FMT, (k & ~31) + act_stage_pos(FMT, k & 31))] = (uint8_t)(v >> (8 * b));
             }
         } else {
-            *(uint32_t*)(dst + 4 * wi) = v;
+            *(uint32_t*)(dst + act_slice_pos(FMT, k0)) = v;
         }
     }
     }

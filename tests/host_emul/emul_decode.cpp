@@ -201,11 +201,11 @@ static int emul_gemv1_any(int fmt, int K, const uint8_t* W, int n_rows, const ui
         const uint8_t* blk = xq + (size_t)sb * 292;
         if (d32) {
             for (int j = 0; j < 8; j++) actd[sb * 8 + j] = d32[sb * 8 + j];
-            for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = xq[sb * 256 + k];
+            for (int k = 0; k < 256; k++) aq[(sb >> 2) * 1024 + act_slice_pos(fmt, (sb & 3) * 256 + (k & ~31) + act_stage_pos(fmt, k & 31))] = xq[sb * 256 + k];
             continue;
         }
         memcpy(&actd[sb * 8], blk, 4);
-        for (int k = 0; k < 256; k++) aq[sb * 256 + (k & ~31) + act_stage_pos(fmt, k & 31)] = blk[4 + k];
+        for (int k = 0; k < 256; k++) aq[(sb >> 2) * 1024 + act_slice_pos(fmt, (sb & 3) * 256 + (k & ~31) + act_stage_pos(fmt, k & 31))] = blk[4 + k];
     }
     const int entries = fmt == T_IQ3_XXS ? 256 : fmt == T_IQ3_S ? 512 : 0;
     (void)rep_log2;                                        // the single-column decoders fix their replica counts
