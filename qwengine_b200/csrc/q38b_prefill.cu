@@ -31,12 +31,17 @@ namespace {
 constexpr int PF_ROWS = 128;       // weight rows per CTA (MMA M)
 constexpr int PF_NTILE = 256;      // tokens per accumulator (MMA N)
 constexpr int PF_KSLAB = 64;       // K elements per stage: one 128-byte swizzle row of bf16
-constexpr int PF_STAGES = 2;
+// The two operands have rings of their own: the dequantized weights (16 KB per slab) four deep, so that the decoders,
+// whose loads come straight from L2 / HBM, run well ahead of the tensor core; the activation tiles (64 KB per slab) two.
+constexpr int PF_A_STAGES = 4, PF_B_STAGES = 2;
 constexpr int PF_A_BYTES = PF_ROWS * PF_KSLAB * 2;        // 16 KB
 constexpr int PF_B_BYTES = PF_NTILE * PF_KSLAB * 2;       // 32 KB per accumulator
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + 2 * PF_B_BYTES;
-constexpr int PF_THREADS = 320;    // 8 decode warps + TMA warp + MMA warp
-constexpr int PF_SMEM = 1024 + PF_STAGES * PF_STAGE_BYTES + 256;
+constexpr int PF_B_STAGE_BYTES = 2 * PF_B_BYTES;
+// two groups of 8 decode warps (group g takes the slabs with slab % 2 == g: each thread has two slab times for the load
+// and the decode of its 32 weights) + TMA warp + MMA warp
+constexpr int PF_DECODE_GROUPS = 2, PF_DECODE_WARPS = 8 * PF_DECODE_GROUPS;
+constexpr int PF_THREADS = 32 * (PF_DECODE_WARPS + 2);
+constexpr int PF_SMEM = 1024 + PF_A_STAGES * PF_A_BYTES + PF_B_STAGES * PF_B_STAGE_BYTES + 256;
 
 struct PrefillArgs {
     const uint8_t* W;
@@ -161,13 +166,15 @@ template <int FMT, bool F16>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
     using OP = typename std::conditional<F16, OpF16, OpBf16>::type;
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t* full_a = (uint64_t*)smem;              // [stages] 256 decode threads arrive
-    uint64_t* full_b = full_a + PF_STAGES;           // [stages] TMA bytes
-    uint64_t* empty = full_b + PF_STAGES;            // [stages] tcgen05.commit
-    uint64_t* acc_done = empty + PF_STAGES;          // [1]
+    uint64_t* full_a = (uint64_t*)smem;              // [A stages] 256 decode threads arrive
+    uint64_t* empty_a = full_a + PF_A_STAGES;        // [A stages] tcgen05.commit
+    uint64_t* full_b = empty_a + PF_A_STAGES;        // [B stages] TMA bytes
+    uint64_t* empty_b = full_b + PF_B_STAGES;        // [B stages] tcgen05.commit
+    uint64_t* acc_done = empty_b + PF_B_STAGES;      // [1]
     uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    uint8_t* stages = smem + 1024;
+    uint8_t* stages = smem + 1024;                                   // ring of weight tiles
+    uint8_t* stages_b = stages + PF_A_STAGES * PF_A_BYTES;            // ring of activation tiles
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = blockIdx.x * PF_ROWS;
     const int tok0 = blockIdx.y * a.n_acc * PF_NTILE;
@@ -175,15 +182,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < PF_STAGES; s++) {
+        for (int s = 0; s < PF_A_STAGES; s++) {
             mbar_init(smem_u32(&full_a[s]), 256);
+            mbar_init(smem_u32(&empty_a[s]), 1);
+        }
+        for (int s = 0; s < PF_B_STAGES; s++) {
             mbar_init(smem_u32(&full_b[s]), 1);
-            mbar_init(smem_u32(&empty[s]), 1);
+            mbar_init(smem_u32(&empty_b[s]), 1);
         }
         mbar_init(smem_u32(acc_done), 1);
         mbar_fence_init();
     }
-    if (warp == 9) {   // this warp owns the tensor memory allocation (512 columns = two 128 x 256 fp32 accumulators)
+    if (warp == PF_DECODE_WARPS + 1) {   // this warp owns the tensor memory allocation (512 columns = two 128 x 256 fp32 accumulators)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -193,19 +203,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     const uint32_t tmem_base = *tmem_slot;
     if (tid == 0 && (smem_u32(stages) & 1023u)) atomicOr(a.status, ST_TMEM_TIMEOUT);   // swizzled tiles need 1024-byte alignment
 
-    if (warp < 8) {
+    if (warp < PF_DECODE_WARPS) {
         // ---------------- operand A: decode 128 rows x 64 weights per slab ----------------
-        const int r = tid >> 1, half = tid & 1;                  // row of the tile, which 32-weight half of the slab
+        const int grp = warp >> 3, t = tid & 255;
+        const int r = t >> 1, half = t & 1;                      // row of the tile, which 32-weight half of the slab
         const int grow = min(row0 + r, a.M - 1);                 // rows past the end repeat the last row (never stored)
         const uint8_t* wrow = a.W + (size_t)grow * a.row_bytes;
-        for (int slab = 0; slab < n_slabs; slab++) {
-            const int st = slab % PF_STAGES;
-            const uint32_t use = (uint32_t)(slab / PF_STAGES);
-            mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+        for (int slab = grp; slab < n_slabs; slab += PF_DECODE_GROUPS) {
+            const int st = slab % PF_A_STAGES;
+            const uint32_t use = (uint32_t)(slab / PF_A_STAGES);
+            mbar_wait_bounded(smem_u32(&empty_a[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
             const int sub = slab * 2 + half;                     // 32-weight sub-block index within the row
             // the weights come straight from HBM: ask L2 for this row's super-blocks a few slabs ahead (one line each)
             if ((slab & 3) == 0 && half == 0) {
-                const size_t ahead = (size_t)((slab >> 2) + PF_PREFETCH_BLOCKS) * Unit<FMT>::BLOCK_BYTES * (FMT == T_Q8_0 ? 8 : 1);
+                const size_t ahead = (size_t)((slab >> 2) + PF_PREFETCH_BLOCKS) * Unit<FMT>::BLOCK_BYTES;   // BLOCK_BYTES: bytes per 256 weights for every format
                 if (ahead < (size_t)a.row_bytes) {
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + ahead));
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow + min(ahead + 128, (size_t)a.row_bytes - 2)));
@@ -220,7 +231,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 for (int j = 0; j < 16; j++) p[j] = OP::pack(y[2 * j], y[2 * j + 1]);
             }
             // row r of the tile: 128 bytes; 16-byte chunk c goes to chunk c ^ (r & 7) (128-byte swizzle)
-            uint8_t* arow = stages + (size_t)st * PF_STAGE_BYTES + (size_t)r * 128;
+            uint8_t* arow = stages + (size_t)st * PF_A_BYTES + (size_t)r * 128;
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 const int chunk = (4 * half + c) ^ (r & 7);
@@ -229,16 +240,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
             fence_proxy_async();                                 // generic-proxy stores -> visible to the tensor core
             mbar_arrive(smem_u32(&full_a[st]));
         }
-    } else if (warp == 8) {
+    } else if (warp == PF_DECODE_WARPS) {
         // ---------------- operand B: activation tiles by TMA ----------------
         if (lane == 0) {
             for (int slab = 0; slab < n_slabs; slab++) {
-                const int st = slab % PF_STAGES;
-                const uint32_t use = (uint32_t)(slab / PF_STAGES);
-                mbar_wait_bounded(smem_u32(&empty[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
+                const int st = slab % PF_B_STAGES;
+                const uint32_t use = (uint32_t)(slab / PF_B_STAGES);
+                mbar_wait_bounded(smem_u32(&empty_b[st]), (use & 1u) ^ 1u, abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT);
                 const uint32_t fb = smem_u32(&full_b[st]);
                 mbar_arrive_expect_tx(fb, (uint32_t)(a.n_acc * PF_B_BYTES));
-                uint8_t* b0 = stages + (size_t)st * PF_STAGE_BYTES + PF_A_BYTES;
+                uint8_t* b0 = stages_b + (size_t)st * PF_B_STAGE_BYTES;
                 for (int n = 0; n < a.n_acc; n++)
                     tma_load_2d(smem_u32(b0 + n * PF_B_BYTES), &xmap, slab * PF_KSLAB, tok0 + n * PF_NTILE, fb);
             }
@@ -247,17 +258,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             for (int slab = 0; slab < n_slabs; slab++) {
-                const int st = slab % PF_STAGES;
-                const uint32_t use = (uint32_t)(slab / PF_STAGES);
-                mbar_wait_bounded(smem_u32(&full_a[st]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-                mbar_wait_bounded(smem_u32(&full_b[st]), use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+                const int sa = slab % PF_A_STAGES, sb = slab % PF_B_STAGES;
+                mbar_wait_bounded(smem_u32(&full_a[sa]), (uint32_t)(slab / PF_A_STAGES) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+                mbar_wait_bounded(smem_u32(&full_b[sb]), (uint32_t)(slab / PF_B_STAGES) & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t abase = smem_u32(stages + (size_t)st * PF_STAGE_BYTES);
+                const uint32_t abase = smem_u32(stages + (size_t)sa * PF_A_BYTES);
+                const uint32_t bbase = smem_u32(stages_b + (size_t)sb * PF_B_STAGE_BYTES);
 #pragma unroll
                 for (int k = 0; k < PF_KSLAB / 16; k++) {
                     const uint64_t adesc = umma_desc_sw128(abase + 32 * k);
                     for (int n = 0; n < a.n_acc; n++) {
-                        const uint64_t bdesc = umma_desc_sw128(abase + PF_A_BYTES + n * PF_B_BYTES + 32 * k);
+                        const uint64_t bdesc = umma_desc_sw128(bbase + n * PF_B_BYTES + 32 * k);
                         const uint32_t accum = (slab > 0 || k > 0) ? 1u : 0u;
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
@@ -266,8 +277,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                             : "memory");
                     }
                 }
-                // frees the stage once the tensor core has read it
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+                // frees the two stages once the tensor core has read them
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty_a[sa])) : "memory");
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty_b[sb])) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(acc_done)) : "memory");
         }
@@ -306,7 +318,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 9) {
+    if (warp == PF_DECODE_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
