@@ -3,7 +3,7 @@
 // Replaces k_gemv_q8 / gemv_q8n of the reference (src/cuda/gemv.cu:51-125, 215-228).  Shape of the kernel:
 //   * persistent CTAs (one per SM): a producer warp plus NGROUPS groups of 8 consumer warps;
 //   * the weight rows stream HBM -> shared memory through 1-D bulk (TMA) copies, one copy per (row, K-chunk) into
-//     a ring of stages per group, completion tracked by mbarriers; GGUF blocks of most formats are only 2-byte
+//     ONE ring of stages that the groups take tiles from alternately, completion tracked by mbarriers; GGUF blocks of most formats are only 2-byte
 //     aligned, so each copy moves the 16-byte aligned superset of its row slice and the consumers index from the
 //     remainder;
 //   * a stage holds a 16-row tile; the 8 warps of a group split its half super-blocks, decode them into int8 mma

@@ -1,12 +1,13 @@
 // q38b_gemv1.cuh -- single-column decode matvec: y[r] (+)= W[r,:] . x.
 //
 // Same streaming scheme as gemv_kernel (persistent CTA per SM, producer warp, 1-D bulk copies of each row slice's
-// 16-byte aligned superset into a ring of stages guarded by mbarriers), but the stage is small -- 8 rows x one
-// 1024-weight slice -- and belongs to ONE consumer warp: lane l owns granule l of the slice, holds its int8
-// activations in registers for all 8 rows and runs the dp4a decoders of q38b_decode1.cuh.  Stage k goes to warp
-// k % W, so the warps never synchronise with each other except through the per-tile reduction:
-// each (tile, slice) writes its 8 row sums to its own slot and arrives on the tile's mbarrier; the warp that took
-// the tile's last slice waits for the others, adds the slices in order (deterministic) and stores y.
+// 16-byte aligned superset into a ring of stages guarded by mbarriers).  A stage holds a tile of rows (or a K-chunk of
+// it); a (tile, 1024-weight slice) unit belongs to ONE consumer warp: lane l owns granule l of the slice, holds its int8
+// activations in registers for all rows of the tile and runs the dp4a decoders of q38b_decode1.cuh (or, for IQ3_XXS,
+// the row-group mapping there).  Units go to the warps round-robin, so the warps never synchronise with each other
+// except through the per-tile reduction: each (tile, slice) writes its row sums to its own slot and arrives on the
+// tile's mbarrier; the warp that took the tile's last slice waits for the others, adds the slices in order
+// (deterministic) and stores y.
 #pragma once
 #include "q38b_act.cuh"
 #include "q38b_decode1.cuh"
@@ -79,13 +80,13 @@ __device__ __forceinline__ TileRef tile_ref(const Gemv1Args& a, int gtile) {
 constexpr int RG_CB_WORDS = 256 * 32, RG_SGN_WORDS = 128 * 32;
 constexpr int RG_STATIC_BYTES = 4 * (RG_CB_WORDS + RG_SGN_WORDS);
 
-// ROWS = rows per tile and stage (8 unless no 8-row plan fits shared memory); two CTAs share an SM so that the
-// prologue of one (or of the next kernel of the stream) overlaps the streaming of the other.
+// ROWS = rows per tile and stage (8, 16 for row groups with an SM to themselves, fewer when no such plan fits shared memory).
 // RG: the row-group mapping of q38b_decode1.cuh (IQ3_XXS, rows 8 bytes aligned): lane = (row of a group of four,
 // sub-block), tables in static shared memory, activations staged in the layout of actr_pos.
 // A32: the column is given in the reference GPU path's per-32 format (ActQ8: xq = int8 values, xd32 = one scale per 32).
-// OCC: CTAs per SM the kernel is built for: 2 (eight consumer warps each, half the shared memory each) or 1 (sixteen
-// consumer warps, all of it: one set of tables, deeper rings and larger tiles for long rows).
+// OCC: CTAs per SM the kernel is built for: 1 (NWARPS = 24 consumer warps, 20 for row groups, all of the SM's shared
+// memory: one set of tables and one quantized column per SM, deeper rings, larger tiles; the default plan) or 2 (eight
+// consumer warps and half the shared memory each, for shapes whose one-CTA plan does not fit).
 template <int FMT, int NWARPS, int ROWS, bool RG, bool A32, int OCC>
 __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gemv1Args a) {
     constexpr int G1_ROWS = ROWS;
