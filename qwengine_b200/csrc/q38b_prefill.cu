@@ -166,7 +166,7 @@ template <int FMT, bool F16>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap xmap) {
     using OP = typename std::conditional<F16, OpF16, OpBf16>::type;
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t* full_a = (uint64_t*)smem;              // [A stages] 256 decode threads arrive
+    uint64_t* full_a = (uint64_t*)smem;              // [A stages] the 8 decode warps of the slab's group arrive
     uint64_t* empty_a = full_a + PF_A_STAGES;        // [A stages] tcgen05.commit
     uint64_t* full_b = empty_a + PF_A_STAGES;        // [B stages] TMA bytes
     uint64_t* empty_b = full_b + PF_B_STAGES;        // [B stages] tcgen05.commit
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
     if (tid == 0) {
         *abort_flag = 0;
         for (int s = 0; s < PF_A_STAGES; s++) {
-            mbar_init(smem_u32(&full_a[s]), 256);
+            mbar_init(smem_u32(&full_a[s]), 8);             // one arrival per decode warp of the slab's group
             mbar_init(smem_u32(&empty_a[s]), 1);
         }
         for (int s = 0; s < PF_B_STAGES; s++) {
@@ -238,7 +238,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillArg
                 *(uint4*)(arow + 16 * chunk) = make_uint4(p[4 * c], p[4 * c + 1], p[4 * c + 2], p[4 * c + 3]);
             }
             fence_proxy_async();                                 // generic-proxy stores -> visible to the tensor core
-            mbar_arrive(smem_u32(&full_a[st]));
+            __syncwarp();                                        // one arrival per warp: 256 arrivals on one barrier word serialise
+            if (lane == 0) mbar_arrive(smem_u32(&full_a[st]));
         }
     } else if (warp == PF_DECODE_WARPS) {
         // ---------------- operand B: activation tiles by TMA ----------------

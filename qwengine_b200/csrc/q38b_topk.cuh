@@ -50,18 +50,34 @@ static __global__ void __launch_bounds__(TOPK_STAGE1_WARPS * 32) topk_lists_kern
         const int i = base + 32 * j + lane;
         key[j] = i < n ? topk_key(xc[i]) : 0u;
     }
-    // this lane's candidate: its largest key, the earliest slot among equals (slots ascend with the position)
+    // This lane's candidate: its largest key, the earliest slot among equals (slots ascend with the position).  Kept
+    // per group of eight slots, so that dropping an element rescans eight slots and four group bests, not all 32.
     uint32_t live = 0u;   // bit j: element j of this lane exists and has not been emitted yet
 #pragma unroll
     for (int j = 0; j < 32; j++) live |= (base + 32 * j + lane) < n ? 1u << j : 0u;
+    uint32_t gbest[4];
+    int gslot[4];         // 32: the group has nothing left
+    auto scan_group = [&](int g) {
+        uint32_t bst = 0u;
+        int sl = 32;
+#pragma unroll
+        for (int j = 7; j >= 0; j--) {
+            const int jj = 8 * g + j;
+            if (((live >> jj) & 1u) && key[jj] >= bst) { bst = key[jj]; sl = jj; }
+        }
+        gbest[g] = bst;
+        gslot[g] = sl;
+    };
+#pragma unroll
+    for (int g = 0; g < 4; g++) scan_group(g);
     uint32_t best = 0u;
     int slot = 32;        // 32: none left
     auto pick = [&]() {
         best = 0u;
         slot = 32;
 #pragma unroll
-        for (int j = 31; j >= 0; j--)
-            if (((live >> j) & 1u) && key[j] >= best) { best = key[j]; slot = j; }
+        for (int g = 3; g >= 0; g--)
+            if (gslot[g] < 32 && gbest[g] >= best) { best = gbest[g]; slot = gslot[g]; }
     };
     pick();
     TopkPair* out = lists + ((size_t)blockIdx.y * n_chunks + chunk) * k;
@@ -71,6 +87,9 @@ static __global__ void __launch_bounds__(TOPK_STAGE1_WARPS * 32) topk_lists_kern
         if (lane == 0) out[r] = w;
         if (my_idx == w.idx && slot < 32) {   // the owner drops the element and looks for its next best
             live &= ~(1u << slot);
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+                if (g == (slot >> 3)) scan_group(g);
             pick();
         }
     }
@@ -84,14 +103,32 @@ static __global__ void __launch_bounds__(32 * TOPK_LISTS_PER_LANE) topk_merge_ke
     TopkPair* sl = (TopkPair*)topk_smem;   // [n_chunks][k]
     const TopkPair* src = lists + (size_t)blockIdx.x * n_chunks * k;
     const int total = n_chunks * k;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) sl[i] = src[i];
+    {   // two pairs per 16-byte load where this column's lists start 16-byte aligned (an even number of pairs in front of
+        // them in the work area); an odd last pair goes alone
+        const bool aligned = (((size_t)blockIdx.x * n_chunks * k) & 1u) == 0;
+        const int n2 = aligned ? total >> 1 : 0;
+        const uint4* src2 = (const uint4*)src;
+        uint4* dst2 = (uint4*)sl;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n2; i += blockDim.x) dst2[i] = src2[i];
+        for (int i = 2 * n2 + threadIdx.x; i < total; i += blockDim.x) sl[i] = src[i];
+    }
     __syncthreads();
     if (threadIdx.x >= 32) return;
     const int lane = threadIdx.x;
-    // lane l walks lists l, l + 32, ...: head[t] = how many elements of list l + 32 t are already taken
+    // lane l walks lists l, l + 32, ...: head[t] = how many elements of list l + 32 t are taken, hk / hi = the element at
+    // the head (registers: only the list that advanced is read again)
     int head[TOPK_LISTS_PER_LANE];
+    uint32_t hk[TOPK_LISTS_PER_LANE];
+    int hi[TOPK_LISTS_PER_LANE];
 #pragma unroll
-    for (int t = 0; t < TOPK_LISTS_PER_LANE; t++) head[t] = 0;
+    for (int t = 0; t < TOPK_LISTS_PER_LANE; t++) {
+        const int list = lane + 32 * t;
+        head[t] = 0;
+        const TopkPair p = list < n_chunks ? sl[list * k] : TopkPair{0u, 0x7fffffff};
+        hk[t] = p.key;
+        hi[t] = p.idx;
+    }
     uint32_t best = 0u;
     int best_idx = 0x7fffffff, best_t = -1;
     auto pick = [&]() {
@@ -100,14 +137,10 @@ static __global__ void __launch_bounds__(32 * TOPK_LISTS_PER_LANE) topk_merge_ke
         best_t = -1;
 #pragma unroll
         for (int t = 0; t < TOPK_LISTS_PER_LANE; t++) {
-            const int list = lane + 32 * t;
-            if (list < n_chunks && head[t] < k) {
-                const TopkPair p = sl[list * k + head[t]];
-                if (p.idx != 0x7fffffff && (best_t < 0 || p.key > best || (p.key == best && p.idx < best_idx))) {
-                    best = p.key;
-                    best_idx = p.idx;
-                    best_t = t;
-                }
+            if (hi[t] != 0x7fffffff && (best_t < 0 || hk[t] > best || (hk[t] == best && hi[t] < best_idx))) {
+                best = hk[t];
+                best_idx = hi[t];
+                best_t = t;
             }
         }
     };
@@ -123,8 +156,14 @@ static __global__ void __launch_bounds__(32 * TOPK_LISTS_PER_LANE) topk_merge_ke
         }
         if (best_t >= 0 && best_idx == w.idx) {
 #pragma unroll
-            for (int t = 0; t < TOPK_LISTS_PER_LANE; t++)
-                if (t == best_t) head[t]++;
+            for (int t = 0; t < TOPK_LISTS_PER_LANE; t++) {
+                if (t == best_t) {
+                    head[t]++;
+                    const TopkPair p = head[t] < k ? sl[(lane + 32 * t) * k + head[t]] : TopkPair{0u, 0x7fffffff};
+                    hk[t] = p.key;
+                    hi[t] = p.idx;
+                }
+            }
             pick();
         }
     }
