@@ -88,7 +88,6 @@ def load_library():
     lib.q38b_pass_weight_bytes.restype = ll
     lib.q38b_pass_kernel_count.argtypes = [vp]
     lib.q38b_pass_set_merge.argtypes = [vp, i32]
-    lib.q38b_debug_pass_set_fuse_swiglu.argtypes = [vp, i32]
     lib.q38b_add_rmsnorm_q8k.argtypes = [vp, vp, vp, vp, vp, i32, ll, i32, C.c_float, vp, vp, ll, vp]
     lib.q38b_gemv_bf16.argtypes = [vp, vp, i32, i32, vp, vp, vp]
     lib.q38b_swiglu_rows_inplace.argtypes = [vp, vp, vp, i32, i32, ll, i32, vp]
@@ -413,10 +412,6 @@ class Pass:
 
     def topk(self, src, off, n, k, dst):
         self.ctx._rc(self.lib.q38b_pass_op_topk(self.h, src, off, n, k, dst), "q38b_pass_op_topk")
-
-    def debug_set_fuse_swiglu(self, enabled):
-        """Test hook: enabled=False keeps SwiGLU steps as kernels of their own."""
-        self.ctx._rc(self.lib.q38b_debug_pass_set_fuse_swiglu(self.h, int(bool(enabled))), "q38b_debug_pass_set_fuse_swiglu")
 
     def barrier(self):
         self.ctx._rc(self.lib.q38b_pass_op_barrier(self.h), "q38b_pass_op_barrier")

@@ -810,14 +810,6 @@ int q38b_gemv_group(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const*
 
 int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                           const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream) {
-    return q38b_gemv_group_gated(ctx, type, n_mats, W, row_bytes, K, M, q8k, x_f32, nullptr, y, y_peers, n_peers, stream);
-}
-
-int q38b_gemv_group_gated(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
-                          const void* q8k, const float* x_f32, const float* x_up, float* const* y, float* const* y_peers, int n_peers,
-                          void* stream) {
-    if (x_up && !x_f32) return Q38B_ERR_ARG;
-    if (x_up && ((uintptr_t)x_up & 15)) return Q38B_ERR_ALIGN;
     if (!ctx || !W || !M || !y || n_mats < 1 || n_mats > G1_MAX_MATS || (!q8k == !x_f32)) return Q38B_ERR_ARG;
     if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return Q38B_ERR_ARG;
     for (int i = 0; i < n_mats * n_peers; i++) if (!y_peers[i] || ((uintptr_t)y_peers[i] & 3)) return Q38B_ERR_ARG;
@@ -846,7 +838,6 @@ int q38b_gemv_group_gated(q38b_ctx* ctx, uint32_t type, int n_mats, const void* 
     g.xq = (const uint8_t*)q8k;
     g.x_f32 = x_f32;
     g.sync = take_pending_sync(ctx);
-    g.x_up = x_up;
     g.n_peers = n_peers;
     for (int i = 0; i < n_mats; i++)
         for (int pr = 0; pr < n_peers; pr++) (i == 0 ? g.y_peer[pr] : g.y_peer_more[i - 1][pr]) = y_peers[i * n_peers + pr];

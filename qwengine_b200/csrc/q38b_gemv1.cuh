@@ -32,7 +32,6 @@ struct Gemv1Args {
     const float* xd32;      // per-32 activations (kernels instantiated with A32): xq = K int8 values, xd32 = K / 32 scales
     const uint8_t* xq;      // Q8_K blocks of the single column, or nullptr:
     const float* x_f32;     // then the K floats of the column, quantized to Q8_K blocks by every CTA in its prologue
-    const float* x_up;      // with x_f32: the column is silu(x_f32) * x_up (SwiGLU of gate and up outputs), formed in the prologue too
     float* y;
     float* y_peer[7];       // the same output position in the buffers of the other GPUs (peer stores), n_peers used
     float* y_peer_more[G1_MAX_MATS - 1][7];   // the same for matrices 1 and 2
@@ -242,19 +241,6 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                 if (sb < a.nsb) {
                     lo4[j] = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane);
                     hi4[j] = *(const float4*)(a.x_f32 + (size_t)sb * 256 + 8 * lane + 4);
-                }
-            }
-            if (a.x_up) {   // the arithmetic of swiglu_block, value by value
-#pragma unroll
-                for (int j = 0; j < QB; j++) {
-                    const int sb = sb0 + j * NWARPS;
-                    if (sb >= a.nsb) continue;
-                    const float4 ul = *(const float4*)(a.x_up + (size_t)sb * 256 + 8 * lane);
-                    const float4 uh = *(const float4*)(a.x_up + (size_t)sb * 256 + 8 * lane + 4);
-                    lo4[j].x = swiglu_value(lo4[j].x, ul.x); lo4[j].y = swiglu_value(lo4[j].y, ul.y);
-                    lo4[j].z = swiglu_value(lo4[j].z, ul.z); lo4[j].w = swiglu_value(lo4[j].w, ul.w);
-                    hi4[j].x = swiglu_value(hi4[j].x, uh.x); hi4[j].y = swiglu_value(hi4[j].y, uh.y);
-                    hi4[j].z = swiglu_value(hi4[j].z, uh.z); hi4[j].w = swiglu_value(hi4[j].w, uh.w);
                 }
             }
 #pragma unroll

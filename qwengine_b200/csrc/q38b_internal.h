@@ -40,11 +40,6 @@ extern "C" int q38b_gemv_group_plannable(const q38b_ctx* ctx, uint32_t type, int
 // q38b_gemv_group with peer stores: y_peers[i * n_peers + r] is where peer r keeps the output of matrix i
 extern "C" int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                                      const void* q8k, const float* x_f32, float* const* y, float* const* y_peers, int n_peers, void* stream);
-// the same with the column formed in the kernel's prologue from two fp32 vectors: silu(x_f32) * x_up (SwiGLU of the gate
-// and up outputs, the arithmetic of q38b_swiglu_q8k) when x_up is not null
-extern "C" int q38b_gemv_group_gated(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
-                                     const void* q8k, const float* x_f32, const float* x_up, float* const* y, float* const* y_peers,
-                                     int n_peers, void* stream);
 // the same for the multi-column kernel (nb columns of Q8_K blocks, q8k_stride blocks apart; y[i][c * y_ld[i] + r]); no peers
 extern "C" int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb);
 // the same with the columns given as floats (x_f32, x_f32_ld floats apart; quantized inside the kernel) instead of Q8_K

@@ -88,19 +88,14 @@ struct q38b_pass {
     float* pin_in = nullptr;
     float* pin_out = nullptr;
     size_t pin_in_n = 0, pin_out_n = 0;
-    // 1: single-column replays fold a SwiGLU step into the matvecs that read its output, like a quantize step (one kernel
-    // fewer per FFN block).  Off by default: every CTA of the down projection then evaluates all of silu(g) * u in its
-    // prologue, which measured slower on B200 than the separate SwiGLU kernel (26.4 us against 15.7 + about 5 us for
-    // K = 17408).  q38b_debug_pass_set_fuse_swiglu switches it on.
-    int fuse_swiglu = 0;
     int merge_steps = 1;         // replays: one launch for matvecs that share a column, quantize steps folded into single-column launches
     // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
     // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
     struct Captured {
-        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, one_cta, fuse_swiglu;
+        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, one_cta;
         bool operator==(const Captured& o) const {
             return n_ops == o.n_ops && peer_store == o.peer_store && merge_steps == o.merge_steps && uniform_columns == o.uniform_columns &&
-                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && one_cta == o.one_cta && fuse_swiglu == o.fuse_swiglu;
+                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && one_cta == o.one_cta;
         }
     };
     Captured captured[9] = {};
@@ -151,11 +146,11 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
 }
 
 // One launch of the merged single-column replay: `n` matvec ops (indices into p->ops) that read one column, which comes
-// as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source(s) of that quantize or SwiGLU op (folded into
-// the launch: the kernel forms the Q8_K blocks in its prologue).
+// as the Q8_K buffer of the ops or, when `quant` >= 0, as the fp32 source of that quantize op (folded into the launch:
+// the kernel forms the Q8_K blocks in its prologue).
 struct Merged { int first_op; int n; int ops[3]; int quant; };
 
-// Which steps of a replay can share launches.  A quantize step (for one column also a SwiGLU step) is folded into the
+// Which steps of a replay can share launches.  A quantize step is folded into the
 // matvecs that read its output when they follow it directly, nothing else reads that output before it is rewritten, and
 // all of them run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
 void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vector<char>& skip) {
@@ -187,14 +182,13 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
     while (i < n) {
         int quant = -1;
         size_t g0 = i;
-        const bool gated = ops[i].kind == OP_SWIGLU && nb == 1 && p->fuse_swiglu;
-        if (ops[i].kind == OP_QUANT || gated) {
-            const int col = gated ? ops[i].c : ops[i].b;
+        if (ops[i].kind == OP_QUANT) {
+            const int col = ops[i].b;
             const size_t j = ranks ? i + 1 : next_real(i + 1);   // several ranks: only a matvec right after the quantize step
             std::vector<size_t> run;                              // the matvecs the quantize step would be folded into
             for (size_t k = j; on_column(k, col); k = next_in_run(k)) run.push_back(k);
             const size_t run_end = run.empty() ? j : next_real(run.back() + 1);
-            bool ok = !run.empty() && ops[i].off % 4 == 0 && (!gated || ops[i].d % 4 == 0);
+            bool ok = !run.empty() && ops[i].off % 4 == 0;
             for (size_t k = run_end; ok && k < n; k++) {   // nobody else reads the Q8_K buffer before it is written again
                 const Op& o = ops[k];
                 if ((o.kind == OP_QUANT && o.b == col) || (o.kind == OP_SWIGLU && o.c == col)) break;
@@ -305,8 +299,6 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
             }
             const void* q8k = mg.quant >= 0 ? nullptr : p->bufs[g0.b].ptr;
             const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
-            const float* xu = nullptr;   // a folded SwiGLU step: the column is silu(xf) * xu
-            if (mg.quant >= 0 && p->ops[mg.quant].kind == OP_SWIGLU) xu = (const float*)p->bufs[p->ops[mg.quant].b].ptr + p->ops[mg.quant].d;
             float* peers[3 * 7];
             int np = 0;
             if (p->peer_store && ctx->n_ranks > 1) {
@@ -321,7 +313,7 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                     if (k != np) return Q38B_ERR_ARG;   // all outputs of one launch live in peer-visible buffers, or none
                 }
             }
-            const int rc = q38b_gemv_group_gated(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, xu, y, peers, np, st);
+            const int rc = q38b_gemv_group_peers(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, q8k, xf, y, peers, np, st);
             if (rc != Q38B_OK) return rc;
         }
         if (skip[oi]) continue;
@@ -615,7 +607,7 @@ int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const q38b_pass::Captured now = {p->ops.size(), p->peer_store, p->merge_steps, p->ctx->uniform_columns, p->ctx->pass_pdl,
-                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->one_cta, p->fuse_swiglu};
+                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->one_cta};
     if (p->graphs[nb] && !(now == p->captured[nb])) {
         cudaGraphExecDestroy(p->graphs[nb]);
         p->graphs[nb] = nullptr;
@@ -684,7 +676,7 @@ int q38b_pass_set_merge(q38b_pass* p, int enabled) {
 // steps[3 i ..] = {kind (0 quantize, 1 matvec, 2 SwiGLU, 3 all-gather, 4 barrier), column buffer, output offset}; every
 // matvec is a 512 x 1024 Q4_K matrix writing 512 floats at its offset.  launch_of[i] receives the position in the step
 // list at which step i is launched (its own index unless it joined an earlier launch), -1 for folded quantize steps.
-int q38b_debug_merge_plan(int n_ranks, int nb, int fuse_swiglu, int n_steps, const int* steps, int* launch_of) {
+int q38b_debug_merge_plan(int n_ranks, int nb, int n_steps, const int* steps, int* launch_of) {
     if (n_ranks < 1 || nb < 1 || n_steps < 0 || !steps || !launch_of) return Q38B_ERR_ARG;
     q38b_ctx ctx;
     ctx.sm_count = 148;
@@ -692,7 +684,6 @@ int q38b_debug_merge_plan(int n_ranks, int nb, int fuse_swiglu, int n_steps, con
     ctx.n_ranks = n_ranks;
     q38b_pass p;
     p.ctx = &ctx;
-    p.fuse_swiglu = fuse_swiglu;
     p.mats.push_back({(uint32_t)T_Q4_K, nullptr, 576, 1024, 512, false});
     for (int b = 0; b < 8; b++) p.bufs.push_back({nullptr, 1 << 20, b >= 4, {}, 0, false});   // 0..3 fp32, 4..7 Q8_K columns
     for (int i = 0; i < n_steps; i++) {
@@ -715,13 +706,6 @@ int q38b_debug_merge_plan(int n_ranks, int nb, int fuse_swiglu, int n_steps, con
         for (int t = 0; t < mg.n; t++) launch_of[mg.ops[t]] = mg.first_op;
     }
     return (int)merged.size();
-}
-
-// Test hook: 0 keeps SwiGLU steps as kernels of their own.
-int q38b_debug_pass_set_fuse_swiglu(q38b_pass* p, int enabled) {
-    if (!p) return Q38B_ERR_ARG;
-    p->fuse_swiglu = enabled ? 1 : 0;
-    return Q38B_OK;
 }
 
 int q38b_pass_kernel_count(const q38b_pass* p) {

@@ -277,35 +277,3 @@ def test_pass_from_gguf_file(ctx, tmp_path):
             q.Pass(ctx).matrix_from_gguf(g2, "missing")
         finally:
             g2.close()
-
-
-def test_swiglu_folded_into_the_down_projection(ctx):
-    """A SwiGLU step whose output only the next matvec reads is folded into that launch (every CTA forms silu(g) * u and
-    its Q8_K blocks in its prologue, the arithmetic of the SwiGLU kernel): one kernel fewer per layer, the same bits."""
-    K, FFN = 1024, 1536
-    wg = synth.make_weights("IQ3_XXS", FFN, K, seed=31, scale=2e-4)
-    wu = synth.make_weights("IQ3_XXS", FFN, K, seed=32, scale=2e-4)
-    wd = synth.make_weights("IQ4_XS", 300, FFN, seed=33)
-    x = torch.from_numpy(synth.make_activations(1, K, seed=34)).cuda()
-    outs, counts = [], []
-    for fuse in (True, False):
-        ps = q.Pass(ctx, max_nb=1)
-        ps.debug_set_fuse_swiglu(fuse)
-        xin, xq, gu, hq, y = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(2 * FFN), ps.buffer_q8k(FFN), ps.buffer_f32(300)
-        for _ in range(2):   # two layers
-            ps.quantize(xin, 0, K, xq)
-            ps.gemv(ps.matrix_upload("IQ3_XXS", wg, K), xq, gu, 0)
-            ps.gemv(ps.matrix_upload("IQ3_XXS", wu, K), xq, gu, FFN)
-            ps.swiglu(gu, 0, gu, FFN, FFN, hq)
-            ps.gemv(ps.matrix_upload("IQ4_XS", wd, FFN), hq, y, 0)
-        ps.buffer_tensor(xin).copy_(x)
-        for _ in range(3):
-            ps.run(1)
-        torch.cuda.synchronize()
-        ctx.check()
-        outs.append(ps.buffer_tensor(y)[0].clone())
-        counts.append(ps.kernel_count)
-        ps.close()
-    assert counts == [4, 6]
-    assert torch.equal(outs[0].view(torch.int32), outs[1].view(torch.int32))
-    assert bool(torch.isfinite(outs[0]).all()) and float(outs[0].abs().max()) > 0

@@ -14,12 +14,12 @@ def plan():
     build.build()
     lib = load_library()
     i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
-    lib.q38b_debug_merge_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p]
+    lib.q38b_debug_merge_plan.argtypes = [C.c_int, C.c_int, C.c_int, i32p, i32p]
 
-    def run(n_ranks, nb, steps, fuse_swiglu=False):
+    def run(n_ranks, nb, steps):
         s = np.array(steps, np.int32).reshape(-1, 3)
         out = np.zeros(len(s), np.int32)
-        n = lib.q38b_debug_merge_plan(n_ranks, nb, int(fuse_swiglu), len(s), s, out)
+        n = lib.q38b_debug_merge_plan(n_ranks, nb, len(s), s, out)
         assert n >= 0
         return n, out.tolist()
     return run
@@ -29,13 +29,6 @@ def test_quantize_folds_and_column_mates_share_a_launch(plan):
     steps = [(Q, 4, 0), (MV, 4, 0), (MV, 4, 512), (MV, 4, 1024), (SW, 5, 0), (MV, 5, 2048)]
     n, where = plan(1, 1, steps)
     assert n == 1 and where == [-1, 1, 1, 1, 4, 5]
-    n, where = plan(1, 1, steps, fuse_swiglu=True)
-    assert n == 2 and where == [-1, 1, 1, 1, -1, 5], "the SwiGLU step is folded into the matvec that reads its output"
-    n, where = plan(1, 2, steps, fuse_swiglu=True)
-    assert n == 1 and where == [-1, 1, 1, 1, 4, 5], "several columns: SwiGLU stays a kernel of its own"
-    # a second reader of the SwiGLU output later in the pass: the Q8_K blocks must exist, so nothing is folded
-    n, where = plan(1, 1, [(SW, 5, 0), (MV, 5, 0), (Q, 4, 0), (MV, 4, 512), (MV, 5, 2048)], fuse_swiglu=True)
-    assert where[0] == 0
 
 
 def test_single_rank_steps_over_barriers(plan):
