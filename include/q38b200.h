@@ -5,8 +5,9 @@
  * Each entry point names the reference interface it replaces (file:line inside the reference project).
  * Conventions, all taken from the reference:
  *   - `type` is the ggml type id the reference's QuantFormat enum carries verbatim
- *     (include/q38rt/q38rt_types.h:36-67): Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ3_XXS = 18,
- *     IQ3_S = 21, IQ4_XS = 23;
+ *     (include/q38rt/q38rt_types.h:36-67): Q8_0 = 8, Q2_K = 10, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ2_XXS = 16,
+ *     IQ2_XS = 17, IQ3_XXS = 18, IQ1_S = 19, IQ3_S = 21, IQ2_S = 22, IQ4_XS = 23, IQ1_M = 29 (the last six of the
+ *     list: one-column kernel, exact dequantizer and prefill GEMM; several columns run as one launch per column);
  *   - weights are row-major GGUF blocks exactly as in the file, `row_bytes` apart (src/cuda/gemv.cuh:26-29);
  *     M counts output rows, K the row length (a multiple of 256);
  *   - output column c of a multi-column call is y + c * y_ld (src/cuda/gemv.cuh:31-34);
@@ -14,7 +15,8 @@
  *     (`stream` is a cudaStream_t passed as void*); all pointers named *_dev are device pointers.
  * Activations are ggml Q8_K blocks (float d, int8 qs[256], int16 bsums[16]; src/quant/quant_formats.h:95), the format
  * the reference's CPU kernels consume (src/cpu/cpu_kernels.h:13-22), produced on the device bit-identically to
- * quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381).
+ * quantize_row_q8_K_ref (src/quant/quant_ref.cpp:353-381); the *_act_q8 entry points take the reference GPU path's
+ * per-32 format instead (ActQ8, src/cuda/gemv.cuh:14-21).
  * Every function returns 0 on success or a negative q38b_status; nothing calls exit().
  */
 #ifndef Q38B200_H
