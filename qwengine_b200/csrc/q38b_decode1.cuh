@@ -245,14 +245,25 @@ template <> struct Gran<T_IQ4_XS> {
         uint32_t w[4];
         sp_ld64(p, 8 + 16 * s, w[0], w[1]);
         sp_ld64(p, 16 + 16 * s, w[2], w[3]);
-        int dot = 0;
+        // The 16 levels split into the eight negative ones (nibbles 0..7) and the eight positive ones (8..15).  PRMT with a
+        // nibble of the data word as its selector picks one of eight table bytes by the nibble's low three bits, and
+        // returns the SIGN of that byte in all eight bits when the nibble's top bit is set.  With two tables of
+        // non-negative bytes -- the negated negative levels, looked up with the word itself, and the positive levels in
+        // reverse order, looked up with the complemented word (nibble 8 + m becomes 7 - m, nibbles below 8 get their top
+        // bit set) -- each look-up yields the level's magnitude where the nibble belongs to its half and zero elsewhere:
+        // sum = dp4a(positive part) - dp4a(negated negative part), no masks and no third PRMT to merge the halves.
+        constexpr uint32_t NL0 = 0x4153687Fu, NL1 = 0x0A162331u;   // 127, 104, 83, 65 | 49, 35, 22, 10
+        constexpr uint32_t HR0 = 0x35455971u, HR1 = 0x010D1926u;   // 113, 89, 69, 53 | 38, 25, 13, 1
+        int pos = 0, neg = 0;
 #pragma unroll
         for (int t = 0; t < 4; t++) {
-            uint32_t x0, x1;
-            Unit<T_IQ4_XS>::lut8(w[t], x0, x1);
-            dot = dp4a_ss(x0, a.q[2 * t], dot);
-            dot = dp4a_ss(x1, a.q[2 * t + 1], dot);
+            const uint32_t nw = ~w[t];
+            neg = dp4a_ss(prmt(NL0, NL1, w[t]), a.q[2 * t], neg);
+            pos = dp4a_ss(prmt(HR0, HR1, nw), a.q[2 * t], pos);
+            neg = dp4a_ss(prmt(NL0, NL1, w[t] >> 16), a.q[2 * t + 1], neg);
+            pos = dp4a_ss(prmt(HR0, HR1, nw >> 16), a.q[2 * t + 1], pos);
         }
+        const int dot = pos - neg;
         const uint32_t hdr = sp_ld32(p, 0);            // fp16 d | scales_h
         const uint32_t sl = sp_ld8(p, 4 + (s >> 1));
         const int ls = (int)(((sl >> (4 * (s & 1))) & 0xFu) | ((((hdr >> 16) >> (2 * s)) & 3u) << 4)) - 32;
