@@ -348,13 +348,17 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
         const int in_chunk = min(a.chunk_slices, a.n_slices - chunk * a.chunk_slices);
         const int n_arr = (cslice == in_chunk - 1) ? a.chunk_slices - in_chunk + 1 : 1;
         if constexpr (RG) {
-            // row groups: pass ps = rows 4 ps .. 4 ps + 3 (lane / 8 picks the row), the four blocks of the slice in turn
+            // row groups: lane / 8 picks one of the four rows of a pass, the four blocks of the slice in turn.  A 16-row
+            // tile deals rows ps, ps + 8, ps + 4, ps + 12 to pass ps: with packed rows of 1960 bytes (K = 5120; 6664 for
+            // K = 17408) rows 8 apart sit 64 bytes apart modulo a 128-byte line and rows 4 apart 32 bytes, so the two rows
+            // of a half warp's 64-bit loads and the four rows of a warp's 32-bit loads fall on disjoint banks.
             const int s = lane & 7;
+            const int row_of_sub = G1_ROWS == 16 ? (sub & 1) * 8 + (sub >> 1) * 4 : sub;
             SP rowp[PASSES];
             float acc[PASSES];
 #pragma unroll
             for (int ps = 0; ps < PASSES; ps++) {
-                const int r = 4 * ps + sub;
+                const int r = G1_ROWS == 16 ? ps + row_of_sub : 4 * ps + sub;
                 rowp[ps] = st + (r * a.slot_stride + (int)((src_lo + (uint32_t)r * rb_step) & 15u));
                 acc[ps] = 0.0f;
             }
@@ -371,7 +375,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (s == 0) rslot[4 * ps + sub] = v;
+                if (s == 0) rslot[G1_ROWS == 16 ? ps + row_of_sub : 4 * ps + sub] = v;
             }
         } else {
         typename Gran<FMT>::Acts acts;
