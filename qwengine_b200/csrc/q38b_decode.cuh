@@ -279,21 +279,17 @@ template <> struct Unit<T_IQ3_S> {
 // IQ4_XS: 136 bytes = fp16 d | u16 scales_h | scales_l[4] | qs[128] nibbles (low = weights 0-15, high = 16-31 of
 // each 32).  w = d * (ls - 32) * levels[nibble] (src/quant/quant_ref.cpp:284-300; cpu_kernels.cpp:351-384).
 // The 16-entry level table lives in four registers; PRMT uses four nibbles of the data word directly as its
-// selector: low 3 bits pick among 8 entries, bit 3 picks the table half.
+// selector: the low 3 bits pick among the 8 entries of a half, and with the top bit set PRMT returns the picked byte's
+// sign (zero for these tables), which separates the halves (see run).
 // ------------------------------------------------------------------------------------------------
 template <> struct Unit<T_IQ4_XS> {
     static constexpr int BLOCK_BYTES = 136;
     static constexpr int CODEBOOK_ENTRIES = 0;
 
-    // levels -127,-104,-83,-65 | -49,-35,-22,-10 | 1,13,25,38 | 53,69,89,113 as little-endian int8 words
-    static constexpr uint32_t L0 = 0xBFAD9881u, L1 = 0xF6EADDCFu, L2 = 0x26190D01u, L3 = 0x71594535u;
-
-    static Q38B_HD void lut8(uint32_t w, uint32_t& x0, uint32_t& x1) {
-        const uint32_t s1 = w & 0x77777777u, s1h = s1 >> 16;
-        const uint32_t t2 = (w >> 1) & 0x44444444u;
-        x0 = prmt(prmt(L0, L1, s1), prmt(L2, L3, s1), t2 | 0x3210u);
-        x1 = prmt(prmt(L0, L1, s1h), prmt(L2, L3, s1h), (t2 >> 16) | 0x3210u);
-    }
+    // levels -127,-104,-83,-65,-49,-35,-22,-10 | 1,13,25,38,53,69,89,113 as two tables of non-negative bytes: the negative
+    // ones negated (127, 104, 83, 65 | 49, 35, 22, 10) and the positive ones in reverse order (113, 89, 69, 53 |
+    // 38, 25, 13, 1), looked up with the data word and with its complement: see Gran<T_IQ4_XS>::dot
+    static constexpr uint32_t NL0 = 0x4153687Fu, NL1 = 0x0A162331u, HR0 = 0x35455971u, HR1 = 0x010D1926u;
 
     static Q38B_HD int scale(const uint8_t* p, int s) {
         const uint32_t sh = ld_u16(p + 2), sl = ld_u8(p + 4 + (s >> 1));
@@ -306,12 +302,17 @@ template <> struct Unit<T_IQ4_XS> {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int s = 4 * h + j;
-            uint32_t a0, a1, a2, a3, b0, b1;
-            lut8(ld_u32(pA + 8 + 16 * s + 4 * t), a0, a2);
-            lut8(ld_u32(pB + 8 + 16 * s + 4 * t), a1, a3);
+            // The levels as two fragments of non-negative bytes, positive part and negated negative part (the two-table
+            // PRMT look-up of the one-column decoder): two mma on the same activations and a subtraction cost less than
+            // the masks and the merging PRMT of a single signed fragment; the tensor pipe is idle anyway.
+            uint32_t b0, b1;
+            const uint32_t wA = ld_u32(pA + 8 + 16 * s + 4 * t), wB = ld_u32(pB + 8 + 16 * s + 4 * t);
             load_b64(act, 32 * s + 8 * t, b0, b1);
-            int c[4] = {0, 0, 0, 0};
-            mma_k32(c, a0, a1, a2, a3, b0, b1);
+            int c[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0};
+            mma_k32(c, prmt(HR0, HR1, ~wA), prmt(HR0, HR1, ~wB), prmt(HR0, HR1, ~wA >> 16), prmt(HR0, HR1, ~wB >> 16), b0, b1);
+            mma_k32(cn, prmt(NL0, NL1, wA), prmt(NL0, NL1, wB), prmt(NL0, NL1, wA >> 16), prmt(NL0, NL1, wB >> 16), b0, b1);
+#pragma unroll
+            for (int i = 0; i < 4; i++) c[i] -= cn[i];
             const int scA = scale(pA, s), scB = scale(pB, s);
             sumi[0] += scA * c[0]; sumi[1] += scA * c[1];
             sumi[2] += scB * c[2]; sumi[3] += scB * c[3];

@@ -252,8 +252,8 @@ template <> struct Gran<T_IQ4_XS> {
         // reverse order, looked up with the complemented word (nibble 8 + m becomes 7 - m, nibbles below 8 get their top
         // bit set) -- each look-up yields the level's magnitude where the nibble belongs to its half and zero elsewhere:
         // sum = dp4a(positive part) - dp4a(negated negative part), no masks and no third PRMT to merge the halves.
-        constexpr uint32_t NL0 = 0x4153687Fu, NL1 = 0x0A162331u;   // 127, 104, 83, 65 | 49, 35, 22, 10
-        constexpr uint32_t HR0 = 0x35455971u, HR1 = 0x010D1926u;   // 113, 89, 69, 53 | 38, 25, 13, 1
+        constexpr uint32_t NL0 = Unit<T_IQ4_XS>::NL0, NL1 = Unit<T_IQ4_XS>::NL1;   // 127, 104, 83, 65 | 49, 35, 22, 10
+        constexpr uint32_t HR0 = Unit<T_IQ4_XS>::HR0, HR1 = Unit<T_IQ4_XS>::HR1;   // 113, 89, 69, 53 | 38, 25, 13, 1
         int pos = 0, neg = 0;
 #pragma unroll
         for (int t = 0; t < 4; t++) {
