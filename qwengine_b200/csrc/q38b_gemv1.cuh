@@ -193,6 +193,10 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
     uint8_t* actq = smem + a.off_actq;               // [n_slices * 1024] staged order
     uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
     constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
+    if (a.sync.n > 0 && blockIdx.x == 0 && ctid < a.sync.n) {   // tell the peers first: the flags travel while the tables are filled
+        pdl_wait_prior();
+        peer_sync_signal(a.sync, ctid);
+    }
     if (RG) {
         // the 32 replicas of an entry are 128 bytes: thread t writes 16 of them, so that a warp's store covers 512
         // consecutive bytes (entries by the thread would put all 32 lanes on the same four banks)
@@ -224,7 +228,7 @@ __global__ void __launch_bounds__(32 * (1 + NWARPS), OCC) gemv1_kernel(const Gem
     }
     pdl_wait_prior();
     if (a.sync.n > 0) {
-        peer_sync_wait(a.sync, blockIdx.x == 0, ctid, a.status);
+        peer_sync_poll(a.sync, ctid, a.status);
         named_bar_sync(14, NWARPS * 32);
     }
     if (a.x_f32) {

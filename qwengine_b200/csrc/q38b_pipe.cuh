@@ -104,15 +104,18 @@ struct PeerSync {
 };
 constexpr long long PEER_WAIT_BUDGET_CYCLES = 4000000000LL;   // default: about two seconds
 constexpr int ST_PEER_TIMEOUT = 16;
-// Threads t = 0 .. n - 1 of every CTA call this once the stream's earlier kernels are complete (their stores into the
-// peers' buffers are done); `signaller` is true in one CTA.  Thread t tells rank t and waits (bounded) for rank t.
-__device__ __forceinline__ void peer_sync_wait(const PeerSync& ps, bool signaller, int t, int* status) {
+// The two halves of the barrier, for threads t = 0 .. n - 1.  peer_sync_signal: thread t of ONE CTA tells rank t, once the
+// stream's earlier kernels are complete (their stores into the peers' buffers are done).  peer_sync_poll: thread t of
+// every CTA waits (bounded) for rank t.  A kernel may do other set-up between the two while the flags travel.
+__device__ __forceinline__ void peer_sync_signal(const PeerSync& ps, int t) {
     if (t >= ps.n || t == ps.rank) return;
     const uint32_t e = *(volatile uint32_t*)(ps.local + 10) + (uint32_t)ps.seq + 1u;
-    if (signaller) {
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ps.peer[t] + ps.rank), "r"(e) : "memory");
-    }
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ps.peer[t] + ps.rank), "r"(e) : "memory");
+}
+__device__ __forceinline__ void peer_sync_poll(const PeerSync& ps, int t, int* status) {
+    if (t >= ps.n || t == ps.rank) return;
+    const uint32_t e = *(volatile uint32_t*)(ps.local + 10) + (uint32_t)ps.seq + 1u;
     const long long t0 = clock64();
     for (;;) {
         uint32_t v;
@@ -120,6 +123,11 @@ __device__ __forceinline__ void peer_sync_wait(const PeerSync& ps, bool signalle
         if ((int)(v - e) >= 0) break;
         if (clock64() - t0 > ps.budget) { if (status) atomicOr(status, ST_PEER_TIMEOUT); break; }
     }
+}
+// both at once
+__device__ __forceinline__ void peer_sync_wait(const PeerSync& ps, bool signaller, int t, int* status) {
+    if (signaller) peer_sync_signal(ps, t);
+    peer_sync_poll(ps, t, status);
 }
 
 // Programmatic dependent launch: let the next kernel of the stream start its prologue now; wait until the
