@@ -172,7 +172,7 @@ def run_config(n_layers, world, gather):
     from qwengine_b200 import decode_pass as dp
     cfg = {"workload": "decode_weight_pass_27b_shape", "layers": n_layers, "matrices": len(dp.all_specs(n_layers)),
            "weight_bytes": dp.total_weight_bytes(n_layers, True), "nb": 1,
-           "parallelism": f"row-shard x{world}" + (f" + {gather} gather" if world > 1 else ""),
+           "parallelism": f"row-shard x{world}" + (f" (FFN and head; attention-side projections whole on every rank) + {gather} gather" if world > 1 else ""),
            "cache": "12.5 GB of weights per pass, far larger than L2; no flush needed"}
     return cfg
 
@@ -313,8 +313,8 @@ def sharded_equals_single(torch, dist, q, ctx, rank, world, gather):
 
     x0 = torch.randn((7, dp.HIDDEN), device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
     ps = q.Pass(ctx, max_nb=7)
-    io = dp.build(ps, lambda spec, rows: ps.matrix_device(spec.fmt, weights(spec, rank * rows, rows), spec.K), n_layers=n_layers, head=True,
-                  rank=rank, world=world, gather=gather)
+    io = dp.build(ps, lambda spec, rows, replicated=False: ps.matrix_device(spec.fmt, weights(spec, 0 if replicated else rank * rows, rows), spec.K),
+                  n_layers=n_layers, head=True, rank=rank, world=world, gather=gather)
     outs = {}
     for nb in (1, 7):
         ps.buffer_tensor(io["in_buf"]).copy_(x0)
@@ -386,9 +386,9 @@ def run_ours(args):
     ps = q.Pass(ctx, max_nb=7)
     counter = [0]
 
-    def make_matrix(spec, rows):
-        counter[0] += 1
-        w = device_weights(torch, spec, rows, seed=1000 * counter[0] + rank, scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
+    def make_matrix(spec, rows, replicated=False):
+        counter[0] += 1   # a replicated matrix has the same bytes on every rank
+        w = device_weights(torch, spec, rows, seed=1000 * counter[0] + (0 if replicated else rank), scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
         return ps.matrix_device(spec.fmt, w, spec.K)
 
     io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world, gather=args.gather)

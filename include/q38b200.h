@@ -242,6 +242,9 @@ int q38b_pass_matrix_device(q38b_pass* pass, uint32_t type, const void* W_dev, s
 int q38b_pass_op_quantize(q38b_pass* pass, int src_f32, int src_off, int K, int dst_q8k);
 int q38b_pass_op_gemv(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
 int q38b_pass_op_swiglu(q38b_pass* pass, int g_f32, int g_off, int u_f32, int u_off, int n, int dst_q8k);
+/* q38b_pass_op_gemv whose output stays on this GPU even in a peer-connected pass: for matrices that every rank holds
+ * whole (replicated) because streaming them costs less than exchanging their outputs. */
+int q38b_pass_op_gemv_local(q38b_pass* pass, int matrix, int src_q8k, int dst_f32, int dst_off);
 /* The k best of n logits of buffer src_f32 (from float offset off) per column: dst_f32 gets k values followed by k
  * positions (int32 bit patterns), so that a run can return 8 k bytes per column instead of all logits. */
 int q38b_pass_op_topk(q38b_pass* pass, int src_f32, int off, int n, int k, int dst_f32);

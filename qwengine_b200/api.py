@@ -80,6 +80,7 @@ def load_library():
     lib.q38b_pass_matrix_device.argtypes = [vp, u32, vp, sz, i32, i32]
     lib.q38b_pass_op_quantize.argtypes = [vp, i32, i32, i32, i32]
     lib.q38b_pass_op_gemv.argtypes = [vp, i32, i32, i32, i32]
+    lib.q38b_pass_op_gemv_local.argtypes = [vp, i32, i32, i32, i32]
     lib.q38b_pass_op_swiglu.argtypes = [vp, i32, i32, i32, i32, i32, i32]
     lib.q38b_pass_op_allgather.argtypes = [vp, i32, i32, i32]
     lib.q38b_pass_run.argtypes = [vp, i32, vp]
@@ -397,8 +398,10 @@ class Pass:
     def quantize(self, src, off, K, dst):
         self.ctx._rc(self.lib.q38b_pass_op_quantize(self.h, src, off, K, dst), "q38b_pass_op_quantize")
 
-    def gemv(self, mat, src_q, dst, off=0):
-        self.ctx._rc(self.lib.q38b_pass_op_gemv(self.h, mat, src_q, dst, off), "q38b_pass_op_gemv")
+    def gemv(self, mat, src_q, dst, off=0, local=False):
+        """local=True: the output is not pushed to the peers (a matrix every rank holds whole)."""
+        fn = self.lib.q38b_pass_op_gemv_local if local else self.lib.q38b_pass_op_gemv
+        self.ctx._rc(fn(self.h, mat, src_q, dst, off), "q38b_pass_op_gemv")
 
     def swiglu(self, g, g_off, u, u_off, n, dst_q):
         self.ctx._rc(self.lib.q38b_pass_op_swiglu(self.h, g, g_off, u, u_off, n, dst_q), "q38b_pass_op_swiglu")

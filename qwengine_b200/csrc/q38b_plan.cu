@@ -150,6 +150,9 @@ int enqueue(q38b_pass* p, int nb, cudaStream_t st) {
 // the kernel forms the Q8_K blocks in its prologue).
 struct Merged { int first_op; int n; int ops[3]; int quant; };
 
+// number of ranks a matvec step's output is pushed to (0 for steps recorded with q38b_pass_op_gemv_local)
+int pushes(const q38b_pass* p, const Op& o) { return o.d ? 0 : p->bufs[o.c].n_peer_ranks; }
+
 // Which steps of a replay can share launches.  A quantize step is folded into the
 // matvecs that read its output when they follow it directly, nothing else reads that output before it is rewritten, and
 // all of them run on the one-column kernel.  Consecutive matvecs of one format, K and row stride on one column share a launch.
@@ -219,7 +222,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
             while (on_column(k, col) && mg.n < 3) {
                 const Mat& m = p->mats[ops[k].a];
                 if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
-                if (p->bufs[ops[k].c].n_peer_ranks != p->bufs[ops[mg.first_op].c].n_peer_ranks) break;
+                if (pushes(p, ops[k]) != pushes(p, ops[mg.first_op])) break;   // outputs pushed to the peers or not: one kind per launch
                 if (nb > 1 && mg.n >= 1 && ctx->n_ranks > 1) break;   // the multi-column kernel pushes to the peers for one matrix only   // peer-visible outputs or not: one kind per launch
                 Ms[mg.n] = m.M;
                 if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)
@@ -289,7 +292,7 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                 float* peers[7];
                 int np = 0;
                 const Buf& d0 = p->bufs[g0.c];
-                if (p->peer_store && ctx->n_ranks > 1 && mg.n == 1)
+                if (p->peer_store && ctx->n_ranks > 1 && mg.n == 1 && !g0.d)
                     for (int r = 0; r < d0.n_peer_ranks; r++)
                         if (r != ctx->rank && d0.peer[r]) peers[np++] = (float*)d0.peer[r] + g0.off;
                 const int rc = q38b_gemvn_group_x(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, xf ? nullptr : sb.ptr, sb.n / 256, xf, xf_ld, nb, y,
@@ -301,7 +304,7 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
             const float* xf = mg.quant >= 0 ? (const float*)p->bufs[p->ops[mg.quant].a].ptr + p->ops[mg.quant].off : nullptr;
             float* peers[3 * 7];
             int np = 0;
-            if (p->peer_store && ctx->n_ranks > 1) {
+            if (p->peer_store && ctx->n_ranks > 1 && !g0.d) {
                 const Buf& d0 = p->bufs[g0.c];
                 for (int r = 0; r < d0.n_peer_ranks; r++) np += r != ctx->rank && d0.peer[r];
                 for (int t = 0; t < mg.n; t++) {
@@ -332,7 +335,7 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                 const Buf& d = p->bufs[o.c];
                 float* peers[7];
                 int np = 0;
-                for (int r = 0; p->peer_store && r < d.n_peer_ranks; r++)
+                for (int r = 0; p->peer_store && !o.d && r < d.n_peer_ranks; r++)
                     if (r != ctx->rank && d.peer[r]) peers[np++] = (float*)d.peer[r] + o.off;
                 rc = q38b_gemv_q8k_scatter(ctx, m.type, m.W, m.row_bytes, m.K, m.M, s.ptr, s.n / 256, nb, (float*)d.ptr + o.off, d.n, 0,
                                            peers, np, st);
@@ -577,6 +580,12 @@ int q38b_pass_op_gemv(q38b_pass* p, int mat, int src, int dst, int off) {
     if (p->bufs[src].n < m.K || off < 0 || off + m.M > p->bufs[dst].n) return Q38B_ERR_ARG;
     p->ops.push_back({OP_GEMV, mat, src, dst, 0, 0, off});
     return Q38B_OK;
+}
+
+int q38b_pass_op_gemv_local(q38b_pass* p, int mat, int src, int dst, int off) {
+    const int rc = q38b_pass_op_gemv(p, mat, src, dst, off);
+    if (rc == Q38B_OK) p->ops.back().d = 1;   // d = 1: the output is not pushed to the peers
+    return rc;
 }
 
 int q38b_pass_op_topk(q38b_pass* p, int src, int off, int n, int k, int dst) {

@@ -63,14 +63,20 @@ def total_weight_bytes(n_layers=N_LAYERS, head=True):
     return sum(m.nbytes for m in all_specs(n_layers, head))
 
 
-def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather="peer"):
+def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather="peer", replicate_small=True):
     """Records the pass on `ps` (qwengine_b200.Pass).
 
-    make_matrix(spec, rows) -> matrix id for this rank's shard of `rows` rows (rows = spec.M // world).
+    make_matrix(spec, rows) -> matrix id for this rank's shard of `rows` rows (rows = spec.M // world);
+    make_matrix(spec, spec.M, replicated=True) -> matrix id for a matrix this rank holds whole (only asked for when
+    world > 1 and replicate_small).
     world > 1: gather = "peer" pushes every output slice into the peers' buffers from the matvec kernel and
     synchronises with one cross-GPU barrier per group of matvecs (the context must be peer-connected before the pass
     is created); gather = "nccl" records an NCCL all-gather after every matvec.
-    Returns dict(in_buf, out_buf, out_len).
+    replicate_small: the attention-side projections (in_proj / q, k, v / out: 65 MB per layer) are held whole by every
+    rank and computed by every rank: streaming 65 MB costs a GPU about 11 us, sharding them over N GPUs saves at most
+    (1 - 1/N) of that and costs two cross-GPU exchanges of 4-5 us each per layer.  The FFN (115 MB per layer) and the
+    head (1 GB) are row-sharded.  Bit-identical either way: a row's result does not depend on who computes it.
+    Returns dict(in_buf, out_buf, out_len, topk_buf, topk_k).
     """
     x_in = ps.buffer_f32(HIDDEN)           # the token's hidden state: read by layer 0 only, never written, so that
                                            # every replay computes the same thing from the same input
@@ -87,32 +93,37 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
     if hasattr(ps, "set_peer_store"):
         ps.set_peer_store(peer)
 
-    def matvec(spec, src_q, dst, off):
+    whole = world > 1 and replicate_small   # the attention-side projections are not sharded
+
+    def matvec(spec, src_q, dst, off, shard=True):
+        if world > 1 and not shard:
+            ps.gemv(make_matrix(spec, spec.M, replicated=True), src_q, dst, off, local=True)
+            return
         rows = spec.M // world
         mid = make_matrix(spec, rows)
         ps.gemv(mid, src_q, dst, off + rank * rows)
         if world > 1 and not peer:
             ps.allgather(dst, off, rows)
 
-    def sync():
-        if peer:
+    def sync(after_sharded=True):
+        if peer and after_sharded:
             ps.barrier()
 
     for il in range(n_layers):
         attn, mats = layer_specs(il)
         ps.quantize(x_in if il == 0 else x, 0, HIDDEN, xq)
         if attn:
-            matvec(mats[0], xq, big, 0)
-            matvec(mats[1], xq, kv, 0)
-            matvec(mats[2], xq, kv, 1024)
+            matvec(mats[0], xq, big, 0, shard=not whole)
+            matvec(mats[1], xq, kv, 0, shard=not whole)
+            matvec(mats[2], xq, kv, 1024, shard=not whole)
             proj_out = mats[3]
         else:
-            matvec(mats[0], xq, big, 0)
+            matvec(mats[0], xq, big, 0, shard=not whole)
             proj_out = mats[1]
-        sync()
+        sync(not whole)
         ps.quantize(big, 0, INNER, iq)
-        matvec(proj_out, iq, x, 0)
-        sync()
+        matvec(proj_out, iq, x, 0, shard=not whole)
+        sync(not whole)
         ps.quantize(x, 0, HIDDEN, xq)
         gate, up, down = mats[-3:]
         matvec(gate, xq, gu, 0)

@@ -40,7 +40,7 @@ class OracleRecorder:
     def quantize(self, src, off, K, dst):
         self.bufs[dst] = oracle.port.quantize_q8k(np.ascontiguousarray(self.bufs[src][:, off:off + K]))
 
-    def gemv(self, mat, src_q, dst, off):
+    def gemv(self, mat, src_q, dst, off, local=False):
         spec, w = self.mats[mat]
         y = oracle.port.gemv(F.get(spec.fmt).type_id, w, self.bufs[src_q], spec.K)
         self.bufs[dst][:, off:off + w.shape[0]] = y
@@ -65,8 +65,8 @@ def run_cpu():
     x = synth.make_activations(2, dp.HIDDEN, seed=5)
     rec = OracleRecorder(ws, 2, world)
 
-    def make(spec, rows):
-        rec.mats.append((spec, ws[spec.name][rank * rows:(rank + 1) * rows]))
+    def make(spec, rows, replicated=False):
+        rec.mats.append((spec, ws[spec.name] if replicated else ws[spec.name][rank * rows:(rank + 1) * rows]))
         return len(rec.mats) - 1
 
     # record with the in-buffer filled: buffer 0 is the input
@@ -116,11 +116,14 @@ def run_gpu():
     outs = {}
     for nb in (1, 3):
         x = synth.make_activations(nb, dp.HIDDEN, seed=5)
-        for mode in ("single", "peer", "nccl"):
+        for mode in ("single", "peer", "peer_all_sharded", "nccl"):
             ps = q.Pass(ctx, max_nb=nb)
             w_, r_ = (1, 0) if mode == "single" else (world, rank)
-            io = dp.build(ps, lambda spec, rows: ps.matrix_upload(spec.fmt, ws[spec.name], spec.K, shard=r_, n_shards=w_),
-                          n_layers=N_LAYERS, head=False, rank=r_, world=w_, gather=mode)
+            # "peer_all_sharded": every matrix row-sharded; the other sharded modes keep the attention-side projections whole
+            io = dp.build(ps, lambda spec, rows, replicated=False: ps.matrix_upload(spec.fmt, ws[spec.name], spec.K, shard=0 if replicated else r_,
+                                                                                      n_shards=1 if replicated else w_),
+                          n_layers=N_LAYERS, head=False, rank=r_, world=w_, gather="peer" if mode.startswith("peer") else mode,
+                          replicate_small=mode != "peer_all_sharded")
             y = np.empty((nb, dp.HIDDEN), np.float32)
             for _ in range(3):      # replays reuse the flags and the buffers
                 ps.run_host(nb, io["in_buf"], x, io["out_buf"], 0, y)
@@ -129,6 +132,7 @@ def run_gpu():
             dist.barrier()
             ps.close()
         assert np.array_equal(outs[(nb, "peer")].view(np.uint32), outs[(nb, "single")].view(np.uint32)), "peer gather differs"
+        assert np.array_equal(outs[(nb, "peer_all_sharded")].view(np.uint32), outs[(nb, "single")].view(np.uint32)), "peer gather (all sharded) differs"
         assert np.array_equal(outs[(nb, "nccl")].view(np.uint32), outs[(nb, "single")].view(np.uint32)), "nccl gather differs"
     dist.barrier()
     if rank == 0:
