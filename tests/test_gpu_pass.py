@@ -277,3 +277,27 @@ def test_pass_from_gguf_file(ctx, tmp_path):
             q.Pass(ctx).matrix_from_gguf(g2, "missing")
         finally:
             g2.close()
+
+
+def test_local_matvec_step_equals_the_plain_one(ctx):
+    """q38b_pass_op_gemv_local (a matrix every rank holds whole: no peer stores) is the plain matvec step on one GPU, and
+    local and pushed steps on one column still share nothing they should not: same bits, merged or not."""
+    K, M = 1024, 520
+    w = [synth.make_weights("Q4_K", M, K, seed=90 + i) for i in range(3)]
+    x = synth.make_activations(1, K, seed=93)
+    outs = []
+    for local in (False, True):
+        for merge in (True, False):
+            ps = q.Pass(ctx, max_nb=1)
+            ps.set_merge(merge)
+            xin, xq, y = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(3 * M)
+            ps.quantize(xin, 0, K, xq)
+            for i in range(3):
+                ps.gemv(ps.matrix_upload("Q4_K", w[i], K), xq, y, i * M, local=local and i != 1)
+            out = np.empty((1, 3 * M), np.float32)
+            ps.run_host(1, xin, x, y, 0, out)
+            ctx.check()
+            outs.append(out.copy())
+            ps.close()
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint32), outs[0].view(np.uint32))
