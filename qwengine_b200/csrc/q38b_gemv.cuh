@@ -159,8 +159,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
     pdl_wait_prior();   // activations come from the previous kernel of the stream
     if (a.x_f32) {
         // quantize the columns here (every CTA, the arithmetic of quantize_q8k_kernel): one warp per 256 values, the
-        // loads of three blocks going out together
-        constexpr int QB = 3, NW = NGROUPS * GROUP_WARPS;
+        // loads of five blocks going out together (seven columns of K = 5120 are 140 blocks for 16 warps: two rounds)
+        constexpr int QB = 5, NW = NGROUPS * GROUP_WARPS;
         const int cwarp = ctid >> 5;
         const int n_blocks = a.nb * a.nsb;
         for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS)
