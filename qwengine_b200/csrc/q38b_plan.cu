@@ -223,7 +223,7 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 const Mat& m = p->mats[ops[k].a];
                 if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
                 if (pushes(p, ops[k]) != pushes(p, ops[mg.first_op])) break;   // outputs pushed to the peers or not: one kind per launch
-                if (nb > 1 && mg.n >= 1 && ctx->n_ranks > 1) break;   // the multi-column kernel pushes to the peers for one matrix only   // peer-visible outputs or not: one kind per launch
+                if (nb > 1 && mg.n >= 1 && p->peer_store && pushes(p, ops[k]) > 0) break;   // the multi-column kernel pushes to the peers for one matrix only
                 Ms[mg.n] = m.M;
                 if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)
                             : !q38b_gemvn_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms, nb)) break;
