@@ -733,7 +733,7 @@ int q38b_gemvn_group_x(q38b_ctx* ctx, uint32_t type, int n_mats, const void* con
                        const void* q8k, long long q8k_stride, const float* x_f32, long long x_f32_ld, int nb, float* const* y,
                        const long long* y_ld, float* const* y_peers, int n_peers, void* stream) {
     if (!ctx || !W || !M || !y || !y_ld || (!q8k == !x_f32) || n_mats < 1 || n_mats > GEMV_MAX_MATS) return Q38B_ERR_ARG;
-    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && (!y_peers || n_mats != 1))) return Q38B_ERR_ARG;
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return Q38B_ERR_ARG;   // y_peers[i * n_peers + r]: peer r's copy of matrix i's output
     if (!q38b_gemvn_group_plannable(ctx, type, n_mats, row_bytes, K, M, nb)) return Q38B_ERR_UNSUPPORTED;
     const int al = format_alignment(type);
     if (row_bytes % al) return Q38B_ERR_ALIGN;
@@ -765,6 +765,8 @@ int q38b_gemvn_group_x(q38b_ctx* ctx, uint32_t type, int n_mats, const void* con
     a.x_f32_ld = x_f32_ld;
     a.n_peers = n_peers;
     for (int i = 0; i < n_peers; i++) a.y_peer[i] = y_peers[i];
+    for (int m = 1; m < n_mats; m++)
+        for (int i = 0; i < n_peers; i++) a.y_peer_more[m - 1][i] = y_peers[m * n_peers + i];
     a.static_weights = ctx->static_weights;
     a.status = ctx->d_status;
     a.codebook = codebook_of(ctx, type);

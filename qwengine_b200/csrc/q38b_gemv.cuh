@@ -45,6 +45,7 @@ struct GemvArgs {
     float* y;                // y[c * y_ld + r]
     long long y_ld;
     float* y_peer[7];        // the same output position in the other GPUs' buffers (peer stores), n_peers used
+    float* y_peer_more[GEMV_MAX_MATS - 1][7];   // the same for the further matrices of the launch
     int n_peers;
     int static_weights;     // 1: W was written long before this launch, the producer need not wait for earlier kernels
     int* status;             // device status word (OR of ST_* bits)
@@ -290,7 +291,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
                 float* yo = (mi == 0 ? a.y : a.y_more[mi - 1]) + (size_t)col * (mi == 0 ? a.y_ld : a.y_ld_more[mi - 1]) + row;
                 const float out = a.accumulate ? *yo + v : v;
                 *yo = out;
-                for (int pr = 0; pr < a.n_peers; pr++) a.y_peer[pr][(size_t)col * a.y_ld + row] = out;
+                for (int pr = 0; pr < a.n_peers; pr++)
+                    (mi == 0 ? a.y_peer[pr] : a.y_peer_more[mi - 1][pr])[(size_t)col * (mi == 0 ? a.y_ld : a.y_ld_more[mi - 1]) + row] = out;
             }
         }
     }

@@ -43,7 +43,7 @@ extern "C" int q38b_gemv_group_peers(q38b_ctx* ctx, uint32_t type, int n_mats, c
 // the same for the multi-column kernel (nb columns of Q8_K blocks, q8k_stride blocks apart; y[i][c * y_ld[i] + r]); no peers
 extern "C" int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb);
 // the same with the columns given as floats (x_f32, x_f32_ld floats apart; quantized inside the kernel) instead of Q8_K
-// blocks, and, for a single matrix, with peer stores
+// blocks, and with peer stores (y_peers[i * n_peers + r]: peer r's copy of matrix i's output)
 extern "C" int q38b_gemvn_group_x(q38b_ctx* ctx, uint32_t type, int n_mats, const void* const* W, size_t row_bytes, int K, const int* M,
                                   const void* q8k, long long q8k_stride, const float* x_f32, long long x_f32_ld, int nb, float* const* y,
                                   const long long* y_ld, float* const* y_peers, int n_peers, void* stream);

@@ -223,7 +223,6 @@ void merge_plan(const q38b_pass* p, int nb, std::vector<Merged>& out, std::vecto
                 const Mat& m = p->mats[ops[k].a];
                 if (m.type != m0.type || m.K != m0.K || m.row_bytes != m0.row_bytes) break;
                 if (pushes(p, ops[k]) != pushes(p, ops[mg.first_op])) break;   // outputs pushed to the peers or not: one kind per launch
-                if (nb > 1 && mg.n >= 1 && p->peer_store && pushes(p, ops[k]) > 0) break;   // the multi-column kernel pushes to the peers for one matrix only
                 Ms[mg.n] = m.M;
                 if (nb == 1 ? !q38b_gemv_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms)
                             : !q38b_gemvn_group_plannable(ctx, m0.type, mg.n + 1, m0.row_bytes, m0.K, Ms, nb)) break;
@@ -289,12 +288,20 @@ int enqueue_ops(q38b_pass* p, int nb, cudaStream_t st) {
                     xf = (const float*)src.ptr + p->ops[mg.quant].off;
                     xf_ld = src.n;
                 }
-                float* peers[7];
+                float* peers[3 * 7];
                 int np = 0;
-                const Buf& d0 = p->bufs[g0.c];
-                if (p->peer_store && ctx->n_ranks > 1 && mg.n == 1 && !g0.d)
-                    for (int r = 0; r < d0.n_peer_ranks; r++)
-                        if (r != ctx->rank && d0.peer[r]) peers[np++] = (float*)d0.peer[r] + g0.off;
+                if (p->peer_store && ctx->n_ranks > 1 && !g0.d) {
+                    const Buf& d0 = p->bufs[g0.c];
+                    for (int r = 0; r < d0.n_peer_ranks; r++) np += r != ctx->rank && d0.peer[r];
+                    for (int t = 0; t < mg.n; t++) {
+                        const Op& g = p->ops[mg.ops[t]];
+                        const Buf& d = p->bufs[g.c];
+                        int k = 0;
+                        for (int r = 0; r < d.n_peer_ranks; r++)
+                            if (r != ctx->rank && d.peer[r]) peers[t * np + k++] = (float*)d.peer[r] + g.off;
+                        if (k != np) return Q38B_ERR_ARG;   // all outputs of one launch live in peer-visible buffers, or none
+                    }
+                }
                 const int rc = q38b_gemvn_group_x(ctx, m0.type, mg.n, W, m0.row_bytes, m0.K, M, xf ? nullptr : sb.ptr, sb.n / 256, xf, xf_ld, nb, y,
                                                   ylds, peers, np, st);
                 if (rc != Q38B_OK) return rc;
