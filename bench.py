@@ -385,10 +385,12 @@ def run_ours(args):
     n_layers = args.layers
     ps = q.Pass(ctx, max_nb=7)
     counter = [0]
+    made = []   # the weight tensors in the order the pass asked for them
 
     def make_matrix(spec, rows, replicated=False):
         counter[0] += 1   # a replicated matrix has the same bytes on every rank
         w = device_weights(torch, spec, rows, seed=1000 * counter[0] + (0 if replicated else rank), scale=dp.UNIT_GAIN_SCALE.get(spec.fmt, 1e-3))
+        made.append(w)
         return ps.matrix_device(spec.fmt, w, spec.K)
 
     io = dp.build(ps, make_matrix, n_layers=n_layers, head=True, rank=rank, world=world, gather=args.gather)
@@ -424,6 +426,18 @@ def run_ours(args):
         ms1 = timed(1, args.steps, warm)
     ms7 = timed(7, max(3, args.steps // 2), 3)
     ctx.check()
+    # What the cross-GPU exchanges cost: the same pass on the same weights with no exchange recorded (no peer stores, no
+    # barriers: every rank's share of the work alone; its results are incomplete and are not used).
+    exchange = None
+    if world > 1:
+        it = iter(made)
+        ps_alone = q.Pass(ctx, max_nb=1)
+        dp.build(ps_alone, lambda spec, rows, replicated=False: ps_alone.matrix_device(spec.fmt, next(it), spec.K), n_layers=n_layers, head=True,
+                 rank=rank, world=world, gather="none")
+        t_alone = torch.tensor([time_pass(torch, ps_alone, 1, max(3, args.steps // 2), warm=3)], device="cuda")
+        dist.all_reduce(t_alone, op=dist.ReduceOp.MAX)
+        ps_alone.close()
+        exchange = {"ms_per_step_without_exchange": round(float(t_alone.item()), 4), "share_of_step": round(1.0 - float(t_alone.item()) / ms1, 4)}
     logits = ps.buffer_tensor(io["out_buf"])
     finite = bool(torch.isfinite(logits[:7]).all().item())
 
@@ -507,6 +521,7 @@ def run_ours(args):
             "dtype": "int8", "data": "synthetic",
             "config": run_config(n_layers, world, args.gather),
             "checks": {"outputs_finite": finite, "topk_matches_logits": topk_ok, "sharded_bits_equal_single": shard_ok},
+            "exchange": exchange,
             "tokens_per_s": round(1e3 / ms1, 1),
             "frac_of_nominal_8TBps": round(value / world / HBM_NOMINAL_GBS, 4),
             "nb7": {"ms_per_step": round(ms7, 4), "value": round(total_bytes / ms7 / 1e6, 1), "tokens_per_s": round(7e3 / ms7, 1),

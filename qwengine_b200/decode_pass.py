@@ -71,7 +71,8 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
     world > 1 and replicate_small).
     world > 1: gather = "peer" pushes every output slice into the peers' buffers from the matvec kernel and
     synchronises with one cross-GPU barrier per group of matvecs (the context must be peer-connected before the pass
-    is created); gather = "nccl" records an NCCL all-gather after every matvec.
+    is created); gather = "nccl" records an NCCL all-gather after every matvec; gather = "none" records no exchange at
+    all (this rank's share of the work alone, for timing: the results are incomplete).
     replicate_small: the attention-side projections (in_proj / q, k, v / out: 65 MB per layer) are held whole by every
     rank and computed by every rank: streaming 65 MB costs a GPU about 11 us, sharding them over N GPUs saves at most
     (1 - 1/N) of that and costs two cross-GPU exchanges of 4-5 us each per layer.  The FFN (115 MB per layer) and the
@@ -102,7 +103,7 @@ def build(ps, make_matrix, n_layers=N_LAYERS, head=True, rank=0, world=1, gather
         rows = spec.M // world
         mid = make_matrix(spec, rows)
         ps.gemv(mid, src_q, dst, off + rank * rows)
-        if world > 1 and not peer:
+        if world > 1 and gather == "nccl":
             ps.allgather(dst, off, rows)
 
     def sync(after_sharded=True):
