@@ -19,6 +19,7 @@ using namespace q38b;
 namespace {
 
 constexpr int NGROUPS = 2;
+constexpr long long GEMV_PART_ITEMS = 131072;   // (tile, K-part) sums the scratch area of the multi-column kernel holds: 64 MB
 constexpr int GEMV_THREADS = 32 * (1 + NGROUPS * GROUP_WARPS);
 
 #define Q38B_CUDA(ctx, call)                                   \
@@ -83,9 +84,22 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
         if (i < n_mats) a.n_tiles += (Ms[i] + TILE_ROWS - 1) / TILE_ROWS;
     }
     for (int i = n_mats; i < GEMV_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
+    // K-parts for rows longer than 8192: about 12 super-blocks each (8 for Q8_0's larger blocks), boundaries at multiples
+    // of 4 super-blocks.  A rule of K and the format alone, so that a sum is built from the same pieces whatever the
+    // column count, the row count or the GPU count.
+    const int n_units = (nsb + 3) / 4;
+    const int units_per_part = type == T_Q8_0 ? 2 : 3;
+    a.n_parts = K <= 8192 ? 1 : (n_units + units_per_part - 1) / units_per_part;
+    if (a.n_parts > GEMV_MAX_PARTS) a.n_parts = GEMV_MAX_PARTS;   // longer parts; the plan fails below if they do not fit
+    int max_part = 0;
+    for (int q = 0; q <= a.n_parts; q++) a.part_sb0[q] = std::min(nsb, 4 * (int)((long long)n_units * q / a.n_parts));
+    for (int q = 0; q < a.n_parts; q++) max_part = std::max(max_part, a.part_sb0[q + 1] - a.part_sb0[q]);
+    if (a.n_parts > 1 && (long long)a.n_tiles * a.n_parts > GEMV_PART_ITEMS) return Q38B_ERR_NOMEM;   // the scratch area's size
+    // a CTA's range of (part, tile) items touches at most two neighbouring parts: it stages their activations only
+    a.act_sb = a.n_parts == 1 ? nsb : std::min(nsb, 2 * max_part);
     a.off_actd = 256;
-    a.off_actq = a.off_actd + align_up(nsb * 32, 16);
-    a.off_cb = a.off_actq + align_up(nb * K, 128);
+    a.off_actq = a.off_actd + align_up(a.act_sb * 32, 16);
+    a.off_cb = a.off_actq + align_up(nb * a.act_sb * 256, 128);
     // rows of a group land 16 bytes (32 for the formats read with 64-bit loads) further round the 32 banks
     const int bank_skew = (type == T_Q4_K || type == T_Q5_K) ? 32 : 16;
     for (int rep_log2 = cb_entries ? 5 : 0; rep_log2 >= 0; rep_log2 -= (rep_log2 == 5 ? 2 : 3)) {
@@ -93,11 +107,11 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
         a.off_red = a.off_cb + align_up(cb_entries * 4 << rep_log2, 128);
         a.off_stage = a.off_red + NGROUPS * 2 * GROUP_THREADS * 16;
         const int avail = budget - a.off_stage;
-        // K-chunk sizes to try: the whole row, then fewer super-blocks, multiples of 4 first (8 half super-blocks
-        // per 4 keep the 8 warps of a group evenly loaded)
+        // K-chunk sizes to try: the whole row (or part), then -- whole rows only -- fewer super-blocks, multiples of 4
+        // first (8 half super-blocks per 4 keep the 8 warps of a group evenly loaded)
         for (int pass = 0; pass < 2; pass++)
-            for (int cs = nsb; cs >= 1; cs--) {
-                const bool even = cs == nsb || cs % 4 == 0;
+            for (int cs = max_part; cs >= (a.n_parts == 1 ? 1 : max_part); cs--) {
+                const bool even = cs == max_part || cs % 4 == 0;
                 if (even != (pass == 0)) continue;
                 int slot = align_up(cs * bb + 32, 16);
                 while (slot % 128 != bank_skew) slot += 16;
@@ -106,13 +120,13 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
                 const int stages = avail / stage;
                 if (stages < 3 && !(stages == 2 && cs == 1)) continue;
                 a.chunk_sb = cs;
-                a.n_chunks = (nsb + cs - 1) / cs;
+                a.n_chunks = (max_part + cs - 1) / cs;
                 a.n_stages = std::min(stages, MAX_STAGES);
                 a.slot_stride = slot;
                 a.stage_bytes = stage;
                 p->smem = a.off_stage + a.n_stages * stage + 128;
-                const int ctas_needed = (a.n_tiles + NGROUPS - 1) / NGROUPS;
-                p->grid = std::max(1, std::min(ctx->sm_count, ctas_needed));
+                const long long items = (long long)a.n_tiles * a.n_parts;
+                p->grid = (int)std::max<long long>(1, std::min<long long>(ctx->sm_count, (items + NGROUPS - 1) / NGROUPS));
                 return Q38B_OK;
             }
         if (!cb_entries) break;
@@ -122,7 +136,7 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
 
 template <int FMT>
 int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
-    auto kern = gemv_kernel<FMT, NGROUPS>;
+    auto kern = p.a.n_parts > 1 ? gemv_kernel<FMT, NGROUPS, true> : gemv_kernel<FMT, NGROUPS, false>;
     const int rc = ensure_kernel_smem(ctx, (const void*)kern, ctx->smem_optin, false);
     if (rc != Q38B_OK) return rc;
     cudaLaunchConfig_t cfg;
@@ -136,7 +150,10 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
-    Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p.a));
+    GemvArgs a = p.a;
+    a.parts = ctx->d_parts;
+    a.part_count = ctx->d_part_count;
+    Q38B_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, a));
     return Q38B_OK;
 }
 
@@ -394,12 +411,17 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
             cudaGetSymbolAddress((void**)&t16[2], q38b_iq2s_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[3], q38b_iq1s_codes) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         for (int i = 0; i < 4; i++) c->d_code16[i] = (const uint32_t*)t16[i];
         // candidate lists of q38b_topk: 8 columns x TOPK_MAX_CHUNKS lists x TOPK_MAX_K pairs (1.5 MB), so that the decode path never allocates
+        if (cudaMalloc(&c->d_parts, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
+        if (cudaMalloc(&c->d_part_count, (size_t)GEMV_PART_ITEMS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
+        if (cudaMemset(c->d_part_count, 0, (size_t)GEMV_PART_ITEMS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         if (cudaMalloc(&c->d_topk, (size_t)8 * TOPK_MAX_CHUNKS * TOPK_MAX_K * sizeof(TopkPair)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
     } while (0);
     if (rc != Q38B_OK) {
         c->last_cuda = (int)cudaGetLastError();
         if (c->d_status) cudaFree(c->d_status);
         if (c->d_topk) cudaFree(c->d_topk);
+        if (c->d_parts) cudaFree(c->d_parts);
+        if (c->d_part_count) cudaFree(c->d_part_count);
         delete c;
         return rc;
     }
@@ -411,6 +433,8 @@ void q38b_ctx_destroy(q38b_ctx* ctx) {
     if (!ctx) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_topk) cudaFree(ctx->d_topk);
+    if (ctx->d_parts) cudaFree(ctx->d_parts);
+    if (ctx->d_part_count) cudaFree(ctx->d_part_count);
     if (ctx->d_flags) cudaFree(ctx->d_flags);
     delete ctx;
 }
@@ -533,11 +557,6 @@ int q38b_quantize_q8k(q38b_ctx* ctx, const float* x, long long x_ld, int K, int 
 }
 
 // takes the cross-GPU barrier the planner left for the next launch, if any
-// rows so long that the multi-column kernel runs them as two launches over the halves of K
-static bool gemvn_splits_k(uint32_t type, int K) {
-    return K > 8192 && (K / 256) % 2 == 0 && type != T_Q8_0 && ((size_t)(K / 512) * block_bytes((int)type)) % 16 == 0;
-}
-
 static PeerSync take_pending_sync(q38b_ctx* ctx) {
     PeerSync ps;
     memset(&ps, 0, sizeof(ps));
@@ -673,16 +692,21 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
             return dispatch_gemv1(ctx, type, p1, st);
         }
     }
-    // Long rows on the multi-column kernel: the staged activations (nb x K bytes) would leave almost no shared memory
-    // for the weight stages, so the matvec runs as two launches over the two halves of K, the second accumulating onto
-    // the first.  The rule depends on K and the format alone: columns stay bit-identical for every nb this kernel serves.
-    if (gemvn_splits_k(type, K)) {   // (the second half must start 16-byte aligned like any matrix)
-        const int Kh = K / 2;
-        const size_t w_off = (size_t)(Kh / 256) * block_bytes((int)type);
-        int rc = q38b_gemv_q8k_scatter(ctx, type, W, row_bytes, Kh, M, q8k, q8k_stride, nb, y, y_ld, accumulate, y_peers, n_peers, stream);
-        if (rc != Q38B_OK) return rc;
-        return q38b_gemv_q8k_scatter(ctx, type, (const uint8_t*)W + w_off, row_bytes, Kh, M, (const uint8_t*)q8k + (size_t)(Kh / 256) * Q8K_BYTES,
-                                     q8k_stride, nb, y, y_ld, 1, y_peers, n_peers, stream);
+    {   // more (tile, K-part) sums than the scratch area holds: one launch per block of rows
+        const int n_units = (K / 256 + 3) / 4, upp = type == T_Q8_0 ? 2 : 3;
+        const int n_parts = K <= 8192 ? 1 : std::min(GEMV_MAX_PARTS, (n_units + upp - 1) / upp);
+        const long long rows_per_launch = GEMV_PART_ITEMS / n_parts * TILE_ROWS;
+        if (n_parts > 1 && M > rows_per_launch) {
+            for (long long m0 = 0; m0 < M; m0 += rows_per_launch) {
+                const int m = (int)std::min<long long>(rows_per_launch, M - m0);
+                float* peers_at[7];
+                for (int i = 0; i < n_peers; i++) peers_at[i] = y_peers[i] + m0;
+                const int rc = q38b_gemv_q8k_scatter(ctx, type, (const uint8_t*)W + (size_t)m0 * row_bytes, row_bytes, K, m, q8k, q8k_stride, nb, y + m0,
+                                                     y_ld, accumulate, n_peers ? peers_at : nullptr, n_peers, stream);
+                if (rc != Q38B_OK) return rc;
+            }
+            return Q38B_OK;
+        }
     }
     Plan p;
     memset(&p, 0, sizeof(p));
@@ -718,7 +742,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
 
 int q38b_gemvn_group_plannable(const q38b_ctx* ctx, uint32_t type, int n_mats, size_t row_bytes, int K, const int* M, int nb) {
     if (!ctx || n_mats < 1 || n_mats > GEMV_MAX_MATS || !known_format(type) || K <= 0 || K % 256 || nb < 1 || nb > 8) return 0;
-    if (gemvn_splits_k(type, K) || row_bytes < q38b_row_bytes(type, K)) return 0;
+    if (row_bytes < q38b_row_bytes(type, K)) return 0;
     Plan p;
     memset(&p, 0, sizeof(p));
     return plan_gemv(ctx, type, K, M, n_mats, nb, &p) == Q38B_OK;

@@ -10,7 +10,13 @@
 //     fragments (q38b_decode.cuh) and keep float partial sums per (row, column); at the end of a tile the 8
 //     partial sums are added in a fixed order through shared memory, so results do not depend on timing;
 //   * activations (Q8_K int8 values and block scales of all columns) and the codebook are staged in shared memory
-//     once per CTA.
+//     once per CTA;
+//   * rows longer than 8192 are cut into K-parts of about 12 super-blocks (a rule of K and the format alone).  The work
+//     items (part, tile), part-major, are dealt to the CTAs as equal contiguous ranges: a CTA then needs the
+//     activations of at most two neighbouring parts, which leaves the shared memory to the weight stages, and 320
+//     tiles of 68 super-blocks keep 148 SMs evenly busy instead of 24 of them working a second round.  A part's sums
+//     go to a scratch area in global memory; whichever group adds a tile's last part (a counter per tile, no waiting)
+//     reads them all back in part order and stores the row sums, so the result does not depend on who computed what.
 // Every column is computed by the same instructions whatever nb is, so column c of an nb-column call is
 // bit-identical to a 1-column call on that column (the reference promises the same: src/cuda/gemv.cuh:31-34).
 #pragma once
@@ -27,6 +33,7 @@ constexpr int MAX_STAGES = 8;
 constexpr int Q8K_BYTES = 292;   // float d | int8 qs[256] | int16 bsums[16]  (src/quant/quant_formats.h:95)
 
 constexpr int GEMV_MAX_MATS = 3;
+constexpr int GEMV_MAX_PARTS = 32;
 
 struct GemvArgs {
     // up to three matrices of one format, K and row stride on the same activation columns: their 16-row tiles form one
@@ -54,7 +61,12 @@ struct GemvArgs {
     int nsb;                 // super-blocks per row
     int n_tiles;
     int chunk_sb;            // super-blocks per K-chunk (last chunk may be shorter)
-    int n_chunks;
+    int n_chunks;            // K-chunks per work item (1 when the row is cut into parts: a part is one chunk)
+    int n_parts;             // K-parts of a row (1: the whole row is one work item per tile)
+    int part_sb0[GEMV_MAX_PARTS + 1];   // first super-block of each part (multiples of 4); [n_parts] = nsb
+    int act_sb;              // super-blocks of activations a CTA stages per column (nsb, or two parts' worth)
+    float* parts;            // n_parts > 1: 128 sums (16 rows x 8 columns) per (tile, part)
+    int* part_count;         // ... and per tile how many parts are written (zero between launches)
     int n_stages;
     int slot_stride;         // bytes per row slot inside a stage (multiple of 16)
     int cb_rep_log2;         // log2 of codebook replicas
@@ -63,15 +75,28 @@ struct GemvArgs {
     int stage_bytes;         // TILE_ROWS * slot_stride
 };
 
-template <int FMT, int NGROUPS>
+template <int FMT, int NGROUPS, bool PARTED>
 __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];   // plain pointer arithmetic from here on keeps loads in the shared space
     uint8_t* smem = smem_raw;
-    // One ring of stages for all groups: this CTA's tiles k = 0, 1, 2, ... (tile blockIdx.x + gridDim.x * k) go to group
-    // k % NGROUPS; the n_chunks stage fills of tile k are fills k * n_chunks .. + n_chunks - 1 of the ring.
+    // One ring of stages for all groups: this CTA's work items k = 0, 1, 2, ... go to group k % NGROUPS; the n_chunks
+    // stage fills of item k are fills k * n_chunks .. + n_chunks - 1 of the ring.  Whole rows: item k is tile
+    // blockIdx.x + gridDim.x * k.  K-parts: the items (part, tile), part-major, are cut into gridDim.x equal ranges.
     uint64_t* bars = (uint64_t*)smem;                       // full[MAX_STAGES], empty[MAX_STAGES]
     volatile int* abort_flag = (volatile int*)(smem + 8 * 2 * MAX_STAGES);   // the header ends well before off_actd = 256
     int* issued = (int*)abort_flag + 1;                     // stage fills the producer has issued so far
+    volatile int* last_flag = (volatile int*)abort_flag + 2;   // [NGROUPS]: this group wrote the last part of a tile
+    constexpr bool parted = PARTED;                         // a.n_parts > 1
+    const long long n_items = (long long)a.n_tiles * (parted ? a.n_parts : 1);
+    const long long item_lo = parted ? n_items * blockIdx.x / gridDim.x : 0;
+    const int my_items = parted ? (int)(n_items * (blockIdx.x + 1) / gridDim.x - item_lo)
+                                : (a.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // (the grid is never larger than n_tiles)
+    // the activations this CTA stages: super-blocks [win0, win0 + win_sb) of every column
+    const int part_first = parted ? (int)(item_lo / a.n_tiles) : 0;
+    const int part_last = parted && my_items > 0 ? (int)((item_lo + my_items - 1) / a.n_tiles) : part_first;
+    const int win0 = parted ? a.part_sb0[part_first] : 0;
+    const int win_sb = parted ? a.part_sb0[part_last + 1] - win0 : a.nsb;
+    const int act_ld = a.act_sb * 256;                      // bytes between the staged columns
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
@@ -87,7 +112,6 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
     pdl_launch_dependents();
 
     const int packed_row = a.nsb * Unit<FMT>::BLOCK_BYTES;
-    const int chunk_bytes_full = a.chunk_sb * Unit<FMT>::BLOCK_BYTES;
 
     if (warp == 0) {
         // ---------------- producer: resident weights do not depend on earlier kernels, start at once ----------------
@@ -95,14 +119,15 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         if (lane < TILE_ROWS) {
             int item = 0, stage = 0;
             uint32_t use = 0;
-            for (int k = 0;; k++) {
-                const int gtile = blockIdx.x + gridDim.x * k;
-                if (gtile >= a.n_tiles) break;
+            for (int k = 0; k < my_items; k++) {
+                const int part = parted ? (int)((item_lo + k) / a.n_tiles) : 0;
+                const int gtile = parted ? (int)(item_lo + k - (long long)part * a.n_tiles) : (int)(blockIdx.x + gridDim.x * k);
                 const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
                 const int tile = gtile - a.tile_start[mi];
                 const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
                 const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
                 const uintptr_t safe_end = ((uintptr_t)Wm + (uintptr_t)(Mm - 1) * a.row_bytes + packed_row) & ~(uintptr_t)15;
+                const int part_sb = parted ? a.part_sb0[part] : 0, part_end = parted ? a.part_sb0[part + 1] : a.nsb;
                 for (int chunk = 0; chunk < a.n_chunks; chunk++) {
                     const uint32_t full = smem_u32(&bars[stage]);
                     const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
@@ -111,8 +136,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
                     if (row >= Mm) {
                         mbar_arrive(full);
                     } else {
-                        const int sb0 = chunk * a.chunk_sb;
-                        const int len = (sb0 + a.chunk_sb <= a.nsb ? chunk_bytes_full : (a.nsb - sb0) * Unit<FMT>::BLOCK_BYTES);
+                        const int sb0 = part_sb + chunk * a.chunk_sb;
+                        const int len = min(a.chunk_sb, part_end - sb0) * Unit<FMT>::BLOCK_BYTES;
                         const uintptr_t src = (uintptr_t)Wm + (uintptr_t)row * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
                         const uintptr_t lo = src & ~(uintptr_t)15;
                         uintptr_t hi = (src + len + 15) & ~(uintptr_t)15;
@@ -149,8 +174,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
     const int g = lane >> 2, t = lane & 3;
 
     // stage the codebook (replicated so that lane l reads bank l) and the activations
-    float* actd = (float*)(smem + a.off_actd);       // [nsb][8]
-    uint8_t* actq = smem + a.off_actq;               // [nb][K], staged order
+    float* actd = (float*)(smem + a.off_actd);       // [win_sb][8]
+    uint8_t* actq = smem + a.off_actq;               // [nb][act_sb * 256], staged order
     uint32_t* cbw = (uint32_t*)(smem + a.off_cb);
     constexpr int CBN = Unit<FMT>::CODEBOOK_ENTRIES;
     if (CBN > 0) {
@@ -163,8 +188,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
         // loads of five blocks going out together (seven columns of K = 5120 are 140 blocks for 16 warps: two rounds)
         constexpr int QB = 5, NW = NGROUPS * GROUP_WARPS;
         const int cwarp = ctid >> 5;
-        const int n_blocks = a.nb * a.nsb;
-        for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS)
+        const int n_blocks = a.nb * win_sb;
+        for (int i = ctid; i < win_sb * 8; i += NGROUPS * GROUP_THREADS)
             if ((i & 7) >= a.nb) actd[i] = 0.0f;
         for (int b0 = cwarp; b0 < n_blocks; b0 += QB * NW) {
             float4 lo4[QB], hi4[QB];
@@ -174,8 +199,8 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
                 lo4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                 hi4[j] = lo4[j];
                 if (b < n_blocks) {
-                    const int c = b / a.nsb, sb = b - c * a.nsb;
-                    const float* src = a.x_f32 + (size_t)c * a.x_f32_ld + (size_t)sb * 256 + 8 * lane;
+                    const int c = b / win_sb, sb = b - c * win_sb;   // sb counts from the window's first super-block
+                    const float* src = a.x_f32 + (size_t)c * a.x_f32_ld + (size_t)(win0 + sb) * 256 + 8 * lane;
                     lo4[j] = *(const float4*)src;
                     hi4[j] = *(const float4*)(src + 4);
                 }
@@ -184,14 +209,14 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             for (int j = 0; j < QB; j++) {
                 const int b = b0 + j * NW;
                 if (b >= n_blocks) continue;
-                const int c = b / a.nsb, sb = b - c * a.nsb;
+                const int c = b / win_sb, sb = b - c * win_sb;
                 const float v[8] = {lo4[j].x, lo4[j].y, lo4[j].z, lo4[j].w, hi4[j].x, hi4[j].y, hi4[j].z, hi4[j].w};
                 uint32_t w0, w1;
                 int s8;
                 float d;
                 q8k_block_core(v, w0, w1, s8, d);
                 if (lane == 0) actd[sb * 8 + c] = d;
-                uint8_t* dst = actq + (size_t)c * a.K + sb * 256;
+                uint8_t* dst = actq + (size_t)c * act_ld + sb * 256;
                 if (FMT == T_IQ4_XS) {
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
@@ -204,25 +229,45 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             }
         }
     } else {
-    for (int i = ctid; i < a.nsb * 8; i += NGROUPS * GROUP_THREADS) {
-        const int sb = i >> 3, c = i & 7;
-        actd[i] = c < a.nb ? *(const float*)(a.xq + ((size_t)c * a.x_stride + sb) * Q8K_BYTES) : 0.0f;
-    }
-    for (int i = ctid; i < a.nb * (a.K / 4); i += NGROUPS * GROUP_THREADS) {
-        const int c = i / (a.K / 4), w = i % (a.K / 4);       // word w of column c
-        const int sb = w >> 6, wi = w & 63;
-        const uint32_t v = *(const uint32_t*)(a.xq + ((size_t)c * a.x_stride + sb) * Q8K_BYTES + 4 + 4 * wi);
-        uint8_t* dst = actq + (size_t)c * a.K + sb * 256;
-        if (FMT == T_IQ4_XS) {
+        // copy the Q8_K blocks' scales and values: one warp per block (256 values = 64 words: lane l takes words w and
+        // w + 4 of the 32-value group l / 4, w = l % 4), the loads of eight blocks going out together
+        constexpr int SB = 8, NW = NGROUPS * GROUP_WARPS;
+        const int cwarp = ctid >> 5;
+        const int n_blocks = a.nb * win_sb;
+        for (int i = ctid; i < win_sb * 8; i += NGROUPS * GROUP_THREADS)
+            if ((i & 7) >= a.nb) actd[i] = 0.0f;
+        const int wofs = 8 * (lane >> 2) + (lane & 3);
+        for (int b0 = cwarp; b0 < n_blocks; b0 += SB * NW) {
+            uint32_t w0[SB], w1[SB], dw[SB];
 #pragma unroll
-            for (int b = 0; b < 4; b++) {
-                const int k = 4 * wi + b;
-                dst[(k & ~31) + act_stage_pos(FMT, k & 31)] = (uint8_t)(v >> (8 * b));
+            for (int jb = 0; jb < SB; jb++) {
+                const int b = b0 + jb * NW;
+                w0[jb] = w1[jb] = dw[jb] = 0u;
+                if (b < n_blocks) {
+                    const int c = b / win_sb, sb = b - c * win_sb;
+                    const uint32_t* blk = (const uint32_t*)(a.xq + ((size_t)c * a.x_stride + win0 + sb) * Q8K_BYTES);
+                    w0[jb] = blk[1 + wofs];
+                    w1[jb] = blk[5 + wofs];
+                    if (lane == 0) dw[jb] = blk[0];
+                }
             }
-        } else {
-            *(uint32_t*)(dst + 4 * wi) = v;
+#pragma unroll
+            for (int jb = 0; jb < SB; jb++) {
+                const int b = b0 + jb * NW;
+                if (b >= n_blocks) continue;
+                const int c = b / win_sb, sb = b - c * win_sb;
+                if (lane == 0) actd[sb * 8 + c] = __uint_as_float(dw[jb]);
+                uint8_t* dst = actq + (size_t)c * act_ld + sb * 256 + 32 * (lane >> 2);
+                if (FMT == T_IQ4_XS) {
+                    // act_stage_pos: value k of the group goes to 8 (k % 16 / 4) + 2 (k % 4) + k / 16, i.e. the bytes of
+                    // words w and w + 4 interleaved
+                    *(uint2*)(dst + 8 * (lane & 3)) = make_uint2(prmt(w0[jb], w1[jb], 0x5140u), prmt(w0[jb], w1[jb], 0x7362u));
+                } else {
+                    *(uint32_t*)(dst + 4 * (lane & 3)) = w0[jb];
+                    *(uint32_t*)(dst + 16 + 4 * (lane & 3)) = w1[jb];
+                }
+            }
         }
-    }
     }
     named_bar_sync(15, NGROUPS * GROUP_THREADS);
 
@@ -233,29 +278,60 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
 
     float* red = (float*)(smem + a.off_red) + (size_t)grp * 2 * GROUP_THREADS * 4;
     const bool bvalid = g < a.nb;
-    const uint8_t* bq_col = actq + (size_t)(bvalid ? g : 0) * a.K;
+    const uint8_t* bq_col = actq + (size_t)(bvalid ? g : 0) * act_ld - (size_t)win0 * 256;   // indexed by the super-block's number in the row
 
+    const float* actd_row = actd - win0 * 8;
+    int pending = -1, pending_tile = 0;   // thread 0 of the group, K-parts: the count it drew for the item before, and that item's tile
+    // K-parts: the 128 summing threads of the group look at the count drawn for the item before (by now it has arrived)
+    // and, if that was the tile's last part, add the parts up in part order and store the rows
+    auto finish_pending = [&](bool more) {
+        if (gtid == 0) last_flag[grp] = pending == a.n_parts - 1 ? pending_tile + 1 : 0;
+        named_bar_sync(3 + grp, 128);
+        const int ft = last_flag[grp] - 1;
+        if (ft >= 0) {
+            __threadfence();
+            const float* sp = a.parts + (size_t)ft * a.n_parts * 128 + gtid;
+            float v = __ldcg(sp);
+            for (int p2 = 1; p2 < a.n_parts; p2++) v += __ldcg(sp + p2 * 128);
+            if (gtid == 0) a.part_count[ft] = 0;   // ready for the next launch
+            const int ls = gtid & 31, i = gtid >> 5;
+            const int mi = (ft >= a.tile_start[1]) + (ft >= a.tile_start[2]);
+            const int row = (ft - a.tile_start[mi]) * TILE_ROWS + (ls >> 2) + 8 * (i >> 1);
+            const int col = 2 * (ls & 3) + (i & 1);
+            const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
+            if (row < Mm && col < a.nb) {
+                float* yo = (mi == 0 ? a.y : a.y_more[mi - 1]) + (size_t)col * (mi == 0 ? a.y_ld : a.y_ld_more[mi - 1]) + row;
+                const float out = a.accumulate ? *yo + v : v;
+                *yo = out;
+                for (int pr = 0; pr < a.n_peers; pr++)
+                    (mi == 0 ? a.y_peer[pr] : a.y_peer_more[mi - 1][pr])[(size_t)col * (mi == 0 ? a.y_ld : a.y_ld_more[mi - 1]) + row] = out;
+            }
+        }
+        if (more) named_bar_sync(3 + grp, 128);   // the flag is rewritten only after everyone has read it
+    };
     for (int ti = 0;; ti++) {
-        const int k = grp + NGROUPS * ti;                // this CTA's tile number k
-        const int gtile = blockIdx.x + gridDim.x * k;
-        if (gtile >= a.n_tiles) break;
+        const int k = grp + NGROUPS * ti;                // this CTA's work item k
+        if (k >= my_items) break;
+        const int part = parted ? (int)((item_lo + k) / a.n_tiles) : 0;
+        const int gtile = parted ? (int)(item_lo + k - (long long)part * a.n_tiles) : (int)(blockIdx.x + gridDim.x * k);
         const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
         const int tile = gtile - a.tile_start[mi];        // tile of matrix mi
         const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const int rowA = tile * TILE_ROWS + g, rowB = rowA + 8;
+        const int part_sb = parted ? a.part_sb0[part] : 0, part_end = parted ? a.part_sb0[part + 1] : a.nsb;
         for (int chunk = 0; chunk < a.n_chunks; chunk++) {
             const int item = k * a.n_chunks + chunk;
             const int stage = item % a.n_stages;
             const uint32_t use = (uint32_t)(item / a.n_stages);
             const uint32_t full = smem_u32(&bars[stage]);
             const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
-            // a group reads only its own tiles' fills, so it skips uses of a barrier: once the fill has been issued (the
+            // a group reads only its own items' fills, so it skips uses of a barrier: once the fill has been issued (the
             // producer issues it after the readers of the stage's previous fill released it) the parity is unambiguous
             wait_counter_bounded(smem_u32(issued), item, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             mbar_wait_bounded(full, use & 1u, abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-            const int sb0 = chunk * a.chunk_sb;
-            const int nsb_c = min(a.chunk_sb, a.nsb - sb0);
+            const int sb0 = part_sb + chunk * a.chunk_sb;
+            const int nsb_c = min(a.chunk_sb, part_end - sb0);
             const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes;
             const uintptr_t srcA = (uintptr_t)Wm + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
             const uintptr_t srcB = srcA + 8 * (uintptr_t)a.row_bytes;
@@ -267,7 +343,7 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
                 ActLane al;
                 al.q = bq_col + gsb * 256;
                 al.valid = bvalid;
-                const float2 dx = *(const float2*)(actd + gsb * 8 + 2 * t);
+                const float2 dx = *(const float2*)(actd_row + gsb * 8 + 2 * t);
                 al.dx0 = dx.x;
                 al.dx1 = dx.y;
                 Unit<FMT>::run(baseA + sbi * Unit<FMT>::BLOCK_BYTES, baseB + sbi * Unit<FMT>::BLOCK_BYTES, h, al, cb, acc);
@@ -284,6 +360,19 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < GROUP_WARPS; w++) v += rbuf[(w * 32 + ls) * 4 + i];
+            if (parted) {
+                // The tile's other parts are other CTAs' work: this part's sums go to the scratch area and the tile's
+                // counter goes up by one.  The count comes back while the group works on its next item.
+                if (ti > 0) finish_pending(true);
+                __stcg(a.parts + ((size_t)gtile * a.n_parts + part) * 128 + gtid, v);
+                named_bar_sync(3 + grp, 128);
+                if (gtid == 0) {
+                    __threadfence();   // cumulative: covers the 128 threads' stores ordered before it by the barrier
+                    pending = atomicAdd(a.part_count + gtile, 1);
+                    pending_tile = gtile;
+                }
+                continue;
+            }
             const int row = tile * TILE_ROWS + (ls >> 2) + 8 * (i >> 1);
             const int col = 2 * (ls & 3) + (i & 1);
             const int Mm = mi == 0 ? a.M : a.M_more[mi - 1];
@@ -296,6 +385,7 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS), 1) gemv_kern
             }
         }
     }
+    if (parted && gtid < 128 && grp < my_items) finish_pending(false);
 }
 
 }  // namespace q38b

@@ -207,6 +207,35 @@ def test_columns_bit_identical_to_single_column(ctx, name):
     assert np.max(np.abs(fast - singles[0].cpu().numpy()) / mag) < REL_TOL
 
 
+@pytest.mark.parametrize("name", ["IQ3_XXS", "IQ3_S", "IQ4_XS", "Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("M,K", [(1, 8448), (37, 17408), (531, 8448), (531, 17408)])
+def test_long_rows_in_k_parts(ctx, name, M, K):
+    """Rows longer than 8192 on the multi-column kernel: the row is cut into K-parts that different CTAs compute and the
+    last one adds up.  The sums match the oracle, do not depend on the column count, the row count of the call or on
+    which launch it is, and accumulate / strided outputs work as for short rows."""
+    f = F.get(name)
+    wn = synth.make_weights(f, M, K, seed=131, scale=scale_for(name))
+    w = dev(wn)
+    xqn = oracle.port.quantize_q8k(synth.make_activations(8, K, seed=132))
+    xq = dev(xqn)
+    y8 = ctx.gemv(f, w, xq, K)
+    assert rel_err(y8.cpu().numpy(), wn, xqn, f, K) < REL_TOL
+    for nb in (2, 7):
+        y = ctx.gemv(f, w, xq[:nb], K)
+        assert torch.equal(y.view(torch.int32), y8[:nb].view(torch.int32)), (name, nb)
+        assert torch.equal(ctx.gemv(f, w, xq[:nb], K), y)          # the tile counters are back at zero
+    if M > 100:
+        cut = 16 * 9 + 5                                            # shards that do not end on a tile boundary
+        top = ctx.gemv(f, dev(wn[:cut]), xq[:7], K)
+        rest = ctx.gemv(f, dev(wn[cut:]), xq[:7], K)
+        assert torch.equal(torch.cat([top, rest], dim=1), y8[:7])
+    buf = torch.full((3, M + 12), 2.0, dtype=torch.float32, device="cuda")
+    ctx.gemv(f, w, xq[:3], K, out=buf[:, :M], accumulate=True)
+    assert torch.equal(buf[:, :M], y8[:3] + 2.0)
+    assert torch.all(buf[:, M:] == 2.0)
+    ctx.check()
+
+
 @pytest.mark.parametrize("name", ["IQ3_XXS", "Q4_K", "Q6_K", "Q8_0"])
 def test_accumulate_and_output_stride(ctx, name):
     f = F.get(name)

@@ -142,6 +142,36 @@ def test_gemv_group_equals_separate_calls(ctx, fmt):
     assert all(float(g.abs().max()) == 0.0 for g in got)
 
 
+@pytest.mark.parametrize("fmt", ["IQ4_XS", "IQ3_XXS", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("nb", [2, 7])
+def test_long_rows_merged_launches_equal_single_ones(ctx, fmt, nb):
+    """Rows of 17408 on several columns (the K-part path of the multi-column kernel): three matrices behind one quantize
+    step, merged into one launch with the quantize folded in, give the bits of one kernel per step; replays agree."""
+    K = 17408
+    Ms = [200, 7, 531]
+    ws = [synth.make_weights(fmt, M, K, seed=70 + i, scale=dp.UNIT_GAIN_SCALE.get(fmt, 1e-4), zero_mean=True) for i, M in enumerate(Ms)]
+    x = synth.make_activations(nb, K, seed=9)
+    outs = []
+    for merge in (True, False):
+        ps = q.Pass(ctx, max_nb=nb)
+        ps.set_merge(merge)
+        src, xq, dst = ps.buffer_f32(K), ps.buffer_q8k(K), ps.buffer_f32(1024)
+        ps.quantize(src, 0, K, xq)
+        off = 0
+        for M, w in zip(Ms, ws):
+            ps.gemv(ps.matrix_upload(fmt, w, K), xq, dst, off)
+            off += M
+        y = np.empty((nb, off), np.float32)
+        for _ in range(2):
+            ps.run_host(nb, src, x, dst, 0, y)
+            ctx.check()
+            outs.append(y.copy())
+        ps.close()
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint32), outs[0].view(np.uint32))
+    assert np.all(np.isfinite(outs[0])) and float(np.abs(outs[0]).max()) > 0
+
+
 def test_merged_replay_equals_one_kernel_per_step(ctx):
     """Shared launches and folded quantize steps change nothing in the results, and fewer kernels run."""
     n_layers = 4
