@@ -19,6 +19,7 @@ using namespace q38b;
 namespace {
 
 constexpr int NGROUPS = 2;
+constexpr int GEMV_WHOLE_ROW_K = 8192;          // longer rows run as K-parts (measured on B200: parts on K = 5120 / 6144 cost more per item than they even out)
 constexpr long long GEMV_PART_ITEMS = 131072;   // (tile, K-part) sums the scratch area of the multi-column kernel holds: 64 MB
 constexpr int GEMV_THREADS = 32 * (1 + NGROUPS * GROUP_WARPS);
 
@@ -89,7 +90,7 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
     // column count, the row count or the GPU count.
     const int n_units = (nsb + 3) / 4;
     const int units_per_part = type == T_Q8_0 ? 2 : 3;
-    a.n_parts = K <= 8192 ? 1 : (n_units + units_per_part - 1) / units_per_part;
+    a.n_parts = K <= GEMV_WHOLE_ROW_K ? 1 : (n_units + units_per_part - 1) / units_per_part;
     if (a.n_parts > GEMV_MAX_PARTS) a.n_parts = GEMV_MAX_PARTS;   // longer parts; the plan fails below if they do not fit
     int max_part = 0;
     for (int q = 0; q <= a.n_parts; q++) a.part_sb0[q] = std::min(nsb, 4 * (int)((long long)n_units * q / a.n_parts));
@@ -142,7 +143,7 @@ int launch_gemv(q38b_ctx* ctx, const Plan& p, cudaStream_t st) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)p.grid);
-    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.blockDim = dim3(GEMV_THREADS + (p.a.n_parts > 1 ? 32 : 0));   // K-parts: one more warp, which adds the parts up
     cfg.dynamicSmemBytes = (size_t)p.smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -412,6 +413,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
         for (int i = 0; i < 4; i++) c->d_code16[i] = (const uint32_t*)t16[i];
         // candidate lists of q38b_topk: 8 columns x TOPK_MAX_CHUNKS lists x TOPK_MAX_K pairs (1.5 MB), so that the decode path never allocates
         if (cudaMalloc(&c->d_parts, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
+        if (cudaMemset(c->d_parts, 0xFF, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }   // PART_EMPTY
         if (cudaMalloc(&c->d_part_count, (size_t)GEMV_PART_ITEMS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         if (cudaMemset(c->d_part_count, 0, (size_t)GEMV_PART_ITEMS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         if (cudaMalloc(&c->d_topk, (size_t)8 * TOPK_MAX_CHUNKS * TOPK_MAX_K * sizeof(TopkPair)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
@@ -694,7 +696,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     }
     {   // more (tile, K-part) sums than the scratch area holds: one launch per block of rows
         const int n_units = (K / 256 + 3) / 4, upp = type == T_Q8_0 ? 2 : 3;
-        const int n_parts = K <= 8192 ? 1 : std::min(GEMV_MAX_PARTS, (n_units + upp - 1) / upp);
+        const int n_parts = K <= GEMV_WHOLE_ROW_K ? 1 : std::min(GEMV_MAX_PARTS, (n_units + upp - 1) / upp);
         const long long rows_per_launch = GEMV_PART_ITEMS / n_parts * TILE_ROWS;
         if (n_parts > 1 && M > rows_per_launch) {
             for (long long m0 = 0; m0 < M; m0 += rows_per_launch) {

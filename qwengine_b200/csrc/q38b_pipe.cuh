@@ -67,14 +67,19 @@ __device__ __forceinline__ int ld_acquire_shared(uint32_t addr) {
     asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ void red_release_shared_add(uint32_t addr, int v) {
+    asm volatile("red.release.cta.shared::cta.add.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// (pause_ns: a background warp's poll leaves the issue slots to the working warps between looks)
 __device__ __forceinline__ bool wait_counter_bounded(uint32_t addr, int than, volatile int* abort_flag, int* status, int code,
-                                                     long long budget = WAIT_BUDGET_CYCLES) {
+                                                     long long budget = WAIT_BUDGET_CYCLES, unsigned pause_ns = 0) {
     if (ld_acquire_shared(addr) > than) return true;
     const long long t0 = clock64();
     for (;;) {
         if (ld_acquire_shared(addr) > than) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > budget) break;
+        if (pause_ns) __nanosleep(pause_ns);
     }
     *abort_flag = 1;
     if (status) atomicOr(status, code);
