@@ -44,7 +44,9 @@ enum q38b_status {
 
 enum q38b_out_kind { Q38B_OUT_F32 = 0, Q38B_OUT_F16 = 1, Q38B_OUT_BF16 = 2 };
 
-/* One context per process and GPU.  Holds the device codebooks, the device status word and launch attributes. */
+/* One context per process and GPU.  Holds the device codebooks, the device status word, launch attributes and the work
+ * areas of the top-k and of the multi-column matvec (64 MB: the K-part sums of rows longer than 8192).  The work areas
+ * serve one launch at a time: issue a context's calls on one stream, or order the streams yourself. */
 int q38b_ctx_create(int device, q38b_ctx** out);
 void q38b_ctx_destroy(q38b_ctx* ctx);
 /* Reads (and clears) the device status word after synchronising `stream`; Q38B_ERR_DEVICE_WAIT if a kernel gave up. */

@@ -448,6 +448,9 @@ int q38b_ctx_check(q38b_ctx* ctx, void* stream) {
     Q38B_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)stream));
     if (bits) {
         Q38B_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), (cudaStream_t)stream));
+        // a multi-column matvec that gave up may have left K-part sums and counts behind: back to the resting state
+        Q38B_CUDA(ctx, cudaMemsetAsync(ctx->d_parts, 0xFF, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float), (cudaStream_t)stream));
+        Q38B_CUDA(ctx, cudaMemsetAsync(ctx->d_part_count, 0, (size_t)GEMV_PART_ITEMS * sizeof(int), (cudaStream_t)stream));
         return Q38B_ERR_DEVICE_WAIT;
     }
     return Q38B_OK;
