@@ -105,6 +105,7 @@ def load_library():
     lib.q38b_debug_set_rowgroup.argtypes = [vp, i32]
     lib.q38b_debug_occupancy_shortfalls.argtypes = [vp, i32]
     lib.q38b_debug_set_one_cta.argtypes = [vp, i32]
+    lib.q38b_debug_set_gemv_part_items.argtypes = [vp, ll]
     lib.q38b_gemv_group.argtypes = [vp, u32, i32, vp, sz, i32, vp, vp, vp, vp, vp]
     _LIB = lib
     return lib
@@ -175,6 +176,10 @@ class Context:
     def debug_set_one_cta(self, mode):
         """Test hook: one CTA per SM for the one-column kernel: 0 never, otherwise wherever such a plan fits (default)."""
         self._rc(self.lib.q38b_debug_set_one_cta(self.h, int(mode)), "q38b_debug_set_one_cta")
+
+    def debug_set_gemv_part_items(self, items):
+        """Test hook: the multi-column kernel's K-part scratch area counts as `items` (tile, part) sums (0: its real size)."""
+        self._rc(self.lib.q38b_debug_set_gemv_part_items(self.h, int(items)), "q38b_debug_set_gemv_part_items")
 
     def set_wait_budget_cycles(self, cycles):
         self._rc(self.lib.q38b_ctx_set_wait_budget_cycles(self.h, int(cycles)), "q38b_ctx_set_wait_budget_cycles")

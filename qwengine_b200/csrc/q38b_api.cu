@@ -95,7 +95,7 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
     int max_part = 0;
     for (int q = 0; q <= a.n_parts; q++) a.part_sb0[q] = std::min(nsb, 4 * (int)((long long)n_units * q / a.n_parts));
     for (int q = 0; q < a.n_parts; q++) max_part = std::max(max_part, a.part_sb0[q + 1] - a.part_sb0[q]);
-    if (a.n_parts > 1 && (long long)a.n_tiles * a.n_parts > GEMV_PART_ITEMS) return Q38B_ERR_NOMEM;   // the scratch area's size
+    if (a.n_parts > 1 && (long long)a.n_tiles * a.n_parts > ctx->part_items) return Q38B_ERR_NOMEM;   // the scratch area's size
     // a CTA's range of (part, tile) items touches at most two neighbouring parts: it stages their activations only
     a.act_sb = a.n_parts == 1 ? nsb : std::min(nsb, 2 * max_part);
     a.off_actd = 256;
@@ -412,6 +412,7 @@ int q38b_ctx_create(int device, q38b_ctx** out) {
             cudaGetSymbolAddress((void**)&t16[2], q38b_iq2s_codes) != cudaSuccess || cudaGetSymbolAddress((void**)&t16[3], q38b_iq1s_codes) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         for (int i = 0; i < 4; i++) c->d_code16[i] = (const uint32_t*)t16[i];
         // candidate lists of q38b_topk: 8 columns x TOPK_MAX_CHUNKS lists x TOPK_MAX_K pairs (1.5 MB), so that the decode path never allocates
+        c->part_items = GEMV_PART_ITEMS;
         if (cudaMalloc(&c->d_parts, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
         if (cudaMemset(c->d_parts, 0xFF, (size_t)GEMV_PART_ITEMS * 128 * sizeof(float)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }   // PART_EMPTY
         if (cudaMalloc(&c->d_part_count, (size_t)GEMV_PART_ITEMS * sizeof(int)) != cudaSuccess) { rc = Q38B_ERR_CUDA; break; }
@@ -481,6 +482,13 @@ int q38b_debug_set_rowgroup(q38b_ctx* ctx, int enabled) {
 int q38b_debug_set_one_cta(q38b_ctx* ctx, int mode) {
     if (!ctx || mode < 0 || mode > 2) return Q38B_ERR_ARG;
     ctx->one_cta = mode ? 1 : 0;
+    return Q38B_OK;
+}
+// Test hook: the multi-column kernel's K-part scratch area counts as `items` (tile, part) sums (0: its real size), so that
+// the launch per block of rows that very tall matrices take can be reached with a small one.
+int q38b_debug_set_gemv_part_items(q38b_ctx* ctx, long long items) {
+    if (!ctx || items < 0 || items > GEMV_PART_ITEMS) return Q38B_ERR_ARG;
+    ctx->part_items = items ? items : GEMV_PART_ITEMS;
     return Q38B_OK;
 }
 // Test hook: enabled = 1 starts counting one-column launches whose CTAs fit an SM less often than their plan assumes;
@@ -700,7 +708,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
     {   // more (tile, K-part) sums than the scratch area holds: one launch per block of rows
         const int n_units = (K / 256 + 3) / 4, upp = type == T_Q8_0 ? 2 : 3;
         const int n_parts = K <= GEMV_WHOLE_ROW_K ? 1 : std::min(GEMV_MAX_PARTS, (n_units + upp - 1) / upp);
-        const long long rows_per_launch = GEMV_PART_ITEMS / n_parts * TILE_ROWS;
+        const long long rows_per_launch = ctx->part_items / n_parts * TILE_ROWS;
         if (n_parts > 1 && M > rows_per_launch) {
             for (long long m0 = 0; m0 < M; m0 += rows_per_launch) {
                 const int m = (int)std::min<long long>(rows_per_launch, M - m0);

@@ -17,6 +17,7 @@ struct q38b_ctx {
     int uniform_columns = 0;   // 1: single-column calls also run the tensor-core kernel (bit-identical to columns of wider calls)
     long long wait_budget_cycles = 4000000000LL;   // bounded waits on other GPUs (q38b_ctx_set_wait_budget_cycles)
     int* d_status = nullptr;
+    long long part_items = 0;      // (tile, K-part) sums one multi-column launch may use of d_parts (test hook: fewer)
     float* d_parts = nullptr;      // multi-column matvec: (tile, K-part) sums of tiles that two groups share; one stream at a time
     int* d_part_count = nullptr;   // ... and how many parts of each tile are written (zero between launches)
     void* d_topk = nullptr;    // work area of q38b_topk (candidate lists)

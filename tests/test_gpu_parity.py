@@ -233,6 +233,13 @@ def test_long_rows_in_k_parts(ctx, name, M, K):
     ctx.gemv(f, w, xq[:3], K, out=buf[:, :M], accumulate=True)
     assert torch.equal(buf[:, :M], y8[:3] + 2.0)
     assert torch.all(buf[:, M:] == 2.0)
+    if M > 100:
+        # a matrix with more (tile, part) sums than the scratch area holds runs as one launch per block of rows
+        ctx.debug_set_gemv_part_items(64)
+        try:
+            assert torch.equal(ctx.gemv(f, w, xq[:7], K), y8[:7])
+        finally:
+            ctx.debug_set_gemv_part_items(0)
     ctx.check()
 
 
