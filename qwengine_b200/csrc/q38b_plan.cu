@@ -92,10 +92,10 @@ struct q38b_pass {
     // What each recorded graph was captured with: a graph is recorded again when any of it has changed since (steps
     // appended, merging or peer stores switched, a context option that picks kernels or launch attributes).
     struct Captured {
-        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, one_cta;
+        size_t n_ops; int peer_store, merge_steps, uniform_columns, pdl, n_ranks, peers_connected, rowgroup, one_cta; long long part_items;
         bool operator==(const Captured& o) const {
             return n_ops == o.n_ops && peer_store == o.peer_store && merge_steps == o.merge_steps && uniform_columns == o.uniform_columns &&
-                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && one_cta == o.one_cta;
+                   pdl == o.pdl && n_ranks == o.n_ranks && peers_connected == o.peers_connected && rowgroup == o.rowgroup && one_cta == o.one_cta && part_items == o.part_items;
         }
     };
     Captured captured[9] = {};
@@ -623,7 +623,7 @@ int q38b_pass_run(q38b_pass* p, int nb, void* stream) {
     if (!p || nb < 1 || nb > p->max_nb) return Q38B_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const q38b_pass::Captured now = {p->ops.size(), p->peer_store, p->merge_steps, p->ctx->uniform_columns, p->ctx->pass_pdl,
-                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->one_cta};
+                                     p->ctx->n_ranks, p->ctx->peers_connected, p->ctx->rowgroup, p->ctx->one_cta, p->ctx->part_items};
     if (p->graphs[nb] && !(now == p->captured[nb])) {
         cudaGraphExecDestroy(p->graphs[nb]);
         p->graphs[nb] = nullptr;
