@@ -63,6 +63,9 @@ int format_alignment(uint32_t t) {
     }
 }
 
+// 4-super-block units per K-part: as long as two parts of activations for 8 columns and three stages of 16 rows fit
+static int gemv_units_per_part(uint32_t type) { return type == T_Q8_0 ? 2 : (type == T_Q6_K || type == T_Q5_K) ? 3 : 4; }
+
 struct Plan {
     GemvArgs a;
     int grid;
@@ -85,11 +88,11 @@ int plan_gemv(const q38b_ctx* ctx, uint32_t type, int K, const int* Ms, int n_ma
         if (i < n_mats) a.n_tiles += (Ms[i] + TILE_ROWS - 1) / TILE_ROWS;
     }
     for (int i = n_mats; i < GEMV_MAX_MATS; i++) a.tile_start[i] = a.n_tiles;
-    // K-parts for rows longer than 8192: about 12 super-blocks each (8 for Q8_0's larger blocks), boundaries at multiples
-    // of 4 super-blocks.  A rule of K and the format alone, so that a sum is built from the same pieces whatever the
+    // K-parts for rows longer than 8192: up to 16 super-blocks each (12 for Q5_K / Q6_K, 8 for Q8_0: larger blocks),
+    // boundaries at multiples of 4 super-blocks.  A rule of K and the format alone, so that a sum is built from the same pieces whatever the
     // column count, the row count or the GPU count.
     const int n_units = (nsb + 3) / 4;
-    const int units_per_part = type == T_Q8_0 ? 2 : 3;
+    const int units_per_part = gemv_units_per_part(type);
     a.n_parts = K <= GEMV_WHOLE_ROW_K ? 1 : (n_units + units_per_part - 1) / units_per_part;
     if (a.n_parts > GEMV_MAX_PARTS) a.n_parts = GEMV_MAX_PARTS;   // longer parts; the plan fails below if they do not fit
     int max_part = 0;
@@ -706,7 +709,7 @@ int q38b_gemv_q8k_scatter(q38b_ctx* ctx, uint32_t type, const void* W, size_t ro
         }
     }
     {   // more (tile, K-part) sums than the scratch area holds: one launch per block of rows
-        const int n_units = (K / 256 + 3) / 4, upp = type == T_Q8_0 ? 2 : 3;
+        const int n_units = (K / 256 + 3) / 4, upp = gemv_units_per_part(type);
         const int n_parts = K <= GEMV_WHOLE_ROW_K ? 1 : std::min(GEMV_MAX_PARTS, (n_units + upp - 1) / upp);
         const long long rows_per_launch = ctx->part_items / n_parts * TILE_ROWS;
         if (n_parts > 1 && M > rows_per_launch) {

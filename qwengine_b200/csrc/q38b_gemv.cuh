@@ -11,14 +11,14 @@
 //     partial sums are added in a fixed order through shared memory, so results do not depend on timing;
 //   * activations (Q8_K int8 values and block scales of all columns) and the codebook are staged in shared memory
 //     once per CTA;
-//   * rows longer than 8192 are cut into K-parts of about 12 super-blocks (a rule of K and the format alone).  The work
+//   * rows longer than 8192 are cut into K-parts of 8 to 16 super-blocks (a rule of K and the format alone).  The work
 //     items (part, tile), part-major, are dealt to the CTAs as equal contiguous ranges: a CTA then needs the
 //     activations of at most two neighbouring parts, which leaves the shared memory to the weight stages, and 320
 //     tiles of 68 super-blocks keep 148 SMs evenly busy instead of 24 of them working a second round.  A part's sums
 //     go to a scratch area in global memory and the consumers carry on; a further warp of the CTA counts the tile's
 //     parts (a counter per tile) and, where it counted the last one, reads them all back, adds them in part order and
 //     stores the row sums -- the result does not depend on who computed what or when.  (Measured on B200, seven
-//     columns, 5120 x 17408 IQ4_XS after its SwiGLU: 40.4 us as two launches over the halves of K, 31.5 us this way.
+//     columns, 5120 x 17408 IQ4_XS after its SwiGLU: 40.4 us as two launches over the halves of K, 30.8 us this way.
 //     The consumers counting and adding themselves, with fences: 33.3 us.  Parts on rows of 5120: in_proj 17 -> 26 us.)
 // Every column is computed by the same instructions whatever nb is, so column c of an nb-column call is
 // bit-identical to a 1-column call on that column (the reference promises the same: src/cuda/gemv.cuh:31-34).
