@@ -368,6 +368,9 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS + (PARTED ? 1 
     // K-parts: (part, tile) of this group's next item, stepped NGROUPS items at a time
     int part_next = parted ? (int)((item_lo + grp) / a.n_tiles) : 0;
     int gtile_next = parted ? (int)(item_lo + grp - (long long)part_next * a.n_tiles) : 0;
+    const uint32_t row_bytes_lo = (uint32_t)a.row_bytes;
+    int ring_stage = (grp * a.n_chunks) % a.n_stages;   // stage and use count of this group's next fill
+    uint32_t ring_use = (uint32_t)((grp * a.n_chunks) / a.n_stages);
     for (int ti = 0;; ti++) {
         const int k = grp + NGROUPS * ti;                // this CTA's work item k
         if (k >= my_items) break;
@@ -379,14 +382,17 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS + (PARTED ? 1 
         }
         const int mi = (gtile >= a.tile_start[1]) + (gtile >= a.tile_start[2]);
         const int tile = gtile - a.tile_start[mi];        // tile of matrix mi
-        const uint8_t* Wm = mi == 0 ? a.W : a.W_more[mi - 1];
+        const uint32_t Wm_lo = (uint32_t)(uintptr_t)(mi == 0 ? a.W : a.W_more[mi - 1]);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const int rowA = tile * TILE_ROWS + g, rowB = rowA + 8;
+        const int rowA = tile * TILE_ROWS + g;
         const int part_sb = parted ? a.part_sb0[part] : 0, part_end = parted ? a.part_sb0[part + 1] : a.nsb;
         for (int chunk = 0; chunk < a.n_chunks; chunk++) {
-            const int item = k * a.n_chunks + chunk;
-            const int stage = item % a.n_stages;
-            const uint32_t use = (uint32_t)(item / a.n_stages);
+            const int item = k * a.n_chunks + chunk;      // fill number; its stage and use are stepped, not divided out
+            const int stage = ring_stage;
+            const uint32_t use = ring_use;
+            const int step = chunk + 1 < a.n_chunks ? 1 : 1 + (NGROUPS - 1) * a.n_chunks;   // on to this group's next item
+            ring_stage += step;
+            while (ring_stage >= a.n_stages) { ring_stage -= a.n_stages; ring_use++; }
             const uint32_t full = smem_u32(&bars[stage]);
             const uint32_t empty = smem_u32(&bars[MAX_STAGES + stage]);
             // a group reads only its own items' fills, so it skips uses of a barrier: once the fill has been issued (the
@@ -396,10 +402,11 @@ __global__ void __launch_bounds__(32 * (1 + NGROUPS * GROUP_WARPS + (PARTED ? 1 
             const int sb0 = part_sb + chunk * a.chunk_sb;
             const int nsb_c = min(a.chunk_sb, part_end - sb0);
             const uint8_t* st = smem + a.off_stage + (size_t)stage * a.stage_bytes;
-            const uintptr_t srcA = (uintptr_t)Wm + (uintptr_t)rowA * a.row_bytes + (uintptr_t)sb0 * Unit<FMT>::BLOCK_BYTES;
-            const uintptr_t srcB = srcA + 8 * (uintptr_t)a.row_bytes;
-            const uint8_t* baseA = st + (size_t)g * a.slot_stride + (srcA & 15);
-            const uint8_t* baseB = st + (size_t)(g + 8) * a.slot_stride + (srcB & 15);
+            // a row slice sits in its slot at the low 4 bits of its global address (32-bit arithmetic is enough for those)
+            const uint32_t srcA = Wm_lo + (uint32_t)rowA * row_bytes_lo + (uint32_t)sb0 * Unit<FMT>::BLOCK_BYTES;
+            const uint32_t srcB = srcA + 8u * row_bytes_lo;
+            const uint8_t* baseA = st + g * a.slot_stride + (srcA & 15u);
+            const uint8_t* baseB = st + (g + 8) * a.slot_stride + (srcB & 15u);
             for (int u = gw; u < 2 * nsb_c; u += GROUP_WARPS) {
                 const int sbi = u >> 1, h = u & 1;
                 const int gsb = sb0 + sbi;
